@@ -1,0 +1,247 @@
+/*
+ * mfb200.h — C ABI of the B200-native MoE feed-forward path.
+ *
+ * The reference engine (Swift + Metal) has no plugin or FFI surface; its MoE path sits behind Swift
+ * classes whose methods encode GPU work into a caller-owned command buffer.  Each entry point below
+ * replaces one of those encode methods (cited per function, paths relative to the reference project
+ * root).  Conventions, all taken from that surface:
+ *   - every buffer is caller-owned device memory passed as a plain pointer (the reference passes
+ *     MTLBuffer + byte offset); kernels never allocate.  A handle owns only its scratch arena;
+ *   - work is enqueued on the caller's stream (`stream` is a cudaStream_t passed as void*; the
+ *     reference's MTLCommandBuffer) and is asynchronous; nothing here synchronises the device;
+ *   - every call returns an int32 status, 0 = MFB_OK; nothing throws or aborts.  The text of the last
+ *     failure on the calling thread is available from mfb_last_error();
+ *   - handles are thread-compatible, not thread-safe, like the reference's wrappers;
+ *   - there is no CPU fallback and no backend dispatch behind this ABI: without a CUDA device every
+ *     compute call fails with MFB_ERR_CUDA.
+ */
+#ifndef MFB200_H
+#define MFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MFB_OK 0
+#define MFB_ERR_INVALID_ARGUMENT 1   /* contract violation (the reference traps with precondition) */
+#define MFB_ERR_UNSUPPORTED_SHAPE 2  /* shape outside what the kernels handle */
+#define MFB_ERR_CUDA 3               /* CUDA runtime error; text in mfb_last_error() */
+#define MFB_ERR_CAPACITY 4           /* more tokens than the handle's scratch arena was created for */
+#define MFB_ERR_ALLOC 5
+#define MFB_ERR_DEVICE_STATUS 6      /* a kernel reported a bounded wait that ran out or a failed self-check */
+#define MFB_ERR_IO 7                 /* staging source too short / unreadable (StreamerError.sizeMismatch) */
+#define MFB_ERR_NO_SLOT 8            /* expert cache cannot place the requested misses */
+/* grouping validation, one code per PrefillMoEGroupingError case
+ * (Sources/Mference/Kernels/Prefill/MoE/PrefillMoEGrouping.swift:52-63) */
+#define MFB_ERR_GROUP_INVALID_QUERY_COUNT 101
+#define MFB_ERR_GROUP_INVALID_TOP_K 102
+#define MFB_ERR_GROUP_INVALID_NUM_EXPERTS 103
+#define MFB_ERR_GROUP_INVALID_TILE_EXPERT_COUNT 104
+#define MFB_ERR_GROUP_PAIR_COUNT_MISMATCH 105
+#define MFB_ERR_GROUP_TOKEN_OUT_OF_RANGE 106
+#define MFB_ERR_GROUP_RANK_OUT_OF_RANGE 107
+#define MFB_ERR_GROUP_EXPERT_OUT_OF_RANGE 108
+#define MFB_ERR_GROUP_DUPLICATE_TOKEN_RANK 109
+#define MFB_ERR_GROUP_SORT_KEY_COUNT_MISMATCH 110
+
+#define MFB_DT_BF16 0
+#define MFB_DT_F16 1
+#define MFB_DT_F32 2
+
+#define MFB_ACT_SILU 0       /* Qwen SwiGLU (moe.metal function constant 4) */
+#define MFB_ACT_GELU_TANH 1  /* Gemma gelu_pytorch_tanh */
+
+#define MFB_ROUTER_SOFTMAX_TOPK 0   /* Sources/Mference/Metal/MoE/moe.metal:190-345 */
+#define MFB_ROUTER_SQRTSOFTPLUS 1   /* moe.metal:737-845 */
+
+#define MFB_MAX_TOP_K 16
+#define MFB_MAX_EXPERTS 512
+
+/* Nine sub-tensor byte offsets inside one expert blob, common to every expert of a layer.
+ * Replaces MoEExpertOffsets (Sources/Mference/Kernels/MoE/MoE.swift:4-29); same field order, 36 bytes.
+ * This implementation additionally requires every offset to be a multiple of 16 bytes. */
+typedef struct mfb_expert_offsets {
+    uint32_t gate_w, gate_s, gate_b;
+    uint32_t up_w, up_s, up_b;
+    uint32_t down_w, down_s, down_b;
+} mfb_expert_offsets;
+
+/* One (token, expert, rank, weight) route.  Replaces PrefillTokenExpertPair
+ * (Sources/Mference/Kernels/Prefill/MoE/PrefillRouter.swift:4-28); 16 bytes, the fp16 weight bits sit in
+ * the low half of weight_bits. */
+typedef struct mfb_pair {
+    uint32_t token, expert, rank, weight_bits;
+} mfb_pair;
+
+/* PrefillMoEGroup / PrefillMoETile (PrefillMoEGrouping.swift:3-29). */
+typedef struct mfb_group {
+    uint32_t expert, pair_start, pair_count;
+} mfb_group;
+typedef struct mfb_tile {
+    uint32_t group_start, group_count, pair_start, pair_count;
+} mfb_tile;
+
+/* Shape and numerics of one MoE layer family.  Plays the part of MoE.init's specialisation arguments
+ * (MoE.swift:65-70) and of the Metal function constants 0-5 / 40-43 (moe.metal:9-25). */
+typedef struct mfb_moe_config {
+    uint32_t d;             /* hidden size, multiple of 64 */
+    uint32_t f;             /* expert intermediate size, multiple of 64 */
+    uint32_t num_experts;   /* <= MFB_MAX_EXPERTS */
+    uint32_t top_k;         /* <= MFB_MAX_TOP_K */
+    uint32_t bits;          /* routed expert code width: 4 or 2 */
+    uint32_t shared_bits;   /* shared expert code width: 4 or 2; 0 = the layer has no shared expert */
+    uint32_t group_size;    /* 64 */
+    uint32_t scale_dtype;   /* MFB_DT_F16 (MLX files) or MFB_DT_BF16 (reference .gturbo files) */
+    uint32_t x_dtype;       /* activation dtype in and out: MFB_DT_BF16 or MFB_DT_F16 */
+    uint32_t activation;    /* MFB_ACT_* */
+    uint32_t router_mode;   /* MFB_ROUTER_* */
+    float swiglu_limit;     /* > 0: clamp gate <= limit, up in [-limit, limit] before the activation */
+    float route_scale;      /* sqrt-softplus mode only */
+    float rms_eps;          /* 1e-6 in the reference (RealForwardRunner.swift:2583) */
+    uint32_t max_tokens;    /* scratch arena capacity in token rows per call */
+    uint32_t flags;         /* MFB_FLAG_* */
+} mfb_moe_config;
+
+#define MFB_FLAG_PREFILL_TENSOR_CORE 1u /* allocate the arena of the tcgen05 grouped-GEMM path */
+
+/* Device-resident weights of one layer. */
+typedef struct mfb_layer_weights {
+    const void* router_w;          /* bf16 [num_experts, d] */
+    const float* logit_bias;       /* optional f32 [num_experts], added to the logits */
+    const void* per_expert_scale;  /* optional bf16 [num_experts] (softmax mode) */
+    const float* correction_bias;  /* optional f32 [num_experts] (sqrt-softplus mode, selection only) */
+    const void* norm_w;            /* optional bf16 [d]; NULL = weight 1 */
+    const uint8_t* pool;           /* slab of expert slots */
+    uint64_t slot_stride;          /* bytes between slots */
+    const int16_t* slot_of;        /* optional device table expert -> slot (-1 = not resident); NULL = identity */
+    const uint8_t* shared_blob;    /* shared expert blob, or NULL */
+    mfb_expert_offsets routed_off;
+    mfb_expert_offsets shared_off;
+} mfb_layer_weights;
+
+typedef struct mfb_moe mfb_moe;
+
+const char* mfb_last_error(void);
+int32_t mfb_version(void);
+/* Fills the offsets of the canonical blob layout (gate W,S,B · up W,S,B · down W,S,B, row-major). */
+int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes);
+
+/* MoE.init / deinit (MoE.swift:65-151): builds the handle and its scratch arena. */
+int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out);
+int32_t mfb_moe_destroy(mfb_moe* moe);
+/* Reads and clears the device status word that kernels set when a bounded wait runs out. Synchronises `stream`. */
+int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status);
+
+/* ---- router -------------------------------------------------------------------------------------------- */
+
+/* Gate GEMV over an unquantised bf16 gate: logits[t,e] = sum_i w[e,i] * x[t,i] (+ bias[e]).
+ * Replaces router_gemv_bf16_r4 as driven by MoEDeepseekV4.encodeRouterGemv
+ * (Sources/Mference/Kernels/MoE/MoEDeepseekV4.swift:153-173; kernel moe.metal:162-185). */
+int32_t mfb_router_logits(mfb_moe* moe, void* stream, const void* x, uint32_t ldx, uint32_t n_tokens,
+                          const void* router_w, const float* logit_bias, float* logits);
+/* Top-k select + routing weights for n_tokens rows of logits.  Ties go to the lower expert index.
+ * Replaces router_topk_select_k8(_par) / router_topk_select_sqrtsoftplus_k6(_par) (moe.metal:190-345,
+ * 737-845) and the selection tail of prefill_router_gemma4_block (Sources/Mference/Metal/Prefill/prefill.metal:586-628). */
+int32_t mfb_router_select(mfb_moe* moe, void* stream, const float* logits, uint32_t n_tokens,
+                          const void* per_expert_scale, const float* correction_bias, uint32_t* out_idx,
+                          uint16_t* out_w);
+/* Both steps.  Replaces MoE.encodeRouterGemma4 (MoE.swift:153-203) for one row and
+ * PrefillRouter.encodeGemma4Block (PrefillRouter.swift:37-89) for a block of rows. */
+int32_t mfb_router_topk(mfb_moe* moe, void* stream, const void* x, uint32_t ldx, uint32_t n_tokens,
+                        const mfb_layer_weights* w, uint32_t* out_idx, uint16_t* out_w);
+/* Expert id -> slot byte offset through the device-resident slot table, plus an all-hit flag per token row.
+ * Replaces MoE.encodeSlotLookup (MoE.swift:302-330; kernel router_slot_lookup_k8, moe.metal:594-617). */
+int32_t mfb_slot_lookup(mfb_moe* moe, void* stream, const uint32_t* idx, uint32_t n_tokens,
+                        const int16_t* slot_of, uint64_t slot_stride, uint64_t* out_offsets, uint32_t* out_all_hit);
+
+/* ---- decode -------------------------------------------------------------------------------------------- */
+
+/* Routed + shared expert FFN with the weighted combine for n_tokens rows:
+ *   y[t] = dtype( residual[t] + shared(x[t]) + sum_r w[t,r] * ffn_{idx[t,r]}(x[t]) ), fp32, rank order.
+ * Each distinct expert's weights are read once for all rows routed to it.  Replaces
+ * MoE.encodeRoutedPersistentPhase1U16Load + encodeRoutedPersistentPhase2Reduce (MoE.swift:220-253, 400-440),
+ * the slot-map form MoE.encodeSlotMapGuardedFFN (MoE.swift:332-398) when w->slot_of is given, and
+ * SharedExpertRuntime.encode (Sources/Mference/Kernels/MoE/SharedExpertInt4.swift:193-222).
+ * residual may be NULL; y may alias residual. */
+int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                       uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, const void* residual,
+                       void* y);
+/* The two halves of mfb_moe_decode, for callers that run cache-hit experts first and the misses after their
+ * fill.  mfb_moe_experts computes the down-projection rows of the listed rank slots (host array; NULL = all
+ * top_k slots) and, when with_shared != 0, of the shared expert, into the handle's arena; mfb_moe_combine then
+ * reduces every slot in rank order.  A hit/miss split gives bit-identical results to one full call.
+ * Replaces MoE.encodeRoutedPersistentPhase1SubsetU16Load (MoE.swift:255-298) followed by
+ * MoE.encodeRoutedPersistentPhase2Reduce (MoE.swift:400-440). */
+int32_t mfb_moe_experts(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                        uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w,
+                        const uint32_t* active_slots, uint32_t active_count, int32_t with_shared);
+int32_t mfb_moe_combine(mfb_moe* moe, void* stream, uint32_t n_tokens, const uint16_t* route_w, int32_t with_shared,
+                        const void* residual, void* y);
+/* One whole layer on the residual stream: h_out = h_in + MoE(RMSNorm(h_in)), router included.
+ * Mirrors the MoE section of RealForwardRunner.produceToken
+ * (Sources/Mference/Runtime/Inference/RealForwardRunner.swift:2811-3253) with every expert resident. */
+int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* h_in, void* h_out,
+                      uint32_t n_tokens);
+/* n_layers of the above back to back (the per-layer loop RealForwardRunner.swift:2646). */
+int32_t mfb_moe_stack(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
+                      void* hidden, uint32_t n_tokens);
+
+/* ---- prefill / ragged batch ---------------------------------------------------------------------------- */
+
+/* Device-side sort of the routing table by (expert, token, rank): sorted pairs, per-expert offsets
+ * (0xFFFFFFFF = absent) and counts, the compacted group list and its length.  Same order as
+ * PrefillMoEGrouping.groupTokenExpertPairs (PrefillMoEGrouping.swift:90-192) without sort keys.
+ * All outputs are device pointers; out_groups holds up to num_experts entries. */
+int32_t mfb_moe_group(mfb_moe* moe, void* stream, const uint32_t* idx, const uint16_t* route_w, uint32_t n_tokens,
+                      mfb_pair* out_sorted, uint32_t* out_offsets, uint32_t* out_counts, mfb_group* out_groups,
+                      uint32_t* out_n_groups);
+/* Host-side grouping with the reference's validation, optional expert sort keys and tiles; plain host
+ * arrays in and out.  Replaces PrefillMoEGrouping.groupTokenExpertPairs for callers that hold the table on
+ * the host (RealForwardRunner.swift:2276-2297). err_a / err_b carry the offending values. */
+int32_t mfb_moe_group_host(const mfb_pair* pairs, int64_t n_pairs, int64_t query_count, int64_t top_k,
+                           int64_t num_experts, int64_t tile_expert_count, const uint64_t* expert_sort_keys,
+                           int64_t n_sort_keys, mfb_pair* out_sorted, uint32_t* out_offsets, uint32_t* out_counts,
+                           mfb_group* out_groups, uint32_t* out_n_groups, mfb_tile* out_tiles,
+                           uint32_t* out_n_tiles, uint32_t* err_a, uint32_t* err_b);
+/* Grouped routed FFN over sorted pairs ("gather-QMM"): partial[(token*top_k + rank), :] = ffn_expert(x[token]).
+ * partial is f32 [n_tokens*top_k, d].  Replaces PrefillGroupedRoutedMoE.encodeStreamedBatched
+ * (Sources/Mference/Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:391-466; kernels prefill.metal:748-820). */
+int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
+                                const uint32_t* n_groups, float* partial);
+/* h2[t,:] = sum_r w[t,r] * partial[t,r,:] in rank order (+ residual).  Replaces
+ * PrefillMoE.encodeReduceTokenMajor (Sources/Mference/Kernels/Prefill/MoE/PrefillMoE.swift:11-38). */
+int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w, uint32_t n_tokens,
+                       const void* residual, void* y);
+/* Whole prefill layer for a block of rows: h_out = h_in + MoE(RMSNorm(h_in)); router, sort, grouped FFN,
+ * shared expert and reduce.  Mirrors RealForwardRunner.executePrefillChunk's MoE section
+ * (RealForwardRunner.swift:2173-2498). */
+int32_t mfb_moe_layer_prefill(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* h_in, void* h_out,
+                              uint32_t n_tokens);
+
+/* ---- glue ---------------------------------------------------------------------------------------------- */
+
+/* out = dtype(x * rsqrt(mean(x^2) + eps) * w).  Replaces rmsnorm_bf16w
+ * (Sources/Mference/Metal/Primitives/rmsnorm.metal:32-93). */
+int32_t mfb_rmsnorm(mfb_moe* moe, void* stream, const void* x, const void* w_bf16, uint32_t n_rows, void* out);
+/* out = dtype(a + b).  Replaces residual_add_fp16 (Sources/Mference/Metal/Primitives/utility.metal:83-92). */
+int32_t mfb_residual_add(mfb_moe* moe, void* stream, const void* a, const void* b, uint64_t n, void* out);
+
+/* ---- synthetic weights (benchmark and test support) ---------------------------------------------------- */
+
+/* Fills device memory with the labelled SplitMix64 streams the benchmark configurations are defined on:
+ * uniform codes, |N(0,0.02)| scales, N(0,0.01) biases, N(0,0.02) bf16 router rows, N(0,1) activations.
+ * Stream labels follow Sources/MferenceValidation/Support/PRNG/SeedTree.swift:12-19. */
+int32_t mfb_synth_expert_pool(void* stream, uint64_t root_seed, uint32_t layer, uint32_t first_expert,
+                              uint32_t n_experts, int32_t shared, uint32_t bits, uint32_t scale_dtype, uint32_t d,
+                              uint32_t f, uint8_t* pool, uint64_t slot_stride);
+int32_t mfb_synth_normal(void* stream, uint64_t root_seed, const char* label, uint64_t n, double mean, double std,
+                         int32_t absolute, uint32_t dtype, void* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MFB200_H */

@@ -1,0 +1,417 @@
+// C ABI entry points: argument validation, the handle and its scratch arena, and the launch sequences.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "prefill_tc.cuh"
+
+namespace mfb {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return MFB_ERR_CUDA;
+}
+
+namespace {
+
+bool pow2_or_wide(uint32_t cols, uint32_t bits) {
+    const uint32_t pieces = cols * bits / 128;
+    if (pieces == 0) return false;
+    return pieces >= 32 || (pieces & (pieces - 1)) == 0;
+}
+
+bool offsets_aligned(const mfb_expert_offsets& o) {
+    const uint32_t* p = &o.gate_w;
+    for (int i = 0; i < 9; ++i)
+        if (p[i] % 16) return false;
+    return true;
+}
+
+template <typename T>
+cudaError_t dev_alloc(T*& p, size_t count) {
+    return cudaMalloc((void**)&p, (count ? count : 1) * sizeof(T));
+}
+
+void free_arena(Arena& a) {
+    cudaFree(a.logits); cudaFree(a.idx); cudaFree(a.route_w); cudaFree(a.xn); cudaFree(a.sorted);
+    cudaFree(a.chunk_hist); cudaFree(a.offsets); cudaFree(a.counts); cudaFree(a.groups); cudaFree(a.n_groups);
+    cudaFree(a.tile_prefix); cudaFree(a.acts); cudaFree(a.partial); cudaFree(a.xs16); cudaFree(a.acts16);
+    cudaFree(a.status);
+    a = Arena();
+}
+
+int32_t check_handle(const mfb_moe* m, uint32_t n_tokens) {
+    MFB_REQUIRE(m != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
+    MFB_REQUIRE(n_tokens <= m->cfg.max_tokens, MFB_ERR_CAPACITY, "%u tokens exceed the arena capacity of %u", n_tokens,
+                m->cfg.max_tokens);
+    return MFB_OK;
+}
+
+int32_t check_weights(const mfb_moe* m, const mfb_layer_weights* w, bool need_router) {
+    MFB_REQUIRE(w != nullptr, MFB_ERR_INVALID_ARGUMENT, "layer weights are NULL");
+    MFB_REQUIRE(!need_router || w->router_w != nullptr, MFB_ERR_INVALID_ARGUMENT, "router weights are NULL");
+    MFB_REQUIRE(w->pool != nullptr, MFB_ERR_INVALID_ARGUMENT, "expert pool is NULL");
+    MFB_REQUIRE(((uintptr_t)w->pool % 16) == 0 && (w->slot_stride % 16) == 0, MFB_ERR_INVALID_ARGUMENT,
+                "pool base and slot stride must be multiples of 16 bytes");
+    MFB_REQUIRE(offsets_aligned(w->routed_off), MFB_ERR_INVALID_ARGUMENT, "routed expert offsets must be multiples of 16 bytes");
+    if (w->shared_blob) {
+        MFB_REQUIRE(m->cfg.shared_bits != 0, MFB_ERR_INVALID_ARGUMENT, "shared blob given but the handle has shared_bits = 0");
+        MFB_REQUIRE(((uintptr_t)w->shared_blob % 16) == 0 && offsets_aligned(w->shared_off), MFB_ERR_INVALID_ARGUMENT,
+                    "shared expert blob and offsets must be multiples of 16 bytes");
+    }
+    return MFB_OK;
+}
+
+uint32_t all_slots(const mfb_moe* m) { return (1u << m->cfg.top_k) - 1u; }
+
+int32_t run_experts(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                    uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, uint32_t slot_mask, bool with_shared) {
+    const mfb_moe_config& c = m->cfg;
+    Arena& a = m->a;
+    const bool shared = with_shared && w->shared_blob != nullptr;
+    MFB_CUDA(launch_group(s, idx, route_w, n_tokens, c.top_k, c.num_experts, slot_mask, shared ? 1 : 0, 0, a, a.sorted,
+                          a.offsets, a.counts, a.groups, a.n_groups, nullptr));
+    DecodeArgs d;
+    d.w = w; d.d = c.d; d.f = c.f; d.num_experts = c.num_experts; d.top_k = c.top_k; d.bits = c.bits;
+    d.shared_bits = c.shared_bits; d.scale_dtype = c.scale_dtype; d.activation = c.activation;
+    d.swiglu_limit = c.swiglu_limit; d.x = x; d.x_dtype = (int)c.x_dtype; d.ldx = ldx; d.sorted = a.sorted;
+    d.groups = a.groups; d.n_groups = a.n_groups;
+    const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
+    d.max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts) + (shared ? 1u : 0u);
+    d.acts = a.acts; d.partial = a.partial; d.slots = c.top_k + 1;
+    MFB_CUDA(launch_decode_ffn(s, d));
+    return MFB_OK;
+}
+
+}  // namespace
+}  // namespace mfb
+
+using namespace mfb;
+
+extern "C" const char* mfb_last_error(void) { return g_error; }
+extern "C" int32_t mfb_version(void) { return 100; }
+
+extern "C" int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes) {
+    MFB_REQUIRE(off && blob_bytes, MFB_ERR_INVALID_ARGUMENT, "layout: NULL output");
+    MFB_REQUIRE(bits == 4 || bits == 2, MFB_ERR_INVALID_ARGUMENT, "layout: bits must be 4 or 2");
+    MFB_REQUIRE(d && f && d % 64 == 0 && f % 64 == 0, MFB_ERR_INVALID_ARGUMENT, "layout: d and f must be multiples of 64");
+    const uint64_t wbytes = (uint64_t)d * f * bits / 8, sbytes = (uint64_t)d * f / 64 * 2;
+    MFB_REQUIRE(3 * (wbytes + 2 * sbytes) <= 0xFFFFFFFFull, MFB_ERR_UNSUPPORTED_SHAPE, "layout: blob exceeds 4 GiB");
+    uint32_t o = 0;
+    uint32_t* p = &off->gate_w;
+    for (int i = 0; i < 9; ++i) { p[i] = o; o += (uint32_t)(i % 3 == 0 ? wbytes : sbytes); }
+    *blob_bytes = o;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
+    MFB_REQUIRE(cfg && out, MFB_ERR_INVALID_ARGUMENT, "create: NULL argument");
+    *out = nullptr;
+    const mfb_moe_config& c = *cfg;
+    MFB_REQUIRE(c.d && c.f && c.d % 64 == 0 && c.f % 64 == 0, MFB_ERR_INVALID_ARGUMENT, "d and f must be multiples of 64");
+    MFB_REQUIRE(c.group_size == 64, MFB_ERR_UNSUPPORTED_SHAPE, "group size must be 64");
+    MFB_REQUIRE(c.bits == 4 || c.bits == 2, MFB_ERR_INVALID_ARGUMENT, "bits must be 4 or 2");
+    MFB_REQUIRE(c.shared_bits == 0 || c.shared_bits == 4 || c.shared_bits == 2, MFB_ERR_INVALID_ARGUMENT, "shared_bits must be 0, 4 or 2");
+    MFB_REQUIRE(c.num_experts >= 1 && c.num_experts <= MFB_MAX_EXPERTS, MFB_ERR_UNSUPPORTED_SHAPE, "num_experts must be in 1..%d", MFB_MAX_EXPERTS);
+    MFB_REQUIRE(c.top_k >= 1 && c.top_k <= MFB_MAX_TOP_K, MFB_ERR_UNSUPPORTED_SHAPE, "top_k must be in 1..%d", MFB_MAX_TOP_K);
+    MFB_REQUIRE(c.scale_dtype == MFB_DT_F16 || c.scale_dtype == MFB_DT_BF16, MFB_ERR_INVALID_ARGUMENT, "scale dtype must be fp16 or bf16");
+    MFB_REQUIRE(c.x_dtype == MFB_DT_F16 || c.x_dtype == MFB_DT_BF16, MFB_ERR_INVALID_ARGUMENT, "activation dtype must be fp16 or bf16");
+    MFB_REQUIRE(c.activation <= MFB_ACT_GELU_TANH && c.router_mode <= MFB_ROUTER_SQRTSOFTPLUS, MFB_ERR_INVALID_ARGUMENT, "activation / router mode");
+    MFB_REQUIRE(c.max_tokens >= 1, MFB_ERR_INVALID_ARGUMENT, "max_tokens must be positive");
+    const uint32_t widths[2] = {c.bits, c.shared_bits};
+    for (uint32_t b : widths) {
+        if (!b) continue;
+        MFB_REQUIRE(pow2_or_wide(c.d, b) && pow2_or_wide(c.f, b), MFB_ERR_UNSUPPORTED_SHAPE,
+                    "a row of d or f codes must span a power-of-two number of 16-byte pieces, or at least 32");
+    }
+    int count = 0;
+    MFB_CUDA(cudaGetDeviceCount(&count));
+    MFB_REQUIRE(count > 0, MFB_ERR_CUDA, "no CUDA device");
+
+    mfb_moe* m = new (std::nothrow) mfb_moe();
+    MFB_REQUIRE(m != nullptr, MFB_ERR_ALLOC, "out of host memory");
+    m->cfg = c;
+    if (m->cfg.rms_eps <= 0.0f) m->cfg.rms_eps = 1e-6f;
+    cudaGetDevice(&m->device);
+    cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, m->device);
+    const uint64_t T = c.max_tokens, K = c.top_k, E = c.num_experts;
+    m->max_pairs = T * K;
+    m->max_rows = T * (K + 1);
+    Arena& a = m->a;
+    a.n_chunks = (uint32_t)((m->max_pairs + GROUP_CHUNK - 1) / GROUP_CHUNK);
+    cudaError_t e = cudaSuccess;
+    auto ok = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    ok(dev_alloc(a.logits, T * E));
+    ok(dev_alloc(a.idx, T * K));
+    ok(dev_alloc(a.route_w, T * K));
+    { uint16_t* p = nullptr; ok(dev_alloc(p, T * c.d)); a.xn = p; }
+    ok(dev_alloc(a.sorted, m->max_rows));
+    ok(dev_alloc(a.chunk_hist, (uint64_t)a.n_chunks * E));
+    ok(dev_alloc(a.offsets, E));
+    ok(dev_alloc(a.counts, E));
+    ok(dev_alloc(a.groups, E + 1));
+    ok(dev_alloc(a.n_groups, 1));
+    ok(dev_alloc(a.tile_prefix, E + 2));
+    ok(dev_alloc(a.acts, m->max_rows * c.f));
+    ok(dev_alloc(a.partial, m->max_rows * c.d));
+    ok(dev_alloc(a.status, 1));
+    if (c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) {
+        const uint64_t rows = m->max_rows + TC_ROW_PAD;
+        ok(dev_alloc(a.xs16, rows * c.d));
+        ok(dev_alloc(a.acts16, rows * c.f));
+    }
+    if (e == cudaSuccess) e = cudaMemset(a.status, 0, sizeof(uint32_t));
+    if (e == cudaSuccess && a.xs16) e = cudaMemset(a.xs16, 0, (m->max_rows + TC_ROW_PAD) * c.d * sizeof(__half));
+    if (e == cudaSuccess && a.acts16) e = cudaMemset(a.acts16, 0, (m->max_rows + TC_ROW_PAD) * c.f * sizeof(__half));
+    if (e != cudaSuccess) {
+        free_arena(a);
+        delete m;
+        set_error("arena allocation failed: %s", cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? MFB_ERR_ALLOC : MFB_ERR_CUDA;
+    }
+    *out = m;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
+    if (!moe) return MFB_OK;
+    tc_release(moe);
+    free_arena(moe->a);
+    delete moe;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status) {
+    MFB_REQUIRE(moe && status, MFB_ERR_INVALID_ARGUMENT, "device_status: NULL argument");
+    MFB_CUDA(cudaMemcpyAsync(status, moe->a.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MFB_CUDA(cudaMemsetAsync(moe->a.status, 0, sizeof(uint32_t), (cudaStream_t)stream));
+    MFB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (*status) { set_error("device status word = 0x%x", *status); return MFB_ERR_DEVICE_STATUS; }
+    return MFB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------- router
+
+extern "C" int32_t mfb_router_logits(mfb_moe* moe, void* stream, const void* x, uint32_t ldx, uint32_t n_tokens,
+                                     const void* router_w, const float* logit_bias, float* logits) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(x && router_w && logits, MFB_ERR_INVALID_ARGUMENT, "router_logits: NULL argument");
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "router_logits: row stride smaller than d");
+    MFB_CUDA(launch_router_logits((cudaStream_t)stream, x, (int)moe->cfg.x_dtype, ldx, n_tokens,
+                                  (const __nv_bfloat16*)router_w, moe->cfg.num_experts, moe->cfg.d, logit_bias, logits));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_router_select(mfb_moe* moe, void* stream, const float* logits, uint32_t n_tokens,
+                                     const void* per_expert_scale, const float* correction_bias, uint32_t* out_idx,
+                                     uint16_t* out_w) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(logits && out_idx && out_w, MFB_ERR_INVALID_ARGUMENT, "router_select: NULL argument");
+    const mfb_moe_config& c = moe->cfg;
+    MFB_CUDA(launch_router_select((cudaStream_t)stream, logits, n_tokens, c.num_experts, c.top_k, (int)c.router_mode,
+                                  (const __nv_bfloat16*)per_expert_scale, correction_bias, c.route_scale, out_idx, out_w));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_router_topk(mfb_moe* moe, void* stream, const void* x, uint32_t ldx, uint32_t n_tokens,
+                                   const mfb_layer_weights* w, uint32_t* out_idx, uint16_t* out_w) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    MFB_REQUIRE(w && w->router_w && x && out_idx && out_w, MFB_ERR_INVALID_ARGUMENT, "router_topk: NULL argument");
+    rc = mfb_router_logits(moe, stream, x, ldx, n_tokens, w->router_w, w->logit_bias, moe->a.logits);
+    if (rc) return rc;
+    return mfb_router_select(moe, stream, moe->a.logits, n_tokens, w->per_expert_scale, w->correction_bias, out_idx, out_w);
+}
+
+extern "C" int32_t mfb_slot_lookup(mfb_moe* moe, void* stream, const uint32_t* idx, uint32_t n_tokens,
+                                   const int16_t* slot_of, uint64_t slot_stride, uint64_t* out_offsets,
+                                   uint32_t* out_all_hit) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(idx && slot_of && out_offsets && out_all_hit, MFB_ERR_INVALID_ARGUMENT, "slot_lookup: NULL argument");
+    MFB_CUDA(launch_slot_lookup((cudaStream_t)stream, idx, n_tokens, moe->cfg.top_k, moe->cfg.num_experts, slot_of,
+                                slot_stride, out_offsets, out_all_hit));
+    return MFB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------- decode
+
+extern "C" int32_t mfb_moe_experts(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                   uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w,
+                                   const uint32_t* active_slots, uint32_t active_count, int32_t with_shared) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, false);
+    if (rc) return rc;
+    MFB_REQUIRE(x && idx && route_w, MFB_ERR_INVALID_ARGUMENT, "experts: NULL argument");
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "experts: row stride smaller than d");
+    uint32_t mask = all_slots(moe);
+    if (active_slots) {
+        mask = 0;
+        for (uint32_t i = 0; i < active_count; ++i) {
+            MFB_REQUIRE(active_slots[i] < moe->cfg.top_k, MFB_ERR_INVALID_ARGUMENT, "experts: active slot %u out of range", active_slots[i]);
+            mask |= 1u << active_slots[i];
+        }
+    }
+    if (n_tokens == 0) return MFB_OK;
+    return run_experts(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, idx, route_w, mask, with_shared != 0);
+}
+
+extern "C" int32_t mfb_moe_combine(mfb_moe* moe, void* stream, uint32_t n_tokens, const uint16_t* route_w,
+                                   int32_t with_shared, const void* residual, void* y) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    MFB_REQUIRE(route_w && y, MFB_ERR_INVALID_ARGUMENT, "combine: NULL argument");
+    const mfb_moe_config& c = moe->cfg;
+    MFB_CUDA(launch_combine((cudaStream_t)stream, moe->a.partial, route_w, n_tokens, c.top_k, c.top_k + 1, c.d,
+                            all_slots(moe), with_shared != 0, residual, y, (int)c.x_dtype));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                  uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, const void* residual,
+                                  void* y) {
+    int32_t rc = mfb_moe_experts(moe, stream, w, x, ldx, n_tokens, idx, route_w, nullptr, 0, 1);
+    if (rc) return rc;
+    return mfb_moe_combine(moe, stream, n_tokens, route_w, w->shared_blob != nullptr, residual, y);
+}
+
+extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* h_in, void* h_out,
+                                 uint32_t n_tokens) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, true);
+    if (rc) return rc;
+    MFB_REQUIRE(h_in && h_out, MFB_ERR_INVALID_ARGUMENT, "layer: NULL argument");
+    if (n_tokens == 0) return MFB_OK;
+    const mfb_moe_config& c = moe->cfg;
+    Arena& a = moe->a;
+    cudaStream_t s = (cudaStream_t)stream;
+    MFB_CUDA(launch_rmsnorm(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, a.xn, (int)c.x_dtype));
+    rc = mfb_router_topk(moe, stream, a.xn, c.d, n_tokens, w, a.idx, a.route_w);
+    if (rc) return rc;
+    return mfb_moe_decode(moe, stream, w, a.xn, c.d, n_tokens, a.idx, a.route_w, h_in, h_out);
+}
+
+extern "C" int32_t mfb_moe_stack(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
+                                 void* hidden, uint32_t n_tokens) {
+    MFB_REQUIRE(layers != nullptr || n_layers == 0, MFB_ERR_INVALID_ARGUMENT, "stack: layers is NULL");
+    for (uint32_t l = 0; l < n_layers; ++l) {
+        const int32_t rc = mfb_moe_layer(moe, stream, &layers[l], hidden, hidden, n_tokens);
+        if (rc) return rc;
+    }
+    return MFB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------- prefill
+
+extern "C" int32_t mfb_moe_group(mfb_moe* moe, void* stream, const uint32_t* idx, const uint16_t* route_w,
+                                 uint32_t n_tokens, mfb_pair* out_sorted, uint32_t* out_offsets, uint32_t* out_counts,
+                                 mfb_group* out_groups, uint32_t* out_n_groups) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    MFB_REQUIRE(idx && out_sorted && out_offsets && out_counts && out_groups && out_n_groups, MFB_ERR_INVALID_ARGUMENT,
+                "group: NULL argument");
+    MFB_CUDA(launch_group((cudaStream_t)stream, idx, route_w, n_tokens, moe->cfg.top_k, moe->cfg.num_experts,
+                          all_slots(moe), 0, 0, moe->a, out_sorted, out_offsets, out_counts, out_groups, out_n_groups, nullptr));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x,
+                                           uint32_t ldx, uint32_t n_tokens, const mfb_pair* sorted,
+                                           const mfb_group* groups, const uint32_t* n_groups, float* partial) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, false);
+    if (rc) return rc;
+    MFB_REQUIRE(x && sorted && groups && n_groups && partial, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped: NULL argument");
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped: row stride smaller than d");
+    if (n_tokens == 0) return MFB_OK;
+    const mfb_moe_config& c = moe->cfg;
+    const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
+    const uint32_t max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts);
+    if ((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c))
+        return tc_grouped_ffn(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, sorted, groups, n_groups, max_groups,
+                              /*routed_only=*/true, partial, c.top_k);
+    DecodeArgs d;
+    mfb_layer_weights routed_only = *w;
+    routed_only.shared_blob = nullptr;
+    d.w = &routed_only; d.d = c.d; d.f = c.f; d.num_experts = c.num_experts; d.top_k = c.top_k; d.bits = c.bits;
+    d.shared_bits = c.shared_bits; d.scale_dtype = c.scale_dtype; d.activation = c.activation;
+    d.swiglu_limit = c.swiglu_limit; d.x = x; d.x_dtype = (int)c.x_dtype; d.ldx = ldx; d.sorted = sorted;
+    d.groups = groups; d.n_groups = n_groups; d.max_groups = max_groups;
+    d.acts = moe->a.acts; d.partial = partial; d.slots = c.top_k;
+    MFB_CUDA(launch_decode_ffn((cudaStream_t)stream, d));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w,
+                                  uint32_t n_tokens, const void* residual, void* y) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(partial && route_w && y, MFB_ERR_INVALID_ARGUMENT, "reduce: NULL argument");
+    const mfb_moe_config& c = moe->cfg;
+    MFB_CUDA(launch_combine((cudaStream_t)stream, partial, route_w, n_tokens, c.top_k, c.top_k, c.d, all_slots(moe), 0,
+                            residual, y, (int)c.x_dtype));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_layer_prefill(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* h_in,
+                                         void* h_out, uint32_t n_tokens) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, true);
+    if (rc) return rc;
+    MFB_REQUIRE(h_in && h_out, MFB_ERR_INVALID_ARGUMENT, "layer_prefill: NULL argument");
+    if (n_tokens == 0) return MFB_OK;
+    const mfb_moe_config& c = moe->cfg;
+    if (!((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c))) return mfb_moe_layer(moe, stream, w, h_in, h_out, n_tokens);
+    Arena& a = moe->a;
+    cudaStream_t s = (cudaStream_t)stream;
+    MFB_CUDA(launch_rmsnorm(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, a.xn, (int)c.x_dtype));
+    rc = mfb_router_topk(moe, stream, a.xn, c.d, n_tokens, w, a.idx, a.route_w);
+    if (rc) return rc;
+    const bool shared = w->shared_blob != nullptr;
+    MFB_CUDA(launch_group(s, a.idx, a.route_w, n_tokens, c.top_k, c.num_experts, all_slots(moe), shared ? 1 : 0, TC_TILE_N, a,
+                          a.sorted, a.offsets, a.counts, a.groups, a.n_groups, a.tile_prefix));
+    const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
+    const uint32_t max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts) + (shared ? 1u : 0u);
+    rc = tc_grouped_ffn(moe, s, w, a.xn, c.d, n_tokens, a.sorted, a.groups, a.n_groups, max_groups, /*routed_only=*/false,
+                        a.partial, c.top_k + 1);
+    if (rc) return rc;
+    MFB_CUDA(launch_combine(s, a.partial, a.route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, h_in, h_out,
+                            (int)c.x_dtype));
+    return MFB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------- glue
+
+extern "C" int32_t mfb_rmsnorm(mfb_moe* moe, void* stream, const void* x, const void* w_bf16, uint32_t n_rows, void* out) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(x && out, MFB_ERR_INVALID_ARGUMENT, "rmsnorm: NULL argument");
+    const mfb_moe_config& c = moe->cfg;
+    MFB_CUDA(launch_rmsnorm((cudaStream_t)stream, x, (int)c.x_dtype, (const __nv_bfloat16*)w_bf16, n_rows, c.d, c.rms_eps, out, (int)c.x_dtype));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_residual_add(mfb_moe* moe, void* stream, const void* a, const void* b, uint64_t n, void* out) {
+    int32_t rc = check_handle(moe, 0);
+    if (rc) return rc;
+    MFB_REQUIRE(a && b && out, MFB_ERR_INVALID_ARGUMENT, "residual_add: NULL argument");
+    MFB_CUDA(launch_residual_add((cudaStream_t)stream, a, b, n, out, (int)moe->cfg.x_dtype));
+    return MFB_OK;
+}

@@ -1,0 +1,100 @@
+// Layer glue: RMSNorm, residual add and the rank-ordered weighted combine.
+#include "common.cuh"
+
+namespace mfb {
+
+namespace {
+
+// rmsnorm_bf16w (Sources/Mference/Metal/Primitives/rmsnorm.metal:32-93): inv = rsqrt(mean(x^2) + eps),
+// out = dtype(x * inv * w).  One block per row, fp32 throughout.
+__global__ void rmsnorm_kernel(const void* __restrict__ x, int in_dtype, const __nv_bfloat16* __restrict__ w,
+                               uint32_t d, float eps, void* __restrict__ out, int out_dtype) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = load_act(x, row * d + i, in_dtype);
+        ss = fmaf(v, v, ss);
+    }
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float inv = rsqrtf(red[0] / (float)d + eps);
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = load_act(x, row * d + i, in_dtype);
+        const float g = w ? __bfloat162float(w[i]) : 1.0f;
+        store_act(out, row * d + i, v * inv * g, out_dtype);
+    }
+}
+
+// residual_add_fp16 (Sources/Mference/Metal/Primitives/utility.metal:83-92) in the activation dtype.
+__global__ void residual_add_kernel(const void* __restrict__ a, const void* __restrict__ b, uint64_t n,
+                                    void* __restrict__ out, int dtype) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) store_act(out, i, load_act(a, i, dtype) + load_act(b, i, dtype), dtype);
+}
+
+// y[t,i] = dtype( residual[t,i] + partial[t,top_k,i] (shared expert, weight 1) + sum_r w[t,r] * partial[t,r,i] )
+// in fp32, residual first, ranks in ascending order: the order of moe_phase2_down_reduce_k8
+// (Sources/Mference/Metal/MoE/moe.metal:349-404) and of prefill_moe_reduce_token_major
+// (Sources/Mference/Metal/Prefill/prefill.metal:631-652).  Four elements per thread.
+__global__ void combine_kernel(const float* __restrict__ partial, const uint16_t* __restrict__ route_w,
+                               uint32_t n_tokens, uint32_t top_k, uint32_t slots, uint32_t d, uint32_t slot_mask,
+                               int with_shared, const void* __restrict__ residual, void* __restrict__ y, int dtype) {
+    const uint32_t quads = d / 4;
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)n_tokens * quads) return;
+    const uint32_t t = (uint32_t)(i / quads), c = (uint32_t)(i % quads) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (residual) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = load_act(residual, (size_t)t * d + c + j, dtype);
+    }
+    const float* base = partial + (size_t)t * slots * d + c;
+    if (with_shared) {
+        const float4 v = *reinterpret_cast<const float4*>(base + (size_t)top_k * d);
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    }
+    for (uint32_t r = 0; r < top_k; ++r) {
+        if (!((slot_mask >> r) & 1u)) continue;
+        const float wr = __half2float(__ushort_as_half(route_w[(size_t)t * top_k + r]));
+        const float4 v = *reinterpret_cast<const float4*>(base + (size_t)r * d);
+        acc[0] = fmaf(wr, v.x, acc[0]); acc[1] = fmaf(wr, v.y, acc[1]);
+        acc[2] = fmaf(wr, v.z, acc[2]); acc[3] = fmaf(wr, v.w, acc[3]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) store_act(y, (size_t)t * d + c + j, acc[j], dtype);
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm(cudaStream_t s, const void* x, int in_dtype, const __nv_bfloat16* w, uint32_t n_rows,
+                           uint32_t d, float eps, void* out, int out_dtype) {
+    if (n_rows == 0) return cudaSuccess;
+    rmsnorm_kernel<<<n_rows, 256, 0, s>>>(x, in_dtype, w, d, eps, out, out_dtype);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual_add(cudaStream_t s, const void* a, const void* b, uint64_t n, void* out, int dtype) {
+    if (n == 0) return cudaSuccess;
+    residual_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n, out, dtype);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(cudaStream_t s, const float* partial, const uint16_t* route_w, uint32_t n_tokens,
+                           uint32_t top_k, uint32_t slots, uint32_t d, uint32_t slot_mask, int with_shared,
+                           const void* residual, void* y, int dtype) {
+    if (n_tokens == 0) return cudaSuccess;
+    const uint64_t n = (uint64_t)n_tokens * (d / 4);
+    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, route_w, n_tokens, top_k, slots, d, slot_mask,
+                                                               with_shared, residual, y, dtype);
+    return cudaGetLastError();
+}
+
+}  // namespace mfb

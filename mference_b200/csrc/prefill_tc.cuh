@@ -1,0 +1,18 @@
+// Tensor-core (tcgen05 / TMEM) grouped expert FFN for prefill and ragged batches: interface used by api.cu.
+#pragma once
+
+#include "common.cuh"
+
+namespace mfb {
+
+constexpr uint32_t TC_TILE_N = 128;   // token rows per tile of the grouped GEMM
+constexpr uint32_t TC_ROW_PAD = 256;  // spare rows behind the gathered activations so a tile may over-read
+
+bool tc_supported(const mfb_moe_config& c);
+void tc_release(mfb_moe* m);
+// partial[(token*slots + rank), :] = ffn_expert(x[token]) for every sorted pair of every group.
+int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                       uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups, const uint32_t* n_groups,
+                       uint32_t max_groups, bool routed_only, float* partial, uint32_t slots);
+
+}  // namespace mfb

@@ -1,0 +1,222 @@
+// Router: gate GEMV over a bf16 gate, top-k selection with routing weights, slot lookup.
+//
+// The logits feed an exact comparison (top-k with ties to the lower index), so their summation order is
+// part of the contract: for every (token, expert) lane l of a 32-lane group accumulates elements
+// l, l+32, l+64, ... with fused multiply-adds in ascending order, then the 32 partial sums are combined by a
+// xor butterfly (16, 8, 4, 2, 1), and an optional per-expert bias is added last.  That is the structure of
+// router_gemv_bf16_r4 (Sources/Mference/Metal/MoE/moe.metal:162-185) with its lane sum made concrete, and it
+// makes a block of B token rows bit-identical to B single-row calls.
+#include "common.cuh"
+
+namespace mfb {
+
+namespace {
+
+constexpr int RT_WARPS = 8;     // warps per block
+constexpr int RT_KC = 256;      // k elements staged per step (8 per lane)
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+
+// Block tile: TM token rows x (RT_WARPS * TE) experts.  Each warp owns TE experts for all TM rows; lane l
+// owns k = l (mod 32).  The staged tiles are stored "lane-major" in shared memory — the RT_KC/32 = 8 values a
+// lane needs from a row are contiguous — so one 16-byte (bf16) or two 16-byte (fp32) loads fetch them.
+template <int TM, int TE>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router_logits_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
+                     const __nv_bfloat16* __restrict__ w, uint32_t num_experts, uint32_t d,
+                     const float* __restrict__ logit_bias, float* __restrict__ logits) {
+    constexpr int BE = RT_WARPS * TE;
+    __shared__ __align__(16) float xs[TM][RT_KC];          // [row][lane*8 + j]  <- element k = j*32 + lane
+    __shared__ __align__(16) uint16_t ws[BE][RT_KC];       // same permutation, raw bf16 bits
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t t0 = blockIdx.y * TM, e0 = blockIdx.x * BE;
+    float acc[TM][TE];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TE; ++j) acc[i][j] = 0.0f;
+
+    for (uint32_t k0 = 0; k0 < d; k0 += RT_KC) {
+        __syncthreads();
+        for (uint32_t i = tid; i < TM * RT_KC; i += RT_WARPS * 32) {
+            const uint32_t r = i / RT_KC, k = i % RT_KC;
+            float v = 0.0f;
+            if (t0 + r < n_tokens && k0 + k < d) v = load_act(x, (size_t)(t0 + r) * ldx + k0 + k, x_dtype);
+            xs[r][(k & 31) * 8 + (k >> 5)] = v;
+        }
+        for (uint32_t i = tid; i < BE * RT_KC; i += RT_WARPS * 32) {
+            const uint32_t r = i / RT_KC, k = i % RT_KC;
+            uint16_t v = 0;
+            if (e0 + r < num_experts && k0 + k < d) v = __bfloat16_as_ushort(w[(size_t)(e0 + r) * d + k0 + k]);
+            ws[r][(k & 31) * 8 + (k >> 5)] = v;
+        }
+        __syncthreads();
+        float xv[TM][8];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[i][lane * 8]);
+            const float4 b = *reinterpret_cast<const float4*>(&xs[i][lane * 8 + 4]);
+            xv[i][0] = a.x; xv[i][1] = a.y; xv[i][2] = a.z; xv[i][3] = a.w;
+            xv[i][4] = b.x; xv[i][5] = b.y; xv[i][6] = b.z; xv[i][7] = b.w;
+        }
+#pragma unroll
+        for (int j = 0; j < TE; ++j) {
+            const uint4 q = *reinterpret_cast<const uint4*>(&ws[warp * TE + j][lane * 8]);
+            const float wv[8] = {bf16_lo(q.x), bf16_hi(q.x), bf16_lo(q.y), bf16_hi(q.y),
+                                 bf16_lo(q.z), bf16_hi(q.z), bf16_lo(q.w), bf16_hi(q.w)};
+#pragma unroll
+            for (int s = 0; s < 8; ++s)   // ascending k for this lane: k0 + s*32 + lane
+#pragma unroll
+                for (int i = 0; i < TM; ++i) acc[i][j] = fmaf(wv[s], xv[i][s], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TE; ++j) {
+            float v = acc[i][j];
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            const uint32_t e = e0 + warp * TE + j, t = t0 + i;
+            if (lane == 0 && e < num_experts && t < n_tokens) {
+                if (logit_bias) v = v + logit_bias[e];
+                logits[(size_t)t * num_experts + e] = v;
+            }
+        }
+}
+
+// sqrt(softplus(x)) in the numerically safe form of moe.metal:737-741.
+__device__ __forceinline__ float sqrtsoftplus(float x) {
+    const float sp = fmaxf(x, 0.0f) + logf(1.0f + expf(-fabsf(x)));
+    return sqrtf(sp);
+}
+
+// One warp per token row.  Blocked ownership as in router_topk_select_k8_par (moe.metal:262-345): lane L owns
+// experts [L*per, L*per + per); every round takes a lane-local strict-greater ascending maximum and a
+// shuffle argmax that prefers the lower index on equal scores, which reproduces the serial insertion scan
+// (strictly greater wins, equal keeps the earlier expert).  The weight tail runs on lane 0 in the serial order.
+constexpr int SEL_MAX_PER_LANE = MFB_MAX_EXPERTS / 32;
+constexpr uint32_t SEL_NONE = 0xFFFFFFFFu;
+
+__global__ void router_select_kernel(const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts,
+                                     uint32_t top_k, int mode, const __nv_bfloat16* __restrict__ per_expert_scale,
+                                     const float* __restrict__ correction_bias, float route_scale,
+                                     uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const float* lg = logits + (size_t)t * num_experts;
+    const uint32_t per = (num_experts + 31) / 32, base = lane * per;
+    float ch[SEL_MAX_PER_LANE];
+#pragma unroll
+    for (int j = 0; j < SEL_MAX_PER_LANE; ++j) {
+        const uint32_t e = base + j;
+        float v = -INFINITY;
+        if ((uint32_t)j < per && e < num_experts) {
+            v = lg[e];
+            if (mode == MFB_ROUTER_SQRTSOFTPLUS) v = sqrtsoftplus(v) + (correction_bias ? correction_bias[e] : 0.0f);
+        }
+        ch[j] = v;
+    }
+    uint32_t taken = 0;
+    uint32_t my_idx = 0;     // lane r keeps the winner of round r
+    float my_score = -INFINITY;
+    for (uint32_t r = 0; r < top_k; ++r) {
+        float bv = -INFINITY;
+        uint32_t bi = SEL_NONE;
+#pragma unroll
+        for (int j = 0; j < SEL_MAX_PER_LANE; ++j)
+            if (!(taken & (1u << j)) && ch[j] > bv) { bv = ch[j]; bi = base + j; }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_down_sync(0xFFFFFFFFu, bv, off);
+            const uint32_t oi = __shfl_down_sync(0xFFFFFFFFu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        bi = __shfl_sync(0xFFFFFFFFu, bi, 0);
+        bv = __shfl_sync(0xFFFFFFFFu, bv, 0);
+        if (bi != SEL_NONE && bi >= base && bi < base + per) taken |= 1u << (bi - base);
+        if (lane == r) {
+            // fewer experts than top_k: the serial scan leaves index 0 with score -inf (moe.metal:321-330)
+            my_idx = bi == SEL_NONE ? 0u : bi;
+            my_score = bi == SEL_NONE ? -INFINITY : bv;
+        }
+    }
+    // weight tail, serial order on values gathered to lane 0 (top_k <= 16 < 32)
+    float score = my_score;
+    if (mode == MFB_ROUTER_SQRTSOFTPLUS) score = lane < top_k ? sqrtsoftplus(lg[my_idx]) : 0.0f;
+    const float max_s = __shfl_sync(0xFFFFFFFFu, score, 0);
+    float term = 0.0f;
+    if (lane < top_k) term = mode == MFB_ROUTER_SQRTSOFTPLUS ? score : expf(score - max_s);
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < top_k; ++r) sum += __shfl_sync(0xFFFFFFFFu, term, r);  // rank order, same on every lane
+    if (lane < top_k) {
+        float wgt;
+        if (mode == MFB_ROUTER_SQRTSOFTPLUS) {
+            const float inv = route_scale / (sum + 1e-20f);
+            wgt = term * inv;
+        } else {
+            const float gain = per_expert_scale ? __bfloat162float(per_expert_scale[my_idx]) : 1.0f;
+            wgt = term / sum * gain;
+        }
+        out_idx[(size_t)t * top_k + lane] = my_idx;
+        out_w[(size_t)t * top_k + lane] = __half_as_ushort(__float2half_rn(wgt));
+    }
+}
+
+// router_slot_lookup_k8 (moe.metal:594-617) for a block of rows and 64-bit offsets.
+__global__ void slot_lookup_kernel(const uint32_t* __restrict__ idx, uint32_t n_tokens, uint32_t top_k,
+                                   uint32_t num_experts, const int16_t* __restrict__ slot_of, uint64_t slot_stride,
+                                   uint64_t* __restrict__ out_offsets, uint32_t* __restrict__ out_all_hit) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_tokens) return;
+    uint32_t all_hit = 1u;
+    for (uint32_t k = 0; k < top_k; ++k) {
+        const uint32_t e = min(idx[(size_t)t * top_k + k], num_experts - 1u);
+        const int16_t slot = slot_of[e];
+        if (slot < 0) { all_hit = 0u; out_offsets[(size_t)t * top_k + k] = 0ull; }
+        else out_offsets[(size_t)t * top_k + k] = (uint64_t)slot * slot_stride;
+    }
+    out_all_hit[t] = all_hit;
+}
+
+}  // namespace
+
+cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
+                                 const __nv_bfloat16* w, uint32_t num_experts, uint32_t d, const float* logit_bias,
+                                 float* logits) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (n_tokens <= 2) {
+        // decode: one expert per warp keeps 64 blocks busy on a 256-expert gate
+        dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 1) / 2);
+        if (n_tokens == 1) { grid.y = 1; router_logits_kernel<1, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits); }
+        else router_logits_kernel<2, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+    } else if (n_tokens <= 64) {
+        dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 7) / 8);
+        router_logits_kernel<8, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+    } else {
+        dim3 grid((num_experts + RT_WARPS * 4 - 1) / (RT_WARPS * 4), (n_tokens + 7) / 8);
+        router_logits_kernel<8, 4><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_router_select(cudaStream_t s, const float* logits, uint32_t n_tokens, uint32_t num_experts,
+                                 uint32_t top_k, int mode, const __nv_bfloat16* per_expert_scale,
+                                 const float* correction_bias, float route_scale, uint32_t* out_idx, uint16_t* out_w) {
+    if (n_tokens == 0) return cudaSuccess;
+    const uint32_t warps = n_tokens >= 4 ? 4 : 1;
+    router_select_kernel<<<(n_tokens + warps - 1) / warps, warps * 32, 0, s>>>(
+        logits, n_tokens, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, out_idx, out_w);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_slot_lookup(cudaStream_t s, const uint32_t* idx, uint32_t n_tokens, uint32_t top_k,
+                               uint32_t num_experts, const int16_t* slot_of, uint64_t slot_stride,
+                               uint64_t* out_offsets, uint32_t* out_all_hit) {
+    if (n_tokens == 0) return cudaSuccess;
+    slot_lookup_kernel<<<(n_tokens + 127) / 128, 128, 0, s>>>(idx, n_tokens, top_k, num_experts, slot_of, slot_stride,
+                                                              out_offsets, out_all_hit);
+    return cudaGetLastError();
+}
+
+}  // namespace mfb
