@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE feed-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+One step = one pass of the 40-layer Qwen3.6-A3B-shaped MoE FFN stack (hidden 2048, 256 experts top-8 + 1 shared,
+intermediate 512, 4-bit group-64 affine weights, bf16 activations, RMSNorm between layers) over one decode batch
+of B token rows.  Weights are seeded synthetic (generated on the device), fully resident in HBM.
+
+Prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same through the
+C ABI with host buffers (pinned host -> device copy of the step's rows and device -> host read of the result inside
+the timed region); `roofline` relates the step to the measured HBM copy bandwidth; `cpu_baseline` is the CPU port of
+the reference's scalar path timed on this box's host cores (a baseline, not a target).
+
+With --gpus N > 1 (under torchrun) every rank serves its own batch from its own full replica of the pool (decode
+does not shard: replicas only), so scaling is weak and `value` sums the ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, F, E, K, LAYERS = 2048, 512, 256, 8, 40
+ROOT_SEED = 0xB2000001
+N_INPUTS = 8          # distinct input batches cycled through the steps
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def layer_bytes(unique_experts: int, n_tokens: int, blob: int) -> int:
+    """Algorithmic bytes of one decode layer: each distinct routed expert once, the shared expert, the bf16 gate,
+    and the activation rows in and out."""
+    return unique_experts * blob + blob + E * D * 2 + n_tokens * D * 2 * 2
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_port_tokens_per_s(batch: int, budget_s: float):
+    """Times the CPU port of the reference's scalar decode path (oracle/mfb_oracle.c: mfbo_ref_moe_layer_f32 plus the
+    router) on this box's host cores, on ONE layer of the stack, and scales by the layer count."""
+    import numpy as np
+    from oracle import oracle as O
+    rows = min(batch, 8)
+    W0 = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=[])
+    x = O.fill_normal(O.seed_for_label(ROOT_SEED, "x"), rows * D, dtype=O.DT_BF16).reshape(rows, D)
+    lg = O.router_logits(x, O.DT_BF16, W0.router)
+    idx, w = O.topk_softmax(lg, K)
+    W = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=sorted(set(idx.reshape(-1).tolist())))
+    xf = O.bf16_to_f32(x)
+    O.ref_moe_layer_f32(W, xf, idx, w)   # warm-up
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        lg = O.router_logits(x, O.DT_BF16, W.router)
+        idx2, w2 = O.topk_softmax(lg, K)
+        O.ref_moe_layer_f32(W, xf, idx2, w2)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or reps >= 2000:
+            break
+    per_layer = dt / reps
+    tok_s = rows / (per_layer * LAYERS)
+    return tok_s, O.num_threads(), f"1 of {LAYERS} layers x {rows} token rows x {reps} repeats, scaled x{LAYERS}", per_layer
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(args.steps, 1), args.warmup
+    budget = max(2.0, min(20.0, 90.0 / (steps + warm)))
+    vals = []
+    cores, sample, per_layer = 1, "", 0.0
+    for i in range(steps + warm):
+        tok_s, cores, sample, per_layer = cpu_port_tokens_per_s(args.batch, budget)
+        if i >= warm:
+            vals.append(tok_s)
+    v = statistics.mean(vals)
+    rows = min(args.batch, 8)
+    print(json.dumps({
+        "impl": "reference", "metric": "moe_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": 1e3 * rows / v, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"configs[1]: {LAYERS}-layer Qwen3.6-A3B MoE FFN stack, decode batch {rows} (CPU port)",
+                   "note": "the reference is Swift + Metal and cannot be built here; this arm is the C port of its scalar "
+                           "path (oracle/mfb_oracle.c) on the host cores"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from mference_b200 import _lib as L
+    from mference_b200.moe import MoE, expert_layout, synth_layer, synth_normal
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = L.load()
+    B = args.batch
+    _, blob = expert_layout(4, D, F)
+
+    layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(LAYERS)]
+    moe = MoE(D, F, E, K, max_tokens=B)
+    stack = moe.make_stack(layers)
+    inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", B * D, dtype=L.DT_BF16).view(B, D) for i in range(N_INPUTS)]
+    torch.cuda.synchronize()
+
+    # distinct experts per layer for each input batch (untimed; same kernels, layer by layer)
+    step_bytes = []
+    idx = torch.empty((B, K), dtype=torch.int32, device="cuda")
+    w = torch.empty((B, K), dtype=torch.float16, device="cuda")
+    for h0 in inputs:
+        h = h0.clone()
+        total = 0
+        for lw in layers:
+            xn = torch.empty_like(h)
+            moe.encode_rmsnorm(h, xn, lw.norm_w)
+            moe.encode_router(xn, lw, idx, w)
+            total += layer_bytes(int(torch.unique(idx).numel()), B, blob)
+            nxt = torch.empty_like(h)
+            moe.encode_decode(lw, xn, idx, w, nxt, residual=h)
+            h = nxt
+        step_bytes.append(total)
+    torch.cuda.synchronize()
+    work = [t.clone() for t in inputs]
+
+    def step(i):
+        buf = work[i % N_INPUTS]
+        buf.copy_(inputs[i % N_INPUTS])
+        moe.encode_stack(stack, buf)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = lib.mfb_launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        step(i)
+        ev[i + 1].record()
+    barrier()
+    launches = lib.mfb_launch_count() - launches0
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+
+    # end to end through the C ABI with host buffers
+    host_in = [t.cpu().pin_memory() for t in inputs]
+    host_out = torch.empty((B, D), dtype=torch.bfloat16).pin_memory()
+    dev = torch.empty((B, D), dtype=torch.bfloat16, device="cuda")
+    for i in range(min(args.warmup, 3)):
+        dev.copy_(host_in[i % N_INPUTS], non_blocking=True)
+        moe.encode_stack(stack, dev)
+        host_out.copy_(dev, non_blocking=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        dev.copy_(host_in[i % N_INPUTS], non_blocking=True)
+        moe.encode_stack(stack, dev)
+        host_out.copy_(dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller reads the result before the next step
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(times[0]), float(times[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = world * B * args.steps / (total_ms * 1e-3)
+    e2e = world * B * args.steps / (e2e_ms * 1e-3)
+    hbm_peak, _, peak_kind = measured_peaks()
+    bytes_per_step = statistics.mean(step_bytes[i % N_INPUTS] for i in range(args.steps))
+    achieved = bytes_per_step / (statistics.mean(per_step_ms) * 1e-3) / 1e9
+    cpu_tok_s, cores, sample, _ = cpu_port_tokens_per_s(B, 12.0)
+    out = {
+        "metric": "moe_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"configs[1]: {LAYERS}-layer Qwen3.6-A3B MoE FFN stack, decode batch {B}", "hidden": D,
+                   "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4, "group_size": 64,
+                   "layers": LAYERS, "batch_per_gpu": B, "activation_dtype": "bf16", "accumulate": "f32",
+                   "parallelism": "replicas" if world > 1 else "single",
+                   "l2": f"inputs larger than L2: {bytes_per_step / 1e6:.0f} MB of distinct weight bytes per step, "
+                         f"{N_INPUTS} input batches cycled"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "peak_kind": peak_kind, "traffic": None, "kernel": "whole step (all kernels of the 40-layer pass)",
+                     "algorithmic_bytes_per_step": bytes_per_step},
+        "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": B * D * 2},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=64, help="decode batch (token rows per step per GPU): 1, 8 or 64")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -126,6 +126,8 @@ typedef struct mfb_moe mfb_moe;
 
 const char* mfb_last_error(void);
 int32_t mfb_version(void);
+/* Number of GPU kernels this library has launched in the calling process so far (monotonic). */
+uint64_t mfb_launch_count(void);
 /* Fills the offsets of the canonical blob layout (gate W,S,B · up W,S,B · down W,S,B, row-major). */
 int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes);
 

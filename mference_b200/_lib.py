@@ -73,6 +73,7 @@ _V, _U32, _U64, _I32, _I64 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_
 SIGNATURES = {
     "mfb_last_error": (C.c_char_p, []),
     "mfb_version": (_I32, []),
+    "mfb_launch_count": (_U64, []),
     "mfb_expert_layout": (_I32, [_U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "mfb_moe_create": (_I32, [C.POINTER(MoEConfig), C.POINTER(_V)]),
     "mfb_moe_destroy": (_I32, [_V]),

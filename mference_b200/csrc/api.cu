@@ -1,4 +1,5 @@
 // C ABI entry points: argument validation, the handle and its scratch arena, and the launch sequences.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -17,6 +18,9 @@ void set_error(const char* fmt, ...) {
     vsnprintf(g_error, sizeof g_error, fmt, ap);
     va_end(ap);
 }
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launches(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int32_t cuda_fail(cudaError_t e, const char* what) {
     set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
@@ -101,6 +105,7 @@ using namespace mfb;
 
 extern "C" const char* mfb_last_error(void) { return g_error; }
 extern "C" int32_t mfb_version(void) { return 100; }
+extern "C" uint64_t mfb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes) {
     MFB_REQUIRE(off && blob_bytes, MFB_ERR_INVALID_ARGUMENT, "layout: NULL output");

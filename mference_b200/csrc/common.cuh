@@ -13,6 +13,7 @@ namespace mfb {
 
 // ---- error plumbing -------------------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
+void count_launches(uint64_t n);   // bookkeeping behind mfb_launch_count()
 int32_t cuda_fail(cudaError_t e, const char* what);
 
 #define MFB_CUDA(call)                                                    \

@@ -315,6 +315,7 @@ cudaError_t launch_nt(cudaStream_t s, const FfnParams& P, uint32_t max_groups) {
     dim3 g1((P.f + rpb1 - 1) / rpb1, max_groups), g2((P.d + rpb2 - 1) / rpb2, max_groups);
     ffn_phase1_kernel<NT><<<g1, FFN_THREADS, smem1, s>>>(P);
     ffn_phase2_kernel<NT><<<g2, FFN_THREADS, smem2, s>>>(P);
+    count_launches(2);
     return cudaGetLastError();
 }
 

@@ -78,12 +78,14 @@ cudaError_t launch_rmsnorm(cudaStream_t s, const void* x, int in_dtype, const __
                            uint32_t d, float eps, void* out, int out_dtype) {
     if (n_rows == 0) return cudaSuccess;
     rmsnorm_kernel<<<n_rows, 256, 0, s>>>(x, in_dtype, w, d, eps, out, out_dtype);
+    count_launches(1);
     return cudaGetLastError();
 }
 
 cudaError_t launch_residual_add(cudaStream_t s, const void* a, const void* b, uint64_t n, void* out, int dtype) {
     if (n == 0) return cudaSuccess;
     residual_add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n, out, dtype);
+    count_launches(1);
     return cudaGetLastError();
 }
 
@@ -94,6 +96,7 @@ cudaError_t launch_combine(cudaStream_t s, const float* partial, const uint16_t*
     const uint64_t n = (uint64_t)n_tokens * (d / 4);
     combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, route_w, n_tokens, top_k, slots, d, slot_mask,
                                                                with_shared, residual, y, dtype);
+    count_launches(1);
     return cudaGetLastError();
 }
 

@@ -171,9 +171,11 @@ cudaError_t launch_group(cudaStream_t s, const uint32_t* idx, const uint16_t* ro
     if (n_chunks > 0) {
         group_hist_kernel<<<blocks, warps * 32, warps * num_experts * sizeof(uint32_t), s>>>(
             idx, n_pairs, top_k, num_experts, slot_mask, n_chunks, a.chunk_hist);
+        count_launches(1);
     }
     if (n_chunks > 0) {
         group_colscan_kernel<<<num_experts, 256, 0, s>>>(a.chunk_hist, n_chunks, num_experts, out_counts);
+        count_launches(1);
     } else {
         cudaError_t e = cudaMemsetAsync(out_counts, 0, num_experts * sizeof(uint32_t), s);
         if (e != cudaSuccess) return e;
@@ -181,9 +183,11 @@ cudaError_t launch_group(cudaStream_t s, const uint32_t* idx, const uint16_t* ro
     group_finalize_kernel<<<1, 256, 0, s>>>(out_counts, num_experts, n_tokens, top_k, append_shared,
                                             tile_rows ? tile_rows : 1u, out_offsets, out_groups, out_n_groups,
                                             tile_prefix, out_sorted);
+    count_launches(1);
     if (n_chunks > 0) {
         group_scatter_kernel<<<blocks, warps * 32, (warps + 1) * num_experts * sizeof(uint32_t), s>>>(
             idx, route_w, n_pairs, top_k, num_experts, slot_mask, n_chunks, a.chunk_hist, out_counts, out_sorted);
+        count_launches(1);
     }
     return cudaGetLastError();
 }

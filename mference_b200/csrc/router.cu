@@ -197,6 +197,7 @@ cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uin
         dim3 grid((num_experts + RT_WARPS * 4 - 1) / (RT_WARPS * 4), (n_tokens + 7) / 8);
         router_logits_kernel<8, 4><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
     }
+    count_launches(1);
     return cudaGetLastError();
 }
 
@@ -207,6 +208,7 @@ cudaError_t launch_router_select(cudaStream_t s, const float* logits, uint32_t n
     const uint32_t warps = n_tokens >= 4 ? 4 : 1;
     router_select_kernel<<<(n_tokens + warps - 1) / warps, warps * 32, 0, s>>>(
         logits, n_tokens, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, out_idx, out_w);
+    count_launches(1);
     return cudaGetLastError();
 }
 
@@ -216,6 +218,7 @@ cudaError_t launch_slot_lookup(cudaStream_t s, const uint32_t* idx, uint32_t n_t
     if (n_tokens == 0) return cudaSuccess;
     slot_lookup_kernel<<<(n_tokens + 127) / 128, 128, 0, s>>>(idx, n_tokens, top_k, num_experts, slot_of, slot_stride,
                                                               out_offsets, out_all_hit);
+    count_launches(1);
     return cudaGetLastError();
 }
 
