@@ -134,6 +134,10 @@ int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offs
 /* MoE.init / deinit (MoE.swift:65-151): builds the handle and its scratch arena. */
 int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out);
 int32_t mfb_moe_destroy(mfb_moe* moe);
+/* on != 0: run every call of this handle through the generic kernels (any supported shape, any slot subset)
+ * instead of the shape-specialised fast kernels; the two agree within the documented tolerance.  Plays the part of
+ * the reference's generic vs. specialised pipeline states (MoE.swift:77-135). */
+int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on);
 /* Reads and clears the device status word that kernels set when a bounded wait runs out. Synchronises `stream`. */
 int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status);
 

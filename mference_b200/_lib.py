@@ -77,6 +77,7 @@ SIGNATURES = {
     "mfb_expert_layout": (_I32, [_U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "mfb_moe_create": (_I32, [C.POINTER(MoEConfig), C.POINTER(_V)]),
     "mfb_moe_destroy": (_I32, [_V]),
+    "mfb_moe_set_generic": (_I32, [_V, _I32]),
     "mfb_moe_device_status": (_I32, [_V, _V, C.POINTER(_U32)]),
     "mfb_router_logits": (_I32, [_V, _V, _V, _U32, _U32, _V, _V, _V]),
     "mfb_router_select": (_I32, [_V, _V, _V, _U32, _V, _V, _V, _V]),

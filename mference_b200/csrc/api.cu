@@ -6,6 +6,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "decode_mma.cuh"
 #include "prefill_tc.cuh"
 
 namespace mfb {
@@ -50,7 +51,7 @@ cudaError_t dev_alloc(T*& p, size_t count) {
 void free_arena(Arena& a) {
     cudaFree(a.logits); cudaFree(a.idx); cudaFree(a.route_w); cudaFree(a.xn); cudaFree(a.sorted);
     cudaFree(a.chunk_hist); cudaFree(a.offsets); cudaFree(a.counts); cudaFree(a.groups); cudaFree(a.n_groups);
-    cudaFree(a.tile_prefix); cudaFree(a.acts); cudaFree(a.partial); cudaFree(a.xs16); cudaFree(a.acts16);
+    cudaFree(a.tile_prefix); cudaFree(a.acts); cudaFree(a.partial); cudaFree(a.xs16); cudaFree(a.acts16); cudaFree(a.xp); cudaFree(a.xp2); cudaFree(a.actp);
     cudaFree(a.status);
     a = Arena();
 }
@@ -78,6 +79,31 @@ int32_t check_weights(const mfb_moe* m, const mfb_layer_weights* w, bool need_ro
 }
 
 uint32_t all_slots(const mfb_moe* m) { return (1u << m->cfg.top_k) - 1u; }
+
+bool use_fast(const mfb_moe* m, uint32_t n_tokens) {
+    return m->a.xp != nullptr && n_tokens <= FAST_MAX_TOKENS && (uint64_t)n_tokens * m->cfg.top_k <= 1024 &&
+           !m->force_generic && fast_smem2(m->cfg, n_tokens) <= 226 * 1024 && fast_smem1(m->cfg) <= 226 * 1024;
+}
+
+FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens, const uint16_t* route_w,
+                       const void* residual, void* y) {
+    const mfb_moe_config& c = m->cfg;
+    Arena& a = m->a;
+    FastParams P;
+    P.pool = w->pool; P.slot_stride = w->slot_stride; P.slot_of = w->slot_of; P.shared_blob = w->shared_blob;
+    P.routed_off = w->routed_off; P.shared_off = w->shared_off;
+    P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.top_k = c.top_k; P.bits = c.bits; P.shared_bits = c.shared_bits;
+    P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
+    P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
+    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.actp = a.actp; P.route_w = route_w;
+    P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
+    return P;
+}
+
+uint32_t max_groups_for(const mfb_moe* m, uint32_t n_tokens, bool shared) {
+    const uint64_t pairs = (uint64_t)n_tokens * m->cfg.top_k;
+    return (uint32_t)(pairs < m->cfg.num_experts ? pairs : m->cfg.num_experts) + (shared ? 1u : 0u);
+}
 
 int32_t run_experts(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                     uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, uint32_t slot_mask, bool with_shared) {
@@ -171,6 +197,12 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     ok(dev_alloc(a.acts, m->max_rows * c.f));
     ok(dev_alloc(a.partial, m->max_rows * c.d));
     ok(dev_alloc(a.status, 1));
+    if (fast_supported(c)) {
+        const uint64_t ft = T < FAST_MAX_TOKENS ? T : FAST_MAX_TOKENS;
+        ok(dev_alloc(a.xp, ft * c.d));
+        if (c.shared_bits && c.shared_bits != c.bits) ok(dev_alloc(a.xp2, ft * c.d));
+        ok(dev_alloc(a.actp, ft * (K + 1) * c.f));
+    }
     if (c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) {
         const uint64_t rows = m->max_rows + TC_ROW_PAD;
         ok(dev_alloc(a.xs16, rows * c.d));
@@ -194,6 +226,12 @@ extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
     tc_release(moe);
     free_arena(moe->a);
     delete moe;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on) {
+    MFB_REQUIRE(moe != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
+    moe->force_generic = on != 0;
     return MFB_OK;
 }
 
@@ -289,6 +327,20 @@ extern "C" int32_t mfb_moe_combine(mfb_moe* moe, void* stream, uint32_t n_tokens
 extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                                   uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, const void* residual,
                                   void* y) {
+    if (moe && w && x && idx && route_w && y && n_tokens && use_fast(moe, n_tokens) && ldx == moe->cfg.d) {
+        int32_t rc = check_weights(moe, w, false);
+        if (rc) return rc;
+        const mfb_moe_config& c = moe->cfg;
+        Arena& a = moe->a;
+        cudaStream_t s = (cudaStream_t)stream;
+        const bool shared = w->shared_blob != nullptr;
+        MFB_CUDA(launch_fast_prep(s, x, (int)c.x_dtype, nullptr, n_tokens, c.d, c.rms_eps, false, nullptr, a.xp, c.bits, a.xp2, c.shared_bits));
+        MFB_CUDA(launch_group(s, idx, route_w, n_tokens, c.top_k, c.num_experts, all_slots(moe), shared ? 1 : 0, 0, a, a.sorted,
+                              a.offsets, a.counts, a.groups, a.n_groups, nullptr));
+        const FastParams P = fast_params(moe, w, n_tokens, route_w, residual, y);
+        MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        return MFB_OK;
+    }
     int32_t rc = mfb_moe_experts(moe, stream, w, x, ldx, n_tokens, idx, route_w, nullptr, 0, 1);
     if (rc) return rc;
     return mfb_moe_combine(moe, stream, n_tokens, route_w, w->shared_blob != nullptr, residual, y);
@@ -305,6 +357,19 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
     const mfb_moe_config& c = moe->cfg;
     Arena& a = moe->a;
     cudaStream_t s = (cudaStream_t)stream;
+    if (use_fast(moe, n_tokens)) {
+        const bool shared = w->shared_blob != nullptr;
+        MFB_CUDA(launch_fast_prep(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, true, a.xn,
+                                  a.xp, c.bits, a.xp2, c.shared_bits));
+        MFB_CUDA(launch_router_logits(s, a.xn, (int)c.x_dtype, c.d, n_tokens, (const __nv_bfloat16*)w->router_w, c.num_experts,
+                                      c.d, w->logit_bias, a.logits));
+        MFB_CUDA(launch_route_small(s, a.logits, n_tokens, c.num_experts, c.top_k, (int)c.router_mode,
+                                    (const __nv_bfloat16*)w->per_expert_scale, w->correction_bias, c.route_scale, shared ? 1 : 0,
+                                    a.idx, a.route_w, a.sorted, a.groups, a.n_groups));
+        const FastParams P = fast_params(moe, w, n_tokens, a.route_w, h_in, h_out);
+        MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        return MFB_OK;
+    }
     MFB_CUDA(launch_rmsnorm(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, a.xn, (int)c.x_dtype));
     rc = mfb_router_topk(moe, stream, a.xn, c.d, n_tokens, w, a.idx, a.route_w);
     if (rc) return rc;

@@ -59,6 +59,10 @@ struct Arena {
     float* partial = nullptr;       // [max_tokens*(K+1), d]   per-(token, slot) down-projection rows
     __half* xs16 = nullptr;         // [max_tokens*(K+1) (+pad), d] gathered fp16 activations (tensor-core path)
     __half* acts16 = nullptr;       // [max_tokens*(K+1) (+pad), f] fp16 activations (tensor-core path)
+    // fast decode path: fp16 activations in the fragment order of the code width(s), fp16 hidden activations
+    __half* xp = nullptr;           // [max_tokens, d]
+    __half* xp2 = nullptr;          // [max_tokens, d] second permutation when shared_bits != bits
+    __half* actp = nullptr;         // [max_tokens*(K+1), f]
     uint32_t* status = nullptr;     // device status word
     uint32_t n_chunks = 0;
 };
@@ -73,6 +77,7 @@ struct mfb_moe {
     uint64_t max_pairs = 0;   // max_tokens * top_k
     uint64_t max_rows = 0;    // max_tokens * (top_k + 1)
     void* tma = nullptr;      // tensor-map cache of the tcgen05 path (opaque here)
+    bool force_generic = false;  // route every call through the generic SIMT kernels (mfb_moe_set_generic)
 };
 
 namespace mfb {

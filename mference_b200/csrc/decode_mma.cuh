@@ -1,0 +1,45 @@
+// Fast decode path (tensor-core fragments fed from TMA-staged packed rows): interface used by api.cu.
+#pragma once
+
+#include "common.cuh"
+
+namespace mfb {
+
+struct FastParams {
+    const uint8_t* pool;
+    uint64_t slot_stride;
+    const int16_t* slot_of;
+    const uint8_t* shared_blob;
+    mfb_expert_offsets routed_off, shared_off;
+    uint32_t d, f, num_experts, top_k, bits, shared_bits, scale_dtype, activation;
+    float limit;
+    const mfb_pair* sorted;
+    const mfb_group* groups;
+    const uint32_t* n_groups;
+    const __half* xp;         // [tokens, d] fp16 activations, permuted for `bits`
+    const __half* xp_shared;  // the same permuted for `shared_bits` (== xp when the widths agree)
+    __half* actp;             // [sorted pairs (+ tokens), f] fp16 hidden activations, permuted per group width
+    const uint16_t* route_w;  // [tokens, top_k] fp16 bits
+    const void* residual;     // [tokens, d] or NULL
+    void* y;                  // [tokens, d]
+    int x_dtype;
+    uint32_t n_tokens;
+    uint32_t* status;
+};
+
+constexpr uint32_t FAST_MAX_TOKENS = 64;   // phase 2 keeps (token, slot) x 16 partial rows in shared memory
+
+__host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits);
+bool fast_supported(const mfb_moe_config& c);
+size_t fast_smem1(const mfb_moe_config& c);
+size_t fast_smem2(const mfb_moe_config& c, uint32_t n_tokens);
+cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __nv_bfloat16* w, uint32_t n_tokens, uint32_t d,
+                             float eps, bool do_norm, void* xn, __half* xp, uint32_t bits, __half* xp2, uint32_t bits2);
+cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups);
+// select + sort of a small batch in one CTA (router.cu)
+cudaError_t launch_route_small(cudaStream_t s, const float* logits, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k,
+                               int mode, const __nv_bfloat16* per_expert_scale, const float* correction_bias,
+                               float route_scale, int append_shared, uint32_t* out_idx, uint16_t* out_w,
+                               mfb_pair* sorted, mfb_group* groups, uint32_t* n_groups);
+
+}  // namespace mfb

@@ -7,6 +7,7 @@
 // router_gemv_bf16_r4 (Sources/Mference/Metal/MoE/moe.metal:162-185) with its lane sum made concrete, and it
 // makes a block of B token rows bit-identical to B single-row calls.
 #include "common.cuh"
+#include "decode_mma.cuh"
 
 namespace mfb {
 
@@ -98,14 +99,11 @@ __device__ __forceinline__ float sqrtsoftplus(float x) {
 constexpr int SEL_MAX_PER_LANE = MFB_MAX_EXPERTS / 32;
 constexpr uint32_t SEL_NONE = 0xFFFFFFFFu;
 
-__global__ void router_select_kernel(const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts,
-                                     uint32_t top_k, int mode, const __nv_bfloat16* __restrict__ per_expert_scale,
-                                     const float* __restrict__ correction_bias, float route_scale,
-                                     uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w) {
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= n_tokens) return;
-    const float* lg = logits + (size_t)t * num_experts;
+// Selection for one row by one warp; lane r < top_k returns the rank-r expert and its fp16 weight bits.
+__device__ __forceinline__ void select_row(const float* __restrict__ lg, uint32_t num_experts, uint32_t top_k, int mode,
+                                           const __nv_bfloat16* __restrict__ per_expert_scale,
+                                           const float* __restrict__ correction_bias, float route_scale, uint32_t lane,
+                                           uint32_t& out_expert, uint16_t& out_weight) {
     const uint32_t per = (num_experts + 31) / 32, base = lane * per;
     float ch[SEL_MAX_PER_LANE];
 #pragma unroll
@@ -158,8 +156,96 @@ __global__ void router_select_kernel(const float* __restrict__ logits, uint32_t 
             const float gain = per_expert_scale ? __bfloat162float(per_expert_scale[my_idx]) : 1.0f;
             wgt = term / sum * gain;
         }
-        out_idx[(size_t)t * top_k + lane] = my_idx;
-        out_w[(size_t)t * top_k + lane] = __half_as_ushort(__float2half_rn(wgt));
+        out_expert = my_idx;
+        out_weight = __half_as_ushort(__float2half_rn(wgt));
+    }
+}
+
+__global__ void router_select_kernel(const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts,
+                                     uint32_t top_k, int mode, const __nv_bfloat16* __restrict__ per_expert_scale,
+                                     const float* __restrict__ correction_bias, float route_scale,
+                                     uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    uint32_t e = 0;
+    uint16_t w = 0;
+    select_row(logits + (size_t)t * num_experts, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale,
+               lane, e, w);
+    if (lane < top_k) {
+        out_idx[(size_t)t * top_k + lane] = e;
+        out_w[(size_t)t * top_k + lane] = w;
+    }
+}
+
+// Small batches (decode): selection for every row and the sort of the routing table by (expert, token, rank) in
+// one CTA, so a decode layer spends one launch on routing.  Same outputs as router_select_kernel followed by the
+// counting sort of group.cu.
+constexpr uint32_t ROUTE_SMALL_MAX_PAIRS = 1024;
+
+__global__ void __launch_bounds__(256) route_small_kernel(
+    const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k, int mode,
+    const __nv_bfloat16* __restrict__ per_expert_scale, const float* __restrict__ correction_bias, float route_scale,
+    int append_shared, uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, mfb_pair* __restrict__ sorted,
+    mfb_group* __restrict__ groups, uint32_t* __restrict__ n_groups) {
+    __shared__ uint32_t s_idx[ROUTE_SMALL_MAX_PAIRS];
+    __shared__ uint16_t s_w[ROUTE_SMALL_MAX_PAIRS];
+    __shared__ uint32_t s_run[MFB_MAX_EXPERTS];
+    __shared__ uint32_t s_total;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_pairs = n_tokens * top_k;
+    for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) s_run[e] = 0;
+    for (uint32_t t = warp; t < n_tokens; t += blockDim.x >> 5) {
+        uint32_t e = 0;
+        uint16_t w = 0;
+        select_row(logits + (size_t)t * num_experts, num_experts, top_k, mode, per_expert_scale, correction_bias,
+                   route_scale, lane, e, w);
+        if (lane < top_k) {
+            s_idx[t * top_k + lane] = e;
+            s_w[t * top_k + lane] = w;
+            out_idx[(size_t)t * top_k + lane] = e;
+            out_w[(size_t)t * top_k + lane] = w;
+        }
+    }
+    __syncthreads();
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&s_run[s_idx[p]], 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0, ng = 0;
+        for (uint32_t e = 0; e < num_experts; ++e) {
+            const uint32_t c = s_run[e];
+            s_run[e] = run;
+            if (c) { groups[ng].expert = e; groups[ng].pair_start = run; groups[ng].pair_count = c; ++ng; }
+            run += c;
+        }
+        if (append_shared) { groups[ng].expert = num_experts; groups[ng].pair_start = run; groups[ng].pair_count = n_tokens; ++ng; }
+        *n_groups = ng;
+        s_total = run;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // ordered scatter: 32 pairs per round in (token, rank) order
+        for (uint32_t p0 = 0; p0 < n_pairs; p0 += 32) {
+            const uint32_t p = p0 + lane;
+            const uint32_t e = p < n_pairs ? s_idx[p] : 0xFFFFFFFFu;
+            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, e);
+            const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+            uint32_t pos = 0;
+            if (p < n_pairs) pos = s_run[e] + before;
+            __syncwarp();
+            if (p < n_pairs && before == 0) s_run[e] += __popc(peers);
+            __syncwarp();
+            if (p < n_pairs) {
+                mfb_pair out;
+                out.token = p / top_k; out.expert = e; out.rank = p % top_k; out.weight_bits = s_w[p];
+                sorted[pos] = out;
+            }
+        }
+    } else if (append_shared) {
+        for (uint32_t t = threadIdx.x - 32; t < n_tokens; t += blockDim.x - 32) {
+            mfb_pair out;
+            out.token = t; out.expert = num_experts; out.rank = top_k; out.weight_bits = 0x3C00u;
+            sorted[s_total + t] = out;
+        }
     }
 }
 
@@ -208,6 +294,18 @@ cudaError_t launch_router_select(cudaStream_t s, const float* logits, uint32_t n
     const uint32_t warps = n_tokens >= 4 ? 4 : 1;
     router_select_kernel<<<(n_tokens + warps - 1) / warps, warps * 32, 0, s>>>(
         logits, n_tokens, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, out_idx, out_w);
+    count_launches(1);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_route_small(cudaStream_t s, const float* logits, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k,
+                               int mode, const __nv_bfloat16* per_expert_scale, const float* correction_bias,
+                               float route_scale, int append_shared, uint32_t* out_idx, uint16_t* out_w,
+                               mfb_pair* sorted, mfb_group* groups, uint32_t* n_groups) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (n_tokens * top_k > ROUTE_SMALL_MAX_PAIRS) return cudaErrorInvalidValue;
+    route_small_kernel<<<1, 256, 0, s>>>(logits, n_tokens, num_experts, top_k, mode, per_expert_scale, correction_bias,
+                                         route_scale, append_shared, out_idx, out_w, sorted, groups, n_groups);
     count_launches(1);
     return cudaGetLastError();
 }

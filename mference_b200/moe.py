@@ -225,6 +225,10 @@ class MoE:
     def encode_residual_add(self, a, b, out):
         L.check(self.lib.mfb_residual_add(self.handle, _stream(), _ptr(a), _ptr(b), a.numel(), _ptr(out)))
 
+    def set_generic(self, on: bool):
+        """Route every call through the generic kernels instead of the shape-specialised fast ones."""
+        L.check(self.lib.mfb_moe_set_generic(self.handle, 1 if on else 0))
+
     def device_status(self) -> int:
         st = C.c_uint32()
         rc = self.lib.mfb_moe_device_status(self.handle, _stream(), C.byref(st))

@@ -43,6 +43,13 @@ SHAPES = [
     (4096, 256, 8, 2, 4, 4, 2),
     (2048, 512, 24, 8, 4, 4, 1),
     (2048, 512, 24, 8, 4, 4, 8),
+    # shapes the tensor-core-fragment fast path takes (d a multiple of 512, f <= 512), both code widths,
+    # token counts that leave partial and multiple 8-column tiles
+    (2048, 512, 12, 4, 2, 4, 3),
+    (2048, 512, 6, 3, 4, 4, 19),
+    (512, 128, 8, 2, 4, 4, 5),
+    (1024, 256, 8, 3, 2, 2, 11),
+    (4096, 512, 6, 2, 4, 2, 2),
 ]
 
 
@@ -209,3 +216,25 @@ def test_capacity_and_argument_errors():
         moe.encode_experts(lw, x[:2], idx[:2], w[:2], active_slots=[5])
     assert ei.value.code == L.ERR_INVALID_ARGUMENT
     assert moe.device_status() == 0
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 9, 64])
+def test_fast_path_agrees_with_generic_path(T):
+    import torch
+    from mference_b200.moe import MoE
+    d, f, E, K = 2048, 512, 32, 8
+    W = O.LayerWeights(d, f, E, K)
+    h = make_x("h", T, d, std=2.0)
+    moe = MoE(d, f, E, K, max_tokens=T)
+    lw = upload_layer(W)
+    hd = to_dev16(h, O.DT_BF16)
+    fast = torch.empty_like(hd)
+    moe.encode_layer(lw, hd, fast)
+    moe.set_generic(True)
+    slow = torch.empty_like(hd)
+    moe.encode_layer(lw, hd, slow)
+    assert moe.device_status() == 0
+    a, b = fast.float().cpu().numpy(), slow.float().cpu().numpy()
+    assert np.isfinite(a).all()
+    # both sit within the tolerance of the oracle; against each other they differ by output rounding at most
+    assert O.rel_l2(a, b) <= TOL_REL_L2
