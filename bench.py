@@ -1,11 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the MoE feed-forward hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--rows fresh|chained] [--layers L]
+                    [--impl ours|reference]
 
 One step = one pass of the 40-layer Qwen3.6-A3B-shaped MoE FFN stack (hidden 2048, 256 experts top-8 + 1 shared,
-intermediate 512, 4-bit group-64 affine weights, bf16 activations, RMSNorm between layers) over one decode batch
-of B token rows.  Weights are seeded synthetic (generated on the device), fully resident in HBM.
+intermediate 512, 4-bit group-64 affine weights, bf16 activations, RMSNorm in front of every layer) over one decode
+batch of B token rows.  Weights are seeded synthetic (generated on the device) and fully resident in HBM.
+
+--rows chained  the residual stream h <- h + MoE(RMSNorm(h)) runs through all layers (mfb_moe_stack).  With the
+                configuration's all-positive synthetic weights every expert's output is close to a multiple of the
+                all-ones vector, so after the first layer all rows route alike and a batch touches far fewer distinct
+                experts than independent rows would.
+--rows fresh    (default for B > 1) every layer gets its own N(0,1) bf16 batch, layers still run strictly one after
+                the other on one stream; rows route independently as the configuration intends (about 57 distinct
+                experts per layer at B = 8, 222 at B = 64).  For B = 1 both modes touch 8 experts per layer; the
+                default there is chained, which keeps the true layer-to-layer dependency.
 
 Prints ONE JSON line.  `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same through the
 C ABI with host buffers (pinned host -> device copy of the step's rows and device -> host read of the result inside
@@ -31,7 +41,7 @@ sys.path.insert(0, ROOT)
 
 D, F, E, K, LAYERS = 2048, 512, 256, 8, 40
 ROOT_SEED = 0xB2000001
-N_INPUTS = 8          # distinct input batches cycled through the steps
+N_INPUTS = 4          # distinct input sets cycled through the steps
 
 
 def measured_peaks():
@@ -95,10 +105,9 @@ def layer_bytes(unique_experts: int, n_tokens: int, blob: int) -> int:
 
 # ----------------------------------------------------------------------------------------------- CPU arm
 
-def cpu_port_tokens_per_s(batch: int, budget_s: float):
+def cpu_port_tokens_per_s(batch: int, budget_s: float, layers: int = LAYERS):
     """Times the CPU port of the reference's scalar decode path (oracle/mfb_oracle.c: mfbo_ref_moe_layer_f32 plus the
     router) on this box's host cores, on ONE layer of the stack, and scales by the layer count."""
-    import numpy as np
     from oracle import oracle as O
     rows = min(batch, 8)
     W0 = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=[])
@@ -118,8 +127,8 @@ def cpu_port_tokens_per_s(batch: int, budget_s: float):
         if dt >= budget_s or reps >= 2000:
             break
     per_layer = dt / reps
-    tok_s = rows / (per_layer * LAYERS)
-    return tok_s, O.num_threads(), f"1 of {LAYERS} layers x {rows} token rows x {reps} repeats, scaled x{LAYERS}", per_layer
+    tok_s = rows / (per_layer * layers)
+    return tok_s, O.num_threads(), f"1 of {layers} layers x {rows} token rows x {reps} repeats, scaled x{layers}"
 
 
 def run_reference(args):
@@ -127,11 +136,11 @@ def run_reference(args):
     if rank != 0:
         return
     steps, warm = max(args.steps, 1), args.warmup
-    budget = max(2.0, min(20.0, 90.0 / (steps + warm)))
+    budget = max(1.0, min(15.0, 90.0 / (steps + warm)))
     vals = []
-    cores, sample, per_layer = 1, "", 0.0
+    cores, sample = 1, ""
     for i in range(steps + warm):
-        tok_s, cores, sample, per_layer = cpu_port_tokens_per_s(args.batch, budget)
+        tok_s, cores, sample = cpu_port_tokens_per_s(args.batch, budget, args.layers)
         if i >= warm:
             vals.append(tok_s)
     v = statistics.mean(vals)
@@ -140,7 +149,7 @@ def run_reference(args):
         "impl": "reference", "metric": "moe_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": 1e3 * rows / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"configs[1]: {LAYERS}-layer Qwen3.6-A3B MoE FFN stack, decode batch {rows} (CPU port)",
+        "config": {"workload": f"configs[1]: {args.layers}-layer Qwen3.6-A3B MoE FFN stack, decode batch {rows} (CPU port)",
                    "note": "the reference is Swift + Metal and cannot be built here; this arm is the C port of its scalar "
                            "path (oracle/mfb_oracle.c) on the host cores"},
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
@@ -163,38 +172,50 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = L.load()
-    B = args.batch
+    B, NL = args.batch, args.layers
+    fresh = args.rows == "fresh"
     _, blob = expert_layout(4, D, F)
 
-    layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(LAYERS)]
+    layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(NL)]
     moe = MoE(D, F, E, K, max_tokens=B)
     stack = moe.make_stack(layers)
-    inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", B * D, dtype=L.DT_BF16).view(B, D) for i in range(N_INPUTS)]
+    n_sets = N_INPUTS
+    if fresh:   # one [NL, B, D] set of independent rows per input set
+        inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", NL * B * D, dtype=L.DT_BF16).view(NL, B, D) for i in range(n_sets)]
+    else:
+        inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", B * D, dtype=L.DT_BF16).view(B, D) for i in range(n_sets)]
     torch.cuda.synchronize()
 
-    # distinct experts per layer for each input batch (untimed; same kernels, layer by layer)
+    # distinct experts per layer for each input set (untimed; same kernels, layer by layer)
     step_bytes = []
     idx = torch.empty((B, K), dtype=torch.int32, device="cuda")
     w = torch.empty((B, K), dtype=torch.float16, device="cuda")
     for h0 in inputs:
-        h = h0.clone()
         total = 0
-        for lw in layers:
-            xn = torch.empty_like(h)
-            moe.encode_rmsnorm(h, xn, lw.norm_w)
+        h = None if fresh else h0.clone()
+        for l, lw in enumerate(layers):
+            src = h0[l] if fresh else h
+            xn = torch.empty_like(src)
+            moe.encode_rmsnorm(src, xn, lw.norm_w)
             moe.encode_router(xn, lw, idx, w)
             total += layer_bytes(int(torch.unique(idx).numel()), B, blob)
-            nxt = torch.empty_like(h)
-            moe.encode_decode(lw, xn, idx, w, nxt, residual=h)
-            h = nxt
+            if not fresh:
+                nxt = torch.empty_like(h)
+                moe.encode_decode(lw, xn, idx, w, nxt, residual=h)
+                h = nxt
         step_bytes.append(total)
     torch.cuda.synchronize()
-    work = [t.clone() for t in inputs]
+    work = [torch.empty_like(t) for t in inputs]
 
-    def step(i):
-        buf = work[i % N_INPUTS]
-        buf.copy_(inputs[i % N_INPUTS])
-        moe.encode_stack(stack, buf)
+    def step(i, src=None):
+        buf = work[i % n_sets]
+        if src is None:
+            buf.copy_(inputs[i % n_sets])
+        if fresh:
+            moe.encode_stack_rows(stack, buf)    # layer l on rows buf[l]; strictly one layer after the other
+        else:
+            moe.encode_stack(stack, buf)
+        return buf
 
     def barrier():
         if world > 1:
@@ -220,19 +241,16 @@ def run_ours(args):
 
     # end to end through the C ABI with host buffers
     host_in = [t.cpu().pin_memory() for t in inputs]
-    host_out = torch.empty((B, D), dtype=torch.bfloat16).pin_memory()
-    dev = torch.empty((B, D), dtype=torch.bfloat16, device="cuda")
-    for i in range(min(args.warmup, 3)):
-        dev.copy_(host_in[i % N_INPUTS], non_blocking=True)
-        moe.encode_stack(stack, dev)
-        host_out.copy_(dev, non_blocking=True)
+    host_out = torch.empty_like(host_in[0]).pin_memory()
+    for i in range(3):
+        work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
+        host_out.copy_(step(i, src="host"), non_blocking=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        dev.copy_(host_in[i % N_INPUTS], non_blocking=True)
-        moe.encode_stack(stack, dev)
-        host_out.copy_(dev, non_blocking=True)
+        work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
+        host_out.copy_(step(i, src="host"), non_blocking=True)
         torch.cuda.current_stream().synchronize()   # the caller reads the result before the next step
     e1.record()
     barrier()
@@ -252,24 +270,26 @@ def run_ours(args):
     value = world * B * args.steps / (total_ms * 1e-3)
     e2e = world * B * args.steps / (e2e_ms * 1e-3)
     hbm_peak, _, peak_kind = measured_peaks()
-    bytes_per_step = statistics.mean(step_bytes[i % N_INPUTS] for i in range(args.steps))
+    bytes_per_step = statistics.mean(step_bytes[i % n_sets] for i in range(args.steps))
     achieved = bytes_per_step / (statistics.mean(per_step_ms) * 1e-3) / 1e9
-    cpu_tok_s, cores, sample, _ = cpu_port_tokens_per_s(B, 12.0)
+    cpu_tok_s, cores, sample = cpu_port_tokens_per_s(B, 10.0, NL)
+    io_bytes = inputs[0].numel() * 2
     out = {
         "metric": "moe_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"configs[1]: {LAYERS}-layer Qwen3.6-A3B MoE FFN stack, decode batch {B}", "hidden": D,
-                   "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4, "group_size": 64,
-                   "layers": LAYERS, "batch_per_gpu": B, "activation_dtype": "bf16", "accumulate": "f32",
-                   "parallelism": "replicas" if world > 1 else "single",
+        "config": {"workload": f"configs[1]: {NL}-layer Qwen3.6-A3B MoE FFN stack, decode batch {B}, {args.rows} rows",
+                   "hidden": D, "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4,
+                   "group_size": 64, "layers": NL, "batch_per_gpu": B, "rows": args.rows, "activation_dtype": "bf16",
+                   "accumulate": "f32", "parallelism": "replicas" if world > 1 else "single",
+                   "distinct_experts_per_layer": round((bytes_per_step / NL - blob - E * D * 2 - B * D * 4) / blob, 1),
                    "l2": f"inputs larger than L2: {bytes_per_step / 1e6:.0f} MB of distinct weight bytes per step, "
-                         f"{N_INPUTS} input batches cycled"},
+                         f"{n_sets} input sets cycled"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "peak_kind": peak_kind, "traffic": None, "kernel": "whole step (all kernels of the 40-layer pass)",
+                     "peak_kind": peak_kind, "traffic": None, "kernel": "whole step (all kernels of the pass)",
                      "algorithmic_bytes_per_step": bytes_per_step},
         "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": B * D * 2},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -284,9 +304,13 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=64, help="decode batch (token rows per step per GPU): 1, 8 or 64")
+    ap.add_argument("--rows", default=None, choices=["fresh", "chained"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers only for profiling a small case")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.rows is None:
+        args.rows = "chained" if args.batch == 1 else "fresh"
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -138,6 +138,11 @@ int32_t mfb_moe_destroy(mfb_moe* moe);
  * instead of the shape-specialised fast kernels; the two agree within the documented tolerance.  Plays the part of
  * the reference's generic vs. specialised pipeline states (MoE.swift:77-135). */
 int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on);
+/* Phase tracing of the fused stack kernel (the reference's MFERENCE_PHASES counters,
+ * Sources/Mference/Runtime/Inference/RealForwardRunner.swift:395-398, 5478-5529): while a device buffer of
+ * n_layers x 8 uint64 is attached, mfb_moe_stack / mfb_moe_stack_rows record the GPU global timer (ns) at the
+ * eight phase boundaries of every layer: norm, logits, select, sort, phase 1, barrier, phase 2, end.  NULL detaches. */
+int32_t mfb_moe_set_trace(mfb_moe* moe, uint64_t* device_stamps);
 /* Reads and clears the device status word that kernels set when a bounded wait runs out. Synchronises `stream`. */
 int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status);
 
@@ -194,6 +199,12 @@ int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_weights* w, co
 /* n_layers of the above back to back (the per-layer loop RealForwardRunner.swift:2646). */
 int32_t mfb_moe_stack(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
                       void* hidden, uint32_t n_tokens);
+
+/* The same loop over separate row blocks: layer l reads and rewrites the n_tokens rows at rows + l * layer_stride
+ * elements (layer_stride = 0 is mfb_moe_stack).  Layers still run strictly one after the other.  Serves callers
+ * that interleave independent micro-batches through the layers. */
+int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
+                           void* rows, uint64_t layer_stride, uint32_t n_tokens);
 
 /* ---- prefill / ragged batch ---------------------------------------------------------------------------- */
 

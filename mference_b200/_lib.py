@@ -78,6 +78,7 @@ SIGNATURES = {
     "mfb_moe_create": (_I32, [C.POINTER(MoEConfig), C.POINTER(_V)]),
     "mfb_moe_destroy": (_I32, [_V]),
     "mfb_moe_set_generic": (_I32, [_V, _I32]),
+    "mfb_moe_set_trace": (_I32, [_V, _V]),
     "mfb_moe_device_status": (_I32, [_V, _V, C.POINTER(_U32)]),
     "mfb_router_logits": (_I32, [_V, _V, _V, _U32, _U32, _V, _V, _V]),
     "mfb_router_select": (_I32, [_V, _V, _V, _U32, _V, _V, _V, _V]),
@@ -88,6 +89,7 @@ SIGNATURES = {
     "mfb_moe_combine": (_I32, [_V, _V, _U32, _V, _I32, _V, _V]),
     "mfb_moe_layer": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _V, _U32]),
     "mfb_moe_stack": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _U32, _V, _U32]),
+    "mfb_moe_stack_rows": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _U32, _V, _U64, _U32]),
     "mfb_moe_group": (_I32, [_V, _V, _V, _V, _U32, _V, _V, _V, _V, _V]),
     "mfb_moe_group_host": (_I32, [_V, _I64, _I64, _I64, _I64, _I64, _V, _I64, _V, _V, _V, _V, C.POINTER(_U32), _V,
                                   C.POINTER(_U32), C.POINTER(_U32), C.POINTER(_U32)]),

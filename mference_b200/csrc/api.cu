@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 #include "decode_mma.cuh"
@@ -198,6 +199,11 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     ok(dev_alloc(a.partial, m->max_rows * c.d));
     ok(dev_alloc(a.status, 1));
     if (fast_supported(c)) {
+        int coop = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device);
+        m->coop = coop != 0;
+        ok(fast_init());
+        ok(dev_alloc(m->mega_bar, 2));
         const uint64_t ft = T < FAST_MAX_TOKENS ? T : FAST_MAX_TOKENS;
         ok(dev_alloc(a.xp, ft * c.d));
         if (c.shared_bits && c.shared_bits != c.bits) ok(dev_alloc(a.xp2, ft * c.d));
@@ -225,6 +231,9 @@ extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
     if (!moe) return MFB_OK;
     tc_release(moe);
     free_arena(moe->a);
+    cudaFree(moe->mega_dev);
+    cudaFree(moe->mega_bar);
+    free(moe->mega_host);
     delete moe;
     return MFB_OK;
 }
@@ -232,6 +241,12 @@ extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
 extern "C" int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on) {
     MFB_REQUIRE(moe != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
     moe->force_generic = on != 0;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_set_trace(mfb_moe* moe, uint64_t* device_stamps) {
+    MFB_REQUIRE(moe != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
+    moe->trace = device_stamps;
     return MFB_OK;
 }
 
@@ -376,14 +391,76 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
     return mfb_moe_decode(moe, stream, w, a.xn, c.d, n_tokens, a.idx, a.route_w, h_in, h_out);
 }
 
-extern "C" int32_t mfb_moe_stack(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
-                                 void* hidden, uint32_t n_tokens) {
-    MFB_REQUIRE(layers != nullptr || n_layers == 0, MFB_ERR_INVALID_ARGUMENT, "stack: layers is NULL");
+// Builds (or reuses) the device table of per-layer weights for the fused stack kernel.
+static int32_t upload_layer_table(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* layers, uint32_t n_layers) {
+    std::vector<MegaLayer> host(n_layers);
     for (uint32_t l = 0; l < n_layers; ++l) {
-        const int32_t rc = mfb_moe_layer(moe, stream, &layers[l], hidden, hidden, n_tokens);
+        const mfb_layer_weights& w = layers[l];
+        MegaLayer& o = host[l];
+        memset(&o, 0, sizeof o);
+        o.router_w = (const __nv_bfloat16*)w.router_w; o.logit_bias = w.logit_bias;
+        o.per_expert_scale = (const __nv_bfloat16*)w.per_expert_scale; o.correction_bias = w.correction_bias;
+        o.norm_w = (const __nv_bfloat16*)w.norm_w; o.pool = w.pool; o.slot_stride = w.slot_stride; o.slot_of = w.slot_of;
+        o.shared_blob = w.shared_blob; o.routed_off = w.routed_off; o.shared_off = w.shared_off;
+    }
+    const size_t bytes = (size_t)n_layers * sizeof(MegaLayer);
+    if (m->mega_host && m->mega_count == n_layers && memcmp(m->mega_host, host.data(), bytes) == 0) return MFB_OK;
+    if (n_layers > m->mega_cap) {
+        cudaFree(m->mega_dev); free(m->mega_host);
+        m->mega_dev = nullptr; m->mega_host = nullptr; m->mega_cap = 0;
+        MFB_CUDA(cudaMalloc(&m->mega_dev, bytes));
+        m->mega_host = malloc(bytes);
+        MFB_REQUIRE(m->mega_host != nullptr, MFB_ERR_ALLOC, "out of host memory");
+        m->mega_cap = n_layers;
+    }
+    memcpy(m->mega_host, host.data(), bytes);
+    m->mega_count = n_layers;
+    // the source is pageable host memory: the runtime stages it before returning, so reusing mega_host is safe
+    MFB_CUDA(cudaMemcpyAsync(m->mega_dev, m->mega_host, bytes, cudaMemcpyHostToDevice, s));
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
+                                      void* rows, uint64_t layer_stride, uint32_t n_tokens) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    MFB_REQUIRE(layers != nullptr || n_layers == 0, MFB_ERR_INVALID_ARGUMENT, "stack: layers is NULL");
+    MFB_REQUIRE(rows != nullptr, MFB_ERR_INVALID_ARGUMENT, "stack: rows is NULL");
+    MFB_REQUIRE(layer_stride == 0 || layer_stride >= (uint64_t)n_tokens * moe->cfg.d, MFB_ERR_INVALID_ARGUMENT,
+                "stack: layer stride smaller than one layer's rows");
+    if (n_layers == 0 || n_tokens == 0) return MFB_OK;
+    const mfb_moe_config& c = moe->cfg;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (use_fast(moe, n_tokens) && moe->coop && fast_smem_stack(c, n_tokens) <= 226 * 1024) {
+        for (uint32_t l = 0; l < n_layers; ++l) {
+            rc = check_weights(moe, &layers[l], true);
+            if (rc) return rc;
+        }
+        rc = upload_layer_table(moe, s, layers, n_layers);
+        if (rc) return rc;
+        Arena& a = moe->a;
+        MegaParams M;
+        M.layers = (const MegaLayer*)moe->mega_dev; M.n_layers = n_layers;
+        M.d = c.d; M.f = c.f; M.num_experts = c.num_experts; M.top_k = c.top_k; M.bits = c.bits; M.shared_bits = c.shared_bits;
+        M.scale_dtype = c.scale_dtype; M.activation = c.activation; M.router_mode = (int)c.router_mode; M.x_dtype = (int)c.x_dtype;
+        M.limit = c.swiglu_limit; M.route_scale = c.route_scale; M.eps = c.rms_eps;
+        M.hidden = rows; M.layer_stride = layer_stride; M.n_tokens = n_tokens;
+        M.xn = a.xn; M.xp = a.xp; M.xp2 = a.xp2; M.logits = a.logits; M.idx = a.idx; M.route_w = a.route_w; M.actp = a.actp;
+        M.bar_counter = moe->mega_bar; M.abort = moe->mega_bar + 1; M.status = a.status; M.trace = moe->trace;
+        MFB_CUDA(launch_stack_mega(s, M, c, moe->sm_count));
+        return MFB_OK;
+    }
+    for (uint32_t l = 0; l < n_layers; ++l) {
+        void* h = (uint8_t*)rows + (size_t)l * layer_stride * 2;
+        rc = mfb_moe_layer(moe, stream, &layers[l], h, h, n_tokens);
         if (rc) return rc;
     }
     return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_stack(mfb_moe* moe, void* stream, const mfb_layer_weights* layers, uint32_t n_layers,
+                                 void* hidden, uint32_t n_tokens) {
+    return mfb_moe_stack_rows(moe, stream, layers, n_layers, hidden, 0, n_tokens);
 }
 
 // ------------------------------------------------------------------------------------------------- prefill

@@ -78,6 +78,14 @@ struct mfb_moe {
     uint64_t max_rows = 0;    // max_tokens * (top_k + 1)
     void* tma = nullptr;      // tensor-map cache of the tcgen05 path (opaque here)
     bool force_generic = false;  // route every call through the generic SIMT kernels (mfb_moe_set_generic)
+    // fused stack kernel: device copy of the per-layer weight table, its host mirror (to skip identical uploads),
+    // the barrier words, and whether the device supports cooperative launches
+    void* mega_dev = nullptr;
+    void* mega_host = nullptr;
+    uint32_t mega_cap = 0, mega_count = 0;
+    uint32_t* mega_bar = nullptr;
+    bool coop = false;
+    uint64_t* trace = nullptr;   // device buffer for phase time stamps (mfb_moe_set_trace), not owned
 };
 
 namespace mfb {

@@ -21,6 +21,7 @@
 // matching within-16 order (see perm_pos).
 #include "common.cuh"
 #include "decode_mma.cuh"
+#include "select.cuh"
 
 namespace mfb {
 
@@ -73,7 +74,7 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
@@ -149,6 +150,24 @@ __host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits) {
 
 namespace {
 
+// Loads that bypass L1: for buffers other CTAs write during the same launch (fused stack kernel) a line left in
+// this SM's L1 by an earlier layer would be stale.
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint16_t ld_cg_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
 struct GroupRef {
     const uint8_t* blob;
     mfb_expert_offsets off;
@@ -156,6 +175,7 @@ struct GroupRef {
     bool shared, ok;
 };
 
+// P.groups / P.sorted may live in global memory (separate kernels) or in shared memory (fused kernel).
 __device__ __forceinline__ GroupRef group_ref(const FastParams& P, uint32_t g) {
     GroupRef v;
     const mfb_group grp = P.groups[g];
@@ -176,39 +196,39 @@ __device__ __forceinline__ GroupRef group_ref(const FastParams& P, uint32_t g) {
     return v;
 }
 
-// Loads the B fragments (activations of token column g of the tile, this warp's k range) and leaves the
-// per-group activation sums of the eight token columns in sx[group][column].
+// B fragments: activations of token column g of the tile for NG consecutive 64-element groups starting at k0.
 template <int NG>
 __device__ __forceinline__ void load_bfrags(const __half* row_ptr /* nullptr: column unused */, uint32_t k0, uint32_t lane,
-                                            uint32_t (&bf)[NG][8], float* sx /* [NG][8] */) {
-    const uint32_t g = lane >> 2, t = lane & 3;
+                                            uint32_t (&bf)[NG][8]) {
+    const uint32_t t = lane & 3;
 #pragma unroll
     for (int gi = 0; gi < NG; ++gi) {
         uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
         if (row_ptr) {
-            const uint4* src = reinterpret_cast<const uint4*>(row_ptr + k0 + gi * 64 + t * 16);
-            lo = src[0]; hi = src[1];
+            const __half* src = row_ptr + k0 + gi * 64 + t * 16;
+            lo = ld_cg_u4(src);
+            hi = ld_cg_u4(src + 8);
         }
         bf[gi][0] = lo.x; bf[gi][1] = lo.y; bf[gi][2] = lo.z; bf[gi][3] = lo.w;
         bf[gi][4] = hi.x; bf[gi][5] = hi.y; bf[gi][6] = hi.z; bf[gi][7] = hi.w;
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&bf[gi][i]));
-            s += v.x + v.y;
-        }
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-        if (t == 0) sx[gi * 8 + g] = s;
     }
-    __syncwarp();
+}
+
+// sum(x) over one 64-element group for this lane's two token columns (2t, 2t+1): four MMAs against an all-ones
+// A fragment leave exactly those sums in c0 and c1 - no conversions, shuffles or shared memory.
+__device__ __forceinline__ float2 group_sum(const uint32_t (&bf)[8]) {
+    constexpr uint32_t ONES = 0x3C003C00u;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mma16816(d, ONES, ONES, ONES, ONES, bf[2 * j], bf[2 * j + 1]);
+    return make_float2(d[0], d[1]);
 }
 
 // One 64-element group of rows g and g+8 of one matrix: sum(code * x) by four MMAs, then the affine factors.
 template <int BITS>
 __device__ __forceinline__ void group_mma(const uint8_t* row_lo, const uint8_t* row_hi, uint32_t byte_off,
                                           const uint32_t (&bf)[8], float s_lo, float b_lo, float s_hi, float b_hi,
-                                          float sx0, float sx1, float (&acc)[4]) {
+                                          float2 sx, float (&acc)[4]) {
     constexpr int W = Unpack<BITS>::WORDS;
     uint32_t wl[W], wh[W];
     if (W == 2) {
@@ -225,11 +245,28 @@ __device__ __forceinline__ void group_mma(const uint8_t* row_lo, const uint8_t* 
     float dsum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < 4; ++j) mma16816(dsum, pl[2 * j], ph[2 * j], pl[2 * j + 1], ph[2 * j + 1], bf[2 * j], bf[2 * j + 1]);
-    acc[0] = fmaf(s_lo, dsum[0], acc[0]); acc[0] = fmaf(b_lo, sx0, acc[0]);
-    acc[1] = fmaf(s_lo, dsum[1], acc[1]); acc[1] = fmaf(b_lo, sx1, acc[1]);
-    acc[2] = fmaf(s_hi, dsum[2], acc[2]); acc[2] = fmaf(b_hi, sx0, acc[2]);
-    acc[3] = fmaf(s_hi, dsum[3], acc[3]); acc[3] = fmaf(b_hi, sx1, acc[3]);
+    acc[0] = fmaf(s_lo, dsum[0], acc[0]); acc[0] = fmaf(b_lo, sx.x, acc[0]);
+    acc[1] = fmaf(s_lo, dsum[1], acc[1]); acc[1] = fmaf(b_lo, sx.y, acc[1]);
+    acc[2] = fmaf(s_hi, dsum[2], acc[2]); acc[2] = fmaf(b_hi, sx.x, acc[2]);
+    acc[3] = fmaf(s_hi, dsum[3], acc[3]); acc[3] = fmaf(b_hi, sx.y, acc[3]);
 }
+
+// NG consecutive 16-bit scales (or biases) of one row with the widest load that fits; element i afterwards by
+// scale_at.
+template <int NG>
+struct ScaleRow {
+    uint32_t w[(NG + 1) / 2];
+    __device__ __forceinline__ void load(const uint16_t* p) {
+        if (NG == 8) { const uint4 v = *reinterpret_cast<const uint4*>(p); w[0] = v.x; w[(NG > 2) ? 1 : 0] = v.y; w[(NG > 4) ? 2 : 0] = v.z; w[(NG > 6) ? 3 : 0] = v.w; }
+        else if (NG == 4) { const uint2 v = *reinterpret_cast<const uint2*>(p); w[0] = v.x; w[(NG > 2) ? 1 : 0] = v.y; }
+        else if (NG == 2) w[0] = *reinterpret_cast<const uint32_t*>(p);
+        else w[0] = *p;
+    }
+    __device__ __forceinline__ float at(int i, int dtype) const {
+        const uint32_t h = (i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xFFFFu);
+        return widen16((uint16_t)h, dtype);
+    }
+};
 
 // ------------------------------------------------------------------------------------------ phase 1
 // Work item = (group, tile of TILE_ROWS rows of gate and up).  Warp w of the 8 compute warps owns k range
@@ -253,8 +290,7 @@ __host__ __device__ inline F1Geom f1_geom(uint32_t d, uint32_t f, uint32_t max_b
 
 template <int BITS>
 __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& G, const F1Geom& geo, const uint8_t* stage,
-                                           uint32_t tile, uint32_t warp, uint32_t lane, float* sx_w, float* red,
-                                           uint32_t& red_buf) {
+                                           uint32_t tile, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t ks = warp % geo.ks_count, rt = warp / geo.ks_count;
     const uint32_t row_bytes = P.d * BITS / 8, row_stride = row_bytes + ROW_PAD;
@@ -262,30 +298,38 @@ __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& 
     const uint8_t* gate_rows = stage;
     const uint8_t* up_rows = stage + geo.tile_rows * geo.row_stride_max;
     const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + 2 * geo.tile_rows * geo.row_stride_max);
-    const uint16_t* gs = sc, *gb = sc + geo.tile_rows * gpr, *us = gb + geo.tile_rows * gpr, *ub = us + geo.tile_rows * gpr;
+    const uint32_t blk = geo.tile_rows * gpr;
     const uint32_t r_lo = rt * 16 + g, r_hi = r_lo + 8;
     const uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const __half* xsrc = (G.shared && P.shared_bits != P.bits) ? P.xp_shared : P.xp;
     const int sdt = (int)P.scale_dtype;
+    const uint8_t* g_lo = gate_rows + r_lo * row_stride, *g_hi = gate_rows + r_hi * row_stride;
+    const uint8_t* u_lo = up_rows + r_lo * row_stride, *u_hi = up_rows + r_hi * row_stride;
 
     for (uint32_t tt = 0; tt < G.pair_count; tt += 8) {
         const uint32_t cols = min(8u, G.pair_count - tt);
         const __half* row_ptr = nullptr;
         if (g < cols) row_ptr = xsrc + (size_t)P.sorted[G.pair_start + tt + g].token * P.d;
         uint32_t bf[8][8];
-        load_bfrags<8>(row_ptr, ks * 512, lane, bf, sx_w);
+        load_bfrags<8>(row_ptr, ks * 512, lane, bf);
         float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int gi = 0; gi < 8; ++gi) {
-            const uint32_t grp = ks * 8 + gi;
-            const uint32_t boff = grp * group_bytes + t * lane_bytes;
-            const float2 sxv = *reinterpret_cast<const float2*>(sx_w + gi * 8 + 2 * t);
-            group_mma<BITS>(gate_rows + r_lo * row_stride, gate_rows + r_hi * row_stride, boff, bf[gi],
-                            widen16(gs[r_lo * gpr + grp], sdt), widen16(gb[r_lo * gpr + grp], sdt),
-                            widen16(gs[r_hi * gpr + grp], sdt), widen16(gb[r_hi * gpr + grp], sdt), sxv.x, sxv.y, ag);
-            group_mma<BITS>(up_rows + r_lo * row_stride, up_rows + r_hi * row_stride, boff, bf[gi],
-                            widen16(us[r_lo * gpr + grp], sdt), widen16(ub[r_lo * gpr + grp], sdt),
-                            widen16(us[r_hi * gpr + grp], sdt), widen16(ub[r_hi * gpr + grp], sdt), sxv.x, sxv.y, au);
+        for (int gp = 0; gp < 4; ++gp) {
+            // scales and biases of two consecutive groups, rows r_lo / r_hi of gate_s, gate_b, up_s, up_b
+            ScaleRow<2> sr[8];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                sr[2 * m].load(sc + m * blk + r_lo * gpr + ks * 8 + gp * 2);
+                sr[2 * m + 1].load(sc + m * blk + r_hi * gpr + ks * 8 + gp * 2);
+            }
+#pragma unroll
+            for (int gj = 0; gj < 2; ++gj) {
+                const int gi = gp * 2 + gj;
+                const uint32_t boff = (ks * 8 + gi) * group_bytes + t * lane_bytes;
+                const float2 sxv = group_sum(bf[gi]);
+                group_mma<BITS>(g_lo, g_hi, boff, bf[gi], sr[0].at(gj, sdt), sr[2].at(gj, sdt), sr[1].at(gj, sdt), sr[3].at(gj, sdt), sxv, ag);
+                group_mma<BITS>(u_lo, u_hi, boff, bf[gi], sr[4].at(gj, sdt), sr[6].at(gj, sdt), sr[5].at(gj, sdt), sr[7].at(gj, sdt), sxv, au);
+            }
         }
         // partial sums of this warp -> shared memory, then a fixed-order sum over the k splits
         float* rb = red + red_buf * (CW * 32 * 8);
@@ -319,75 +363,78 @@ __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& 
     }
 }
 
+// Copy-issuing side of one work item (all 32 lanes of the issuing warp call this).  `seq` counts the items this
+// CTA has issued since its barriers were initialised.  Returns false if the stage never came free.
+__device__ __forceinline__ bool f1_produce(const FastParams& P, const F1Geom& geo, uint8_t* stages, uint64_t* full_bar,
+                                           uint64_t* empty_bar, uint32_t item, uint32_t seq, uint32_t lane) {
+    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
+    const GroupRef G = group_ref(P, item / geo.tiles_per_group);
+    if (!mbar_wait(&empty_bar[s], ph ^ 1u)) return false;
+    if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
+        if (lane == 0) mbar_arrive(&full_bar[s]);
+        return true;
+    }
+    const uint32_t tile = item % geo.tiles_per_group, row0 = tile * geo.tile_rows;
+    const uint32_t row_bytes = P.d * G.bits / 8, row_stride = row_bytes + ROW_PAD, gpr = geo.groups_per_row;
+    uint8_t* st = stages + s * geo.stage_bytes;
+    const uint32_t scale_block = geo.tile_rows * gpr * 2;
+    if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
+    __syncwarp();
+    for (uint32_t r = lane; r < 2 * geo.tile_rows; r += 32) {
+        const bool up = r >= geo.tile_rows;
+        const uint32_t rr = up ? r - geo.tile_rows : r;
+        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + rr) * row_bytes;
+        bulk_g2s(st + (up ? geo.tile_rows * geo.row_stride_max : 0) + rr * row_stride, src, row_bytes, &full_bar[s]);
+    }
+    if (lane < 4) {
+        const uint32_t o = lane == 0 ? G.off.gate_s : (lane == 1 ? G.off.gate_b : (lane == 2 ? G.off.up_s : G.off.up_b));
+        bulk_g2s(st + 2 * geo.tile_rows * geo.row_stride_max + lane * scale_block, G.blob + o + (size_t)row0 * gpr * 2,
+                 scale_block, &full_bar[s]);
+    }
+    return true;
+}
+
+// Compute side of one work item (every compute warp calls this with the same item and seq).
+__device__ __forceinline__ bool f1_consume(const FastParams& P, const F1Geom& geo, const uint8_t* stages, uint64_t* full_bar,
+                                           uint64_t* empty_bar, uint32_t item, uint32_t seq, uint32_t warp, uint32_t lane,
+                                           float* red, uint32_t& red_buf) {
+    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
+    const GroupRef G = group_ref(P, item / geo.tiles_per_group);
+    if (!mbar_wait(&full_bar[s], ph)) return false;
+    if (G.ok) {
+        const uint8_t* st = stages + s * geo.stage_bytes;
+        if (G.bits == 4) f1_compute<4>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, red, red_buf);
+        else f1_compute<2>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, red, red_buf);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+    return true;
+}
+
 __global__ void __launch_bounds__(F1_THREADS, 1) ffn1_mma_kernel(const FastParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[F1_STAGES], empty_bar[F1_STAGES];
-    __shared__ uint32_t abort_flag;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
     const F1Geom geo = f1_geom(P.d, P.f, max_bits);
-    uint8_t* stages = smem;
     float* red = reinterpret_cast<float*>(smem + F1_STAGES * geo.stage_bytes);
-    float* sx = red + 2 * CW * 32 * 8;
     if (threadIdx.x == 0) {
         for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CW); }
-        abort_flag = 0;
         fence_barrier_init();
     }
     __syncthreads();
-
-    const uint32_t n_groups = *P.n_groups;
-    const uint32_t n_items = n_groups * geo.tiles_per_group;
+    const uint32_t n_items = *P.n_groups * geo.tiles_per_group;
     const uint32_t per_cta = (n_items + gridDim.x - 1) / gridDim.x;
     const uint32_t first = blockIdx.x * per_cta, last = min(first + per_cta, n_items);
-
+    uint32_t seq = 0, red_buf = 0;
+    bool ok = true;
     if (warp == CW) {
-        // ---- copy-issuing warp
-        uint32_t issued = 0;
-        for (uint32_t item = first; item < last; ++item, ++issued) {
-            const uint32_t s = issued % F1_STAGES, ph = (issued / F1_STAGES) & 1u;
-            const GroupRef G = group_ref(P, item / geo.tiles_per_group);
-            if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicOr(P.status, STATUS_MBAR_TIMEOUT); abort_flag = 1; break; }
-            if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
-                if (lane == 0) mbar_arrive(&full_bar[s]);
-                continue;
-            }
-            const uint32_t tile = item % geo.tiles_per_group, row0 = tile * geo.tile_rows;
-            const uint32_t row_bytes = P.d * G.bits / 8, row_stride = row_bytes + ROW_PAD, gpr = geo.groups_per_row;
-            uint8_t* st = stages + s * geo.stage_bytes;
-            const uint32_t scale_block = geo.tile_rows * gpr * 2;
-            if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
-            __syncwarp();
-            for (uint32_t r = lane; r < 2 * geo.tile_rows; r += 32) {
-                const bool up = r >= geo.tile_rows;
-                const uint32_t rr = up ? r - geo.tile_rows : r;
-                const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + rr) * row_bytes;
-                bulk_g2s(st + (up ? geo.tile_rows * geo.row_stride_max : 0) + rr * row_stride, src, row_bytes, &full_bar[s]);
-            }
-            if (lane < 4) {
-                const uint32_t o = lane == 0 ? G.off.gate_s : (lane == 1 ? G.off.gate_b : (lane == 2 ? G.off.up_s : G.off.up_b));
-                bulk_g2s(st + 2 * geo.tile_rows * geo.row_stride_max + lane * scale_block,
-                         G.blob + o + (size_t)row0 * gpr * 2, scale_block, &full_bar[s]);
-            }
-        }
-        return;
+        for (uint32_t item = first; item < last && ok; ++item, ++seq) ok = f1_produce(P, geo, smem, full_bar, empty_bar, item, seq, lane);
+    } else {
+        for (uint32_t item = first; item < last && ok; ++item, ++seq)
+            ok = f1_consume(P, geo, smem, full_bar, empty_bar, item, seq, warp, lane, red, red_buf);
     }
-
-    // ---- compute warps
-    float* sx_w = sx + warp * 64;
-    uint32_t red_buf = 0, done = 0;
-    for (uint32_t item = first; item < last; ++item, ++done) {
-        const uint32_t s = done % F1_STAGES, ph = (done / F1_STAGES) & 1u;
-        const GroupRef G = group_ref(P, item / geo.tiles_per_group);
-        if (!mbar_wait(&full_bar[s], ph)) { atomicOr(P.status, STATUS_MBAR_TIMEOUT); break; }
-        if (G.ok) {
-            const uint8_t* st = stages + s * geo.stage_bytes;
-            if (G.bits == 4) f1_compute<4>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, sx_w, red, red_buf);
-            else f1_compute<2>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, sx_w, red, red_buf);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
-    }
+    if (!ok) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
 }
 
 // ------------------------------------------------------------------------------------------ phase 2 + combine
@@ -401,26 +448,25 @@ constexpr int F2_THREADS = CW * 32;
 
 template <int BITS, int NG>
 __device__ __forceinline__ void f2_compute(const FastParams& P, const GroupRef& G, const uint8_t* st, uint32_t row_stride_max,
-                                           uint32_t lane, float* sx_w, float* part, uint32_t slots) {
+                                           uint32_t lane, float* part, uint32_t slots) {
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t row_stride = P.f * BITS / 8 + ROW_PAD, gpr = P.f / 64;
     const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + 16 * row_stride_max);
-    const uint16_t* ds = sc, *db = sc + 16 * gpr;
     const uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
+    ScaleRow<NG> s_lo, s_hi, b_lo, b_hi;
+    s_lo.load(sc + g * gpr); s_hi.load(sc + (g + 8) * gpr);
+    b_lo.load(sc + 16 * gpr + g * gpr); b_hi.load(sc + 16 * gpr + (g + 8) * gpr);
     for (uint32_t tt = 0; tt < G.pair_count; tt += 8) {
         const uint32_t cols = min(8u, G.pair_count - tt);
         const __half* row_ptr = g < cols ? P.actp + (size_t)(G.pair_start + tt + g) * P.f : nullptr;
         uint32_t bf[NG][8];
-        load_bfrags<NG>(row_ptr, 0, lane, bf, sx_w);
+        load_bfrags<NG>(row_ptr, 0, lane, bf);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int gi = 0; gi < NG; ++gi) {
-            const float2 sxv = *reinterpret_cast<const float2*>(sx_w + gi * 8 + 2 * t);
+        for (int gi = 0; gi < NG; ++gi)
             group_mma<BITS>(st + g * row_stride, st + (g + 8) * row_stride, gi * group_bytes + t * lane_bytes, bf[gi],
-                            widen16(ds[g * gpr + gi], sdt), widen16(db[g * gpr + gi], sdt),
-                            widen16(ds[(g + 8) * gpr + gi], sdt), widen16(db[(g + 8) * gpr + gi], sdt), sxv.x, sxv.y, acc);
-        }
+                            s_lo.at(gi, sdt), b_lo.at(gi, sdt), s_hi.at(gi, sdt), b_hi.at(gi, sdt), group_sum(bf[gi]), acc);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
             const uint32_t n = 2 * t + c;
@@ -431,11 +477,50 @@ __device__ __forceinline__ void f2_compute(const FastParams& P, const GroupRef& 
                 dst[g + 8] = acc[2 + c];
             }
         }
-        __syncwarp();
     }
 }
 
-template <int NG>
+template <int BITS>
+__device__ __forceinline__ void f2_dispatch(const FastParams& P, const GroupRef& G, const uint8_t* st, uint32_t row_stride_max,
+                                            uint32_t lane, float* part, uint32_t slots) {
+    switch (P.f / 64) {
+        case 8: f2_compute<BITS, 8>(P, G, st, row_stride_max, lane, part, slots); break;
+        case 4: f2_compute<BITS, 4>(P, G, st, row_stride_max, lane, part, slots); break;
+        case 2: f2_compute<BITS, 2>(P, G, st, row_stride_max, lane, part, slots); break;
+        default: f2_compute<BITS, 1>(P, G, st, row_stride_max, lane, part, slots); break;
+    }
+}
+
+// Issues the copies of one group's 16 down rows + scales into a warp-private stage (all lanes of the warp call).
+__device__ __forceinline__ void f2_issue(const FastParams& P, uint8_t* st, uint64_t* bar, uint32_t gidx, uint32_t row0,
+                                         uint32_t row_stride_max, uint32_t lane) {
+    const GroupRef G = group_ref(P, gidx);
+    if (!G.ok) { if (lane == 0) mbar_arrive(bar); return; }
+    const uint32_t gpr = P.f / 64;
+    const uint32_t row_bytes = P.f * G.bits / 8, row_stride = row_bytes + ROW_PAD, scale_block = 16 * gpr * 2;
+    fence_proxy_async();
+    if (lane == 0) mbar_expect_tx(bar, 16 * row_bytes + 2 * scale_block);
+    __syncwarp();
+    if (lane < 16) bulk_g2s(st + lane * row_stride, G.blob + G.off.down_w + (size_t)(row0 + lane) * row_bytes, row_bytes, bar);
+    else if (lane < 18)
+        bulk_g2s(st + 16 * row_stride_max + (lane - 16) * scale_block,
+                 G.blob + (lane == 16 ? G.off.down_s : G.off.down_b) + (size_t)row0 * gpr * 2, scale_block, bar);
+}
+
+// Rank-ordered weighted combine of this CTA's 16 columns: residual first, shared expert, then ranks ascending.
+__device__ __forceinline__ void f2_combine(const FastParams& P, const float* part, uint32_t slots, uint32_t row0, bool with_shared) {
+    for (uint32_t o = threadIdx.x; o < P.n_tokens * 16; o += blockDim.x) {
+        const uint32_t tok = o >> 4, r = o & 15;
+        const float* pt = part + (size_t)tok * slots * 16;
+        float acc = 0.0f;
+        if (P.residual) acc = widen16(ld_cg_u16((const uint16_t*)P.residual + (size_t)tok * P.d + row0 + r), P.x_dtype);
+        if (with_shared) acc += pt[P.top_k * 16 + r];
+        for (uint32_t k = 0; k < P.top_k; ++k)
+            acc = fmaf(__half2float(__ushort_as_half(P.route_w[(size_t)tok * P.top_k + k])), pt[k * 16 + r], acc);
+        store_act(P.y, (size_t)tok * P.d + row0 + r, acc, P.x_dtype);
+    }
+}
+
 __global__ void __launch_bounds__(F2_THREADS, 1) ffn2_mma_kernel(const FastParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[CW][F2_STAGES];
@@ -446,8 +531,6 @@ __global__ void __launch_bounds__(F2_THREADS, 1) ffn2_mma_kernel(const FastParam
     const uint32_t slots = P.top_k + 1;
     uint8_t* my_stages = smem + warp * F2_STAGES * stage_bytes;
     float* part = reinterpret_cast<float*>(smem + CW * F2_STAGES * stage_bytes);
-    float* sx = part + (size_t)P.n_tokens * slots * 16;
-    float* sx_w = sx + warp * (NG * 8);
     const uint32_t row0 = blockIdx.x * 16;
 
     if (lane == 0) {
@@ -458,46 +541,25 @@ __global__ void __launch_bounds__(F2_THREADS, 1) ffn2_mma_kernel(const FastParam
     __syncthreads();
 
     const uint32_t n_groups = *P.n_groups;
-    auto issue = [&](uint32_t gidx, uint32_t s) {
-        const GroupRef G = group_ref(P, gidx);
-        if (!G.ok) { if (lane == 0) mbar_arrive(&full_bar[warp][s]); return; }
-        const uint32_t row_bytes = P.f * G.bits / 8, row_stride = row_bytes + ROW_PAD, scale_block = 16 * gpr * 2;
-        uint8_t* st = my_stages + s * stage_bytes;
-        fence_proxy_async();
-        if (lane == 0) mbar_expect_tx(&full_bar[warp][s], 16 * row_bytes + 2 * scale_block);
-        __syncwarp();
-        if (lane < 16) bulk_g2s(st + lane * row_stride, G.blob + G.off.down_w + (size_t)(row0 + lane) * row_bytes, row_bytes, &full_bar[warp][s]);
-        else if (lane < 18) bulk_g2s(st + 16 * row_stride_max + (lane - 16) * scale_block,
-                                     G.blob + (lane == 16 ? G.off.down_s : G.off.down_b) + (size_t)row0 * gpr * 2, scale_block, &full_bar[warp][s]);
-    };
     uint32_t n_mine = 0;
     for (uint32_t gidx = warp; gidx < n_groups; gidx += CW) ++n_mine;
-    for (uint32_t i = 0; i < n_mine && i < (uint32_t)F2_STAGES; ++i) issue(warp + i * CW, i);
+    for (uint32_t i = 0; i < n_mine && i < (uint32_t)F2_STAGES; ++i)
+        f2_issue(P, my_stages + i * stage_bytes, &full_bar[warp][i], warp + i * CW, row0, row_stride_max, lane);
     for (uint32_t i = 0; i < n_mine; ++i) {
         const uint32_t s = i % F2_STAGES, ph = (i / F2_STAGES) & 1u;
-        const uint32_t gidx = warp + i * CW;
-        const GroupRef G = group_ref(P, gidx);
+        const GroupRef G = group_ref(P, warp + i * CW);
         if (!mbar_wait(&full_bar[warp][s], ph)) { atomicOr(P.status, STATUS_MBAR_TIMEOUT); break; }
         if (G.ok) {
             const uint8_t* st = my_stages + s * stage_bytes;
-            if (G.bits == 4) f2_compute<4, NG>(P, G, st, row_stride_max, lane, sx_w, part, slots);
-            else f2_compute<2, NG>(P, G, st, row_stride_max, lane, sx_w, part, slots);
+            if (G.bits == 4) f2_dispatch<4>(P, G, st, row_stride_max, lane, part, slots);
+            else f2_dispatch<2>(P, G, st, row_stride_max, lane, part, slots);
         }
         __syncwarp();
-        if (i + F2_STAGES < n_mine) issue(warp + (i + F2_STAGES) * CW, s);
+        if (i + F2_STAGES < n_mine)
+            f2_issue(P, my_stages + s * stage_bytes, &full_bar[warp][s], warp + (i + F2_STAGES) * CW, row0, row_stride_max, lane);
     }
     __syncthreads();
-    // rank-ordered weighted combine of this CTA's 16 columns
-    const bool with_shared = P.shared_blob != nullptr;
-    for (uint32_t o = threadIdx.x; o < P.n_tokens * 16; o += F2_THREADS) {
-        const uint32_t tok = o >> 4, r = o & 15;
-        const float* pt = part + (size_t)tok * slots * 16;
-        float acc = P.residual ? load_act(P.residual, (size_t)tok * P.d + row0 + r, P.x_dtype) : 0.0f;
-        if (with_shared) acc += pt[P.top_k * 16 + r];
-        for (uint32_t k = 0; k < P.top_k; ++k)
-            acc = fmaf(__half2float(__ushort_as_half(P.route_w[(size_t)tok * P.top_k + k])), pt[k * 16 + r], acc);
-        store_act(P.y, (size_t)tok * P.d + row0 + r, acc, P.x_dtype);
-    }
+    f2_combine(P, part, slots, row0, P.shared_blob != nullptr);
 }
 
 // ------------------------------------------------------------------------------------------ prep: RMSNorm + layouts
@@ -543,11 +605,355 @@ __global__ void prep_kernel(const void* __restrict__ h, int dtype, const __nv_bf
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------ fused stack kernel
+// All layers of a decode step in ONE cooperative launch: RMSNorm, gate GEMV, top-k, sort, phase 1, phase 2 and
+// the weighted combine, with grid-wide barriers between dependent phases.  At batch 1 a layer moves 17 MB, which
+// HBM delivers in under 3 us - less than a kernel launch - so the per-layer launch sequence is latency bound by
+// construction; here the only serial costs left are the barriers and the memory latency behind them.
+//
+// Every wait is bounded: a barrier or mbarrier that does not complete within its limit sets the abort word and
+// the device status, every CTA then falls through its remaining barriers and returns; nothing spins for ever.
+namespace {
+
+constexpr long long GRID_WAIT_CYCLES = 4000000000ll;   // ~2 s at 1.9 GHz
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const void* p) { return __uint_as_float(ld_cg_u32(p)); }
+
+struct MegaShared {
+    uint64_t full1[F1_STAGES], empty1[F1_STAGES], full2[CW][2];
+    uint32_t flag;          // barrier outcome broadcast: 1 = proceed, 0 = abort
+    uint32_t n_groups;
+    float red[32];
+};
+
+// Arrive-and-wait over all CTAs.  `epoch` counts the arrivals this CTA expects to have been made in total.
+__device__ __forceinline__ bool grid_barrier(const MegaParams& M, MegaShared& S, uint32_t& epoch) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        epoch += gridDim.x;
+        __threadfence();
+        atomicAdd(M.bar_counter, 1u);
+        bool ok = true;
+        const long long t0 = clock64();
+        while (ld_acquire_u32(M.bar_counter) < epoch) {
+            if (ld_acquire_u32(M.abort) != 0u) { ok = false; break; }
+            if (clock64() - t0 > GRID_WAIT_CYCLES) {
+                atomicOr(M.status, STATUS_GRID_BARRIER_TIMEOUT);
+                atomicExch(M.abort, 1u);
+                ok = false;
+                break;
+            }
+        }
+        __threadfence();
+        S.flag = ok ? 1u : 0u;
+    }
+    __syncthreads();
+    return S.flag != 0u;
+}
+
+// RMSNorm of one row by the first 256 threads of the CTA, arithmetic and order of rmsnorm_kernel (glue.cu).
+// Writes the row in the activation dtype and in the permuted fp16 layout(s).
+__device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLayer& Ly, MegaShared& S, const void* h,
+                                              uint32_t tok) {
+    const uint32_t d = M.d, tid = threadIdx.x;
+    const size_t row = (size_t)tok * d;
+    float ss = 0.0f;
+    if (tid < 256)
+        for (uint32_t i = tid; i < d; i += 256) {
+            const float v = widen16(ld_cg_u16((const uint16_t*)h + row + i), M.x_dtype);
+            ss = fmaf(v, v, ss);
+        }
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+    if (tid < 256 && (tid & 31) == 0) S.red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid < 32) {
+        float v = tid < 8 ? S.red[tid] : 0.0f;
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        if (tid == 0) S.red[8] = v;
+    }
+    __syncthreads();
+    const float inv = rsqrtf(S.red[8] / (float)d + M.eps);
+    if (tid < 256)
+        for (uint32_t i = tid; i < d; i += 256) {
+            float v = widen16(ld_cg_u16((const uint16_t*)h + row + i), M.x_dtype);
+            const float gw = Ly.norm_w ? __bfloat162float(Ly.norm_w[i]) : 1.0f;
+            v = v * inv * gw;
+            const uint16_t bits = narrow16(v, M.x_dtype);
+            ((uint16_t*)M.xn)[row + i] = bits;
+            v = fminf(fmaxf(widen16(bits, M.x_dtype), -65504.0f), 65504.0f);
+            const __half hv = __float2half_rn(v);
+            M.xp[row + (i & ~15u) + perm_pos(i & 15u, M.bits)] = hv;
+            if (M.xp2) M.xp2[row + (i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = hv;
+        }
+    __syncthreads();
+}
+
+// logits[t, e] for the experts this CTA owns (e = blockIdx.x, + gridDim.x, ...), every token, in the fixed
+// summation order of router_logits_kernel: lane l takes k = l, l+32, ... ascending, then a xor butterfly.
+// `stage` is free shared memory: up to two gate rows as fp32, then one activation row per warp as raw 16-bit.
+constexpr uint32_t MEGA_ROWS_PER_PASS = 2;
+
+__device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5, d = M.d;
+    float* w_rows = reinterpret_cast<float*>(stage);                                   // [2][d]
+    uint16_t* x_row = reinterpret_cast<uint16_t*>(stage + MEGA_ROWS_PER_PASS * d * 4) + warp * d;   // [warps][d]
+    for (uint32_t e0 = blockIdx.x; e0 < M.num_experts; e0 += MEGA_ROWS_PER_PASS * gridDim.x) {
+        __syncthreads();
+        uint32_t ne = 0;
+        for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) {
+            const uint32_t e = e0 + j * gridDim.x;
+            if (e >= M.num_experts) break;
+            ++ne;
+            const uint4* src = reinterpret_cast<const uint4*>(Ly.router_w + (size_t)e * d);
+            for (uint32_t i = threadIdx.x; i < d / 8; i += blockDim.x) {
+                const uint4 q = src[i];
+                float* dst = w_rows + j * d + i * 8;
+                dst[0] = __uint_as_float(q.x << 16); dst[1] = __uint_as_float(q.x & 0xFFFF0000u);
+                dst[2] = __uint_as_float(q.y << 16); dst[3] = __uint_as_float(q.y & 0xFFFF0000u);
+                dst[4] = __uint_as_float(q.z << 16); dst[5] = __uint_as_float(q.z & 0xFFFF0000u);
+                dst[6] = __uint_as_float(q.w << 16); dst[7] = __uint_as_float(q.w & 0xFFFF0000u);
+            }
+        }
+        __syncthreads();
+        for (uint32_t t = warp; t < M.n_tokens; t += warps) {
+            const uint16_t* x = (const uint16_t*)M.xn + (size_t)t * d;
+            __syncwarp();
+            for (uint32_t i = lane; i < d / 8; i += 32) *reinterpret_cast<uint4*>(x_row + i * 8) = ld_cg_u4(x + i * 8);
+            __syncwarp();
+            float acc[MEGA_ROWS_PER_PASS] = {0.0f, 0.0f};
+#pragma unroll 8
+            for (uint32_t i = lane; i < d; i += 32) {
+                const float xv = widen16(x_row[i], M.x_dtype);
+#pragma unroll
+                for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) acc[j] = fmaf(w_rows[j * d + i], xv, acc[j]);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) {
+                float v = acc[j];
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                const uint32_t e = e0 + j * gridDim.x;
+                if (lane == 0 && j < ne) {
+                    if (Ly.logit_bias) v = v + Ly.logit_bias[e];
+                    M.logits[(size_t)t * M.num_experts + e] = v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// Counting sort of the routing table into shared memory, identical order to group.cu / route_small_kernel:
+// every CTA builds the same lists.  idx_s holds the table, run_s is scratch of num_experts entries.
+__device__ __forceinline__ void mega_group(const MegaParams& M, MegaShared& S, const uint32_t* idx_s, const uint16_t* w_s,
+                                           uint32_t* run_s, mfb_pair* sorted_s, mfb_group* groups_s, bool shared) {
+    const uint32_t n_pairs = M.n_tokens * M.top_k, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) run_s[e] = 0;
+    __syncthreads();
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&run_s[idx_s[p]], 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0, ng = 0;
+        for (uint32_t e = 0; e < M.num_experts; ++e) {
+            const uint32_t c = run_s[e];
+            run_s[e] = run;
+            if (c) { groups_s[ng].expert = e; groups_s[ng].pair_start = run; groups_s[ng].pair_count = c; ++ng; }
+            run += c;
+        }
+        if (shared) { groups_s[ng].expert = M.num_experts; groups_s[ng].pair_start = run; groups_s[ng].pair_count = M.n_tokens; ++ng; }
+        S.n_groups = ng;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (uint32_t p0 = 0; p0 < n_pairs; p0 += 32) {
+            const uint32_t p = p0 + lane;
+            const uint32_t e = p < n_pairs ? idx_s[p] : 0xFFFFFFFFu;
+            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, e);
+            const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+            uint32_t pos = 0;
+            if (p < n_pairs) pos = run_s[e] + before;
+            __syncwarp();
+            if (p < n_pairs && before == 0) run_s[e] += __popc(peers);
+            __syncwarp();
+            if (p < n_pairs) {
+                mfb_pair out;
+                out.token = p / M.top_k; out.expert = e; out.rank = p % M.top_k; out.weight_bits = w_s[p];
+                sorted_s[pos] = out;
+            }
+        }
+    } else if (shared) {
+        for (uint32_t t = threadIdx.x - 32; t < M.n_tokens; t += blockDim.x - 32) {
+            mfb_pair out;
+            out.token = t; out.expert = M.num_experts; out.rank = M.top_k; out.weight_bits = 0x3C00u;
+            sorted_s[n_pairs + t] = out;
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaParams M) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ MegaShared S;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool has_shared_cfg = M.shared_bits != 0;
+    const uint32_t max_bits = has_shared_cfg && M.shared_bits > M.bits ? M.shared_bits : M.bits;
+    const F1Geom geo = f1_geom(M.d, M.f, max_bits);
+    const uint32_t slots = M.top_k + 1, n_pairs = M.n_tokens * M.top_k;
+    // ---- shared memory carve-up.  Region A serves phase 1 (two stages) and is reused by phase 2 (per-warp
+    // stages + the per-(token, slot) partial rows); the routing lists and small scratch follow it.
+    uint8_t* region_a = smem;
+    const uint32_t region_a_bytes = F1_STAGES * geo.stage_bytes;
+    float* red = reinterpret_cast<float*>(smem + region_a_bytes);
+    mfb_pair* sorted_s = reinterpret_cast<mfb_pair*>(red + 2 * CW * 32 * 8);
+    mfb_group* groups_s = reinterpret_cast<mfb_group*>(sorted_s + (n_pairs + M.n_tokens));
+    uint32_t* idx_s = reinterpret_cast<uint32_t*>(groups_s + (M.num_experts + 1));
+    uint16_t* w_s = reinterpret_cast<uint16_t*>(idx_s + n_pairs);
+    uint32_t* run_s = reinterpret_cast<uint32_t*>(w_s + ((n_pairs + 1) & ~1u));
+    // phase 2 view of region A
+    const uint32_t row_stride2_max = M.f * max_bits / 8 + ROW_PAD, gpr2 = M.f / 64;
+    const uint32_t stage2_bytes = 16 * row_stride2_max + 2 * 16 * gpr2 * 2;
+    uint8_t* my_stages2 = region_a + warp * 2 * stage2_bytes;
+    float* part = reinterpret_cast<float*>(region_a + CW * 2 * stage2_bytes);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW); }
+        for (int w = 0; w < CW; ++w) for (int s = 0; s < 2; ++s) mbar_init(&S.full2[w][s], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    uint32_t epoch = 0, it1 = 0, it2 = 0;
+    bool alive = true;
+    for (uint32_t l = 0; l < M.n_layers && alive; ++l) {
+        const MegaLayer Ly = M.layers[l];
+        void* h = (uint8_t*)M.hidden + (size_t)l * M.layer_stride * 2;   // 16-bit activations
+        const bool shared = Ly.shared_blob != nullptr;
+
+        uint64_t* trace = M.trace ? M.trace + (size_t)l * 8 : nullptr;
+        auto stamp = [&](int slot) {
+            if (trace && blockIdx.x == 0 && threadIdx.x == 0) {
+                uint64_t t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                trace[slot] = t;
+            }
+        };
+        stamp(0);
+        // ---- phase 0a: RMSNorm, token t by CTA t % grid
+        for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x) mega_norm_row(M, Ly, S, h, t);
+        if (!(alive = grid_barrier(M, S, epoch))) break;
+
+        stamp(1);
+        // ---- phase 0b: gate logits, expert e by CTA e % grid
+        mega_logits(M, Ly, region_a);
+        if (!(alive = grid_barrier(M, S, epoch))) break;
+
+        stamp(2);
+        // ---- phase 0c: selection, token t by warp 0 of CTA t % grid
+        for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x) {
+            float* lg_s = red;   // the row is copied to shared memory with L2-coherent loads first
+            for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) lg_s[e] = ld_cg_f32(M.logits + (size_t)t * M.num_experts + e);
+            __syncthreads();
+            if (warp == 0) {
+                uint32_t e = 0;
+                uint16_t wgt = 0;
+                select_row(lg_s, M.num_experts, M.top_k, M.router_mode, Ly.per_expert_scale, Ly.correction_bias, M.route_scale,
+                           lane, e, wgt);
+                if (lane < M.top_k) {
+                    M.idx[(size_t)t * M.top_k + lane] = e;
+                    M.route_w[(size_t)t * M.top_k + lane] = wgt;
+                }
+            }
+            __syncthreads();
+        }
+        if (!(alive = grid_barrier(M, S, epoch))) break;
+
+        stamp(3);
+        // ---- sort of the routing table, redundantly in every CTA (no barrier needed)
+        for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+            idx_s[p] = ld_cg_u32(M.idx + p);
+            w_s[p] = ld_cg_u16(M.route_w + p);
+        }
+        __syncthreads();
+        mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
+
+        FastParams P;
+        P.pool = Ly.pool; P.slot_stride = Ly.slot_stride; P.slot_of = Ly.slot_of; P.shared_blob = Ly.shared_blob;
+        P.routed_off = Ly.routed_off; P.shared_off = Ly.shared_off;
+        P.d = M.d; P.f = M.f; P.num_experts = M.num_experts; P.top_k = M.top_k; P.bits = M.bits; P.shared_bits = M.shared_bits;
+        P.scale_dtype = M.scale_dtype; P.activation = M.activation; P.limit = M.limit;
+        P.sorted = sorted_s; P.groups = groups_s; P.n_groups = &S.n_groups;
+        P.xp = M.xp; P.xp_shared = M.xp2 ? M.xp2 : M.xp; P.actp = M.actp; P.route_w = w_s;
+        P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
+
+        stamp(4);
+        // ---- phase 1
+        const uint32_t n_groups = S.n_groups;
+        const uint32_t n_items = n_groups * geo.tiles_per_group;
+        const uint32_t per_cta = (n_items + gridDim.x - 1) / gridDim.x;
+        const uint32_t first = blockIdx.x * per_cta, last = min(first + per_cta, n_items);
+        bool bad = false;
+        if (warp == CW) {
+            fence_proxy_async();
+            for (uint32_t item = first; item < last; ++item, ++it1)
+                if (!f1_produce(P, geo, region_a, S.full1, S.empty1, item, it1, lane)) { bad = true; break; }
+        } else {
+            uint32_t red_buf = 0;
+            for (uint32_t item = first; item < last; ++item, ++it1)
+                if (!f1_consume(P, geo, region_a, S.full1, S.empty1, item, it1, warp, lane, red, red_buf)) { bad = true; break; }
+        }
+        if (bad) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+        __syncthreads();   // region A is free again: phase 2 may stage into it before the grid barrier
+
+        // ---- phase 2: issue the first copies now so that they fly during the barrier, compute after it
+        const bool p2_cta = blockIdx.x < M.d / 16;
+        const uint32_t row0 = blockIdx.x * 16;
+        uint32_t n_mine = 0;
+        if (p2_cta && warp < CW) {
+            for (uint32_t gidx = warp; gidx < n_groups; gidx += CW) ++n_mine;
+            for (uint32_t i = 0; i < n_mine && i < 2; ++i)
+                f2_issue(P, my_stages2 + ((it2 + i) & 1u) * stage2_bytes, &S.full2[warp][(it2 + i) & 1u], warp + i * CW, row0,
+                         row_stride2_max, lane);
+            for (uint32_t i = threadIdx.x; i < M.n_tokens * slots * 16; i += CW * 32) part[i] = 0.0f;
+        }
+        stamp(5);
+        if (!(alive = grid_barrier(M, S, epoch))) break;
+        stamp(6);
+
+        if (p2_cta && warp < CW) {
+            for (uint32_t i = 0; i < n_mine; ++i, ++it2) {
+                const uint32_t s = it2 & 1u, ph = (it2 >> 1) & 1u;
+                const GroupRef G = group_ref(P, warp + i * CW);
+                if (!mbar_wait(&S.full2[warp][s], ph)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); break; }
+                if (G.ok) {
+                    const uint8_t* st = my_stages2 + s * stage2_bytes;
+                    if (G.bits == 4) f2_dispatch<4>(P, G, st, row_stride2_max, lane, part, slots);
+                    else f2_dispatch<2>(P, G, st, row_stride2_max, lane, part, slots);
+                }
+                __syncwarp();
+                if (i + 2 < n_mine)
+                    f2_issue(P, my_stages2 + s * stage2_bytes, &S.full2[warp][s], warp + (i + 2) * CW, row0, row_stride2_max, lane);
+            }
+        }
+        __syncthreads();
+        if (p2_cta) f2_combine(P, part, slots, row0, shared);
+        stamp(7);
+        if (!(alive = grid_barrier(M, S, epoch))) break;
+    }
+}
+
+}  // namespace
+
 // ------------------------------------------------------------------------------------------ host side
 bool fast_supported(const mfb_moe_config& c) {
     const uint32_t ks = c.d / 512;
     if (c.d % 512 || !(ks == 1 || ks == 2 || ks == 4 || ks == 8)) return false;
     if (c.f % 64 || c.f > 512) return false;            // phase 2 keeps a whole row's activations in registers
+    const uint32_t ng = c.f / 64;
+    if (!(ng == 1 || ng == 2 || ng == 4 || ng == 8)) return false;
     const uint32_t tile_rows = 16 * (CW / ks);
     if (c.f % tile_rows || c.d % 16) return false;
     if (c.top_k + 1 > 32) return false;
@@ -557,26 +963,36 @@ bool fast_supported(const mfb_moe_config& c) {
 size_t fast_smem1(const mfb_moe_config& c) {
     const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
     const F1Geom g = f1_geom(c.d, c.f, max_bits);
-    return (size_t)F1_STAGES * g.stage_bytes + 2 * CW * 32 * 8 * sizeof(float) + CW * 64 * sizeof(float);
+    return (size_t)F1_STAGES * g.stage_bytes + 2 * CW * 32 * 8 * sizeof(float);
 }
 
 size_t fast_smem2(const mfb_moe_config& c, uint32_t n_tokens) {
     const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
     const uint32_t row_stride_max = c.f * max_bits / 8 + ROW_PAD, gpr = c.f / 64;
     const size_t stage_bytes = 16 * row_stride_max + 2 * 16 * gpr * 2;
-    return (size_t)CW * F2_STAGES * stage_bytes + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float) + CW * (c.f / 64) * 8 * sizeof(float);
+    return (size_t)CW * F2_STAGES * stage_bytes + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
 }
 
-template <int NG>
-static cudaError_t launch_f2(cudaStream_t s, const FastParams& P, size_t smem) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(ffn2_mma_kernel<NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
-    ffn2_mma_kernel<NG><<<P.d / 16, F2_THREADS, smem, s>>>(P);
-    return cudaGetLastError();
+size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
+    const size_t pairs = (size_t)n_tokens * c.top_k;
+    const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
+                         ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4;
+    const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
+    const uint32_t row_stride_max = c.f * max_bits / 8 + ROW_PAD, gpr = c.f / 64;
+    const size_t stage2 = 16 * row_stride_max + 2 * 16 * gpr * 2;
+    const size_t phase2 = (size_t)CW * 2 * stage2 + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
+    const size_t region_a = fast_smem1(c) - 2 * CW * 32 * 8 * sizeof(float);
+    if (phase2 > region_a || (size_t)c.d * 26 > region_a) return (size_t)1 << 30;   // does not fit: caller falls back
+    return fast_smem1(c) + lists + 64;
+}
+
+// One-time opt-in to large dynamic shared memory for the fast kernels (called when a handle is created, so that no
+// attribute call happens while a caller captures a CUDA graph).
+cudaError_t fast_init() {
+    cudaError_t e = cudaFuncSetAttribute(ffn1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(ffn2_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    return e;
 }
 
 cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __nv_bfloat16* w, uint32_t n_tokens, uint32_t d,
@@ -588,12 +1004,6 @@ cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __n
 }
 
 cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(ffn1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
     const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
     const F1Geom g = f1_geom(c.d, c.f, max_bits);
     const uint32_t max_items = max_groups * g.tiles_per_group;
@@ -601,15 +1011,19 @@ cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_c
     ffn1_mma_kernel<<<grid, F1_THREADS, fast_smem1(c), s>>>(P);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const size_t smem2 = fast_smem2(c, P.n_tokens);
-    switch (c.f / 64) {
-        case 1: e = launch_f2<1>(s, P, smem2); break;
-        case 2: e = launch_f2<2>(s, P, smem2); break;
-        case 4: e = launch_f2<4>(s, P, smem2); break;
-        case 8: e = launch_f2<8>(s, P, smem2); break;
-        default: return cudaErrorInvalidValue;
-    }
+    ffn2_mma_kernel<<<P.d / 16, F2_THREADS, fast_smem2(c, P.n_tokens), s>>>(P);
     count_launches(2);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe_config& c, int sm_count) {
+    cudaError_t e = cudaMemsetAsync(M.bar_counter, 0, 2 * sizeof(uint32_t), s);   // barrier counter and abort word are adjacent
+    if (e != cudaSuccess) return e;
+    MegaParams copy = M;
+    void* args[] = {&copy};
+    e = cudaLaunchCooperativeKernel((const void*)stack_mega_kernel, dim3((unsigned)sm_count), dim3(F1_THREADS), args,
+                                    fast_smem_stack(c, M.n_tokens), s);
+    count_launches(1);
     return e;
 }
 

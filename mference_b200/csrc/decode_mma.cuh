@@ -27,6 +27,42 @@ struct FastParams {
     uint32_t* status;
 };
 
+// Per-layer weights as the fused stack kernel reads them (device array, one entry per layer).
+struct MegaLayer {
+    const __nv_bfloat16* router_w;
+    const float* logit_bias;
+    const __nv_bfloat16* per_expert_scale;
+    const float* correction_bias;
+    const __nv_bfloat16* norm_w;
+    const uint8_t* pool;
+    uint64_t slot_stride;
+    const int16_t* slot_of;
+    const uint8_t* shared_blob;
+    mfb_expert_offsets routed_off, shared_off;
+};
+
+struct MegaParams {
+    const MegaLayer* layers;
+    uint32_t n_layers;
+    uint32_t d, f, num_experts, top_k, bits, shared_bits, scale_dtype, activation;
+    int router_mode, x_dtype;
+    float limit, route_scale, eps;
+    void* hidden;             // [n_tokens, d] (layer_stride == 0: the residual stream is carried through the layers)
+    uint64_t layer_stride;    // elements between the rows of consecutive layers, or 0
+    uint32_t n_tokens;
+    void* xn;                 // scratch, all device memory owned by the handle
+    __half* xp;
+    __half* xp2;
+    float* logits;
+    uint32_t* idx;
+    uint16_t* route_w;
+    __half* actp;
+    uint32_t* bar_counter;    // [2]: arrivals, abort word (zeroed before every launch)
+    uint32_t* abort;
+    uint32_t* status;
+    uint64_t* trace;          // optional [n_layers][8] global-timer stamps of the phase boundaries (CTA 0)
+};
+
 constexpr uint32_t FAST_MAX_TOKENS = 64;   // phase 2 keeps (token, slot) x 16 partial rows in shared memory
 
 __host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits);
@@ -36,6 +72,10 @@ size_t fast_smem2(const mfb_moe_config& c, uint32_t n_tokens);
 cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __nv_bfloat16* w, uint32_t n_tokens, uint32_t d,
                              float eps, bool do_norm, void* xn, __half* xp, uint32_t bits, __half* xp2, uint32_t bits2);
 cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups);
+size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens);
+cudaError_t fast_init();
+// All layers of a decode step in one cooperative launch (norm, router, sort, both FFN phases, combine).
+cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe_config& c, int sm_count);
 // select + sort of a small batch in one CTA (router.cu)
 cudaError_t launch_route_small(cudaStream_t s, const float* logits, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k,
                                int mode, const __nv_bfloat16* per_expert_scale, const float* correction_bias,

@@ -188,6 +188,11 @@ class MoE:
     def encode_stack(self, stack, hidden):
         L.check(self.lib.mfb_moe_stack(self.handle, _stream(), stack, len(stack), _ptr(hidden), hidden.shape[0]))
 
+    def encode_stack_rows(self, stack, rows):
+        """rows: [n_layers, n_tokens, d]; layer l transforms rows[l] in place, layers run one after the other."""
+        L.check(self.lib.mfb_moe_stack_rows(self.handle, _stream(), stack, len(stack), _ptr(rows), rows.stride(0),
+                                            rows.shape[1]))
+
     # ---- prefill -----------------------------------------------------------------------------------------
     def encode_group(self, indices, routing_weights):
         """Device-side PrefillMoEGrouping: returns (sorted_pairs[int32 P,4], offsets, counts, groups[int32 E,3], n_groups)."""
@@ -228,6 +233,10 @@ class MoE:
     def set_generic(self, on: bool):
         """Route every call through the generic kernels instead of the shape-specialised fast ones."""
         L.check(self.lib.mfb_moe_set_generic(self.handle, 1 if on else 0))
+
+    def set_trace(self, stamps):
+        """Attach (or detach with None) a uint64 [n_layers, 8] CUDA tensor for per-phase global-timer stamps."""
+        L.check(self.lib.mfb_moe_set_trace(self.handle, _ptr(stamps)))
 
     def device_status(self) -> int:
         st = C.c_uint32()

@@ -238,3 +238,35 @@ def test_fast_path_agrees_with_generic_path(T):
     assert np.isfinite(a).all()
     # both sit within the tolerance of the oracle; against each other they differ by output rounding at most
     assert O.rel_l2(a, b) <= TOL_REL_L2
+
+
+@pytest.mark.parametrize("T", [1, 5, 64])
+def test_fused_stack_kernel_equals_layer_by_layer(T):
+    # one cooperative launch for all layers against the per-layer launch sequence: bit for bit
+    import torch
+    from mference_b200.moe import MoE, synth_layer, synth_normal
+    from mference_b200 import DT_BF16
+    d, f, E, K, NL = 2048, 512, 32, 8, 5
+    layers = [synth_layer(0xB2000001, l, d, f, E) for l in range(NL)]
+    moe = MoE(d, f, E, K, max_tokens=T)
+    stack = moe.make_stack(layers)
+    h0 = synth_normal(0xB2000001, "x", T * d, dtype=DT_BF16).view(T, d)
+    a = h0.clone()
+    moe.encode_stack(stack, a)
+    b = h0.clone()
+    for lw in layers:
+        nxt = torch.empty_like(b)
+        moe.encode_layer(lw, b, nxt)
+        b = nxt
+    assert moe.device_status() == 0
+    assert torch.isfinite(a.float()).all()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # separate row blocks per layer, layers in order
+    rows = synth_normal(0xB2000001, "rows", NL * T * d, dtype=DT_BF16).view(NL, T, d)
+    c = rows.clone()
+    moe.encode_stack_rows(stack, c)
+    for l, lw in enumerate(layers):
+        ref = torch.empty_like(rows[l])
+        moe.encode_layer(lw, rows[l], ref)
+        assert torch.equal(c[l].view(torch.int16), ref.view(torch.int16)), l
+    assert moe.device_status() == 0
