@@ -83,7 +83,7 @@ uint32_t all_slots(const mfb_moe* m) { return (1u << m->cfg.top_k) - 1u; }
 
 bool use_fast(const mfb_moe* m, uint32_t n_tokens) {
     return m->a.xp != nullptr && n_tokens <= FAST_MAX_TOKENS && (uint64_t)n_tokens * m->cfg.top_k <= 1024 &&
-           !m->force_generic && fast_smem2(m->cfg, n_tokens) <= 226 * 1024 && fast_smem1(m->cfg) <= 226 * 1024;
+           !m->force_generic && fast_smem2(m->cfg, n_tokens) <= FAST_SMEM_LIMIT && fast_smem1(m->cfg) <= FAST_SMEM_LIMIT;
 }
 
 FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens, const uint16_t* route_w,
@@ -96,7 +96,7 @@ FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens
     P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.top_k = c.top_k; P.bits = c.bits; P.shared_bits = c.shared_bits;
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
     P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
-    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.actp = a.actp; P.route_w = route_w;
+    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.actp = a.actp; P.route_w = route_w;
     P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
     return P;
 }
@@ -431,7 +431,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
     if (n_layers == 0 || n_tokens == 0) return MFB_OK;
     const mfb_moe_config& c = moe->cfg;
     cudaStream_t s = (cudaStream_t)stream;
-    if (use_fast(moe, n_tokens) && moe->coop && fast_smem_stack(c, n_tokens) <= 226 * 1024) {
+    if (use_fast(moe, n_tokens) && moe->coop && fast_smem_stack(c, n_tokens) <= FAST_SMEM_LIMIT) {
         for (uint32_t l = 0; l < n_layers; ++l) {
             rc = check_weights(moe, &layers[l], true);
             if (rc) return rc;

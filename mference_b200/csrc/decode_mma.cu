@@ -1,5 +1,6 @@
 // Decode-time expert FFN, fast path: packed rows staged into shared memory by bulk async copies (TMA unit),
-// unpacked in registers straight into tensor-core fragments, fp32 accumulation.
+// unpacked in registers straight into tensor-core fragments, fp32 accumulation; and the fused stack kernel that
+// runs every layer of a decode step in one cooperative launch.
 //
 // Why tensor-core fragments for a GEMV: at 4 bits per weight B200's HBM delivers ~13 T codes/s while the CUDA
 // cores issue ~36 T lane-instructions/s, i.e. fewer than three instructions per code for everything (unpack,
@@ -13,7 +14,8 @@
 //
 // Arithmetic is the reference's factored form (Sources/Mference/Metal/MoE/moe.metal:349-529, 902-1062):
 // per 64-element group  acc += scale * sum(code * x) + bias * sum(x), fp32; sum(code * x) is produced by four
-// k16 MMAs on exact small integers (codes) times fp16 activations with fp32 accumulation.
+// k16 MMAs on exact small integers (codes) times fp16 activations with fp32 accumulation, sum(x) by four MMAs
+// against an all-ones fragment.
 //
 // The K dimension of an MMA may be permuted freely as long as both operands agree, so packed rows are consumed
 // as they lie in memory: lane (g, t) of a warp takes bytes [8t, 8t+8) of each 32-byte group of rows g and g+8
@@ -27,11 +29,16 @@ namespace mfb {
 
 namespace {
 
-constexpr int CW = 8;                       // compute warps per CTA
-constexpr int F1_THREADS = (CW + 1) * 32;   // + one copy-issuing warp
+constexpr int CW = 16;                      // compute warps per CTA
+constexpr int FAST_THREADS = (CW + 1) * 32; // + one copy-issuing warp
+constexpr int KS = 8;                       // k splits of a phase-1 row tile
+constexpr int RT = CW / KS;                 // 16-row tiles per phase-1 stage
 constexpr int F1_STAGES = 2;
-constexpr uint32_t ROW_PAD = 32;            // bytes added to each staged row: keeps 8-byte fragment loads conflict free
-constexpr uint32_t WAIT_LIMIT = 1u << 24;   // bounded spin on mbarriers
+constexpr int F2_SLOTS = 10;                // ring depth of phase 2 (one slot = one (group, token tile))
+constexpr uint32_t ROW_PAD = 32;            // bytes added to each staged weight row: 8-byte fragment loads stay conflict free
+constexpr uint32_t ACT_PAD = 16;            // bytes added to each staged activation row: 16-byte fragment loads likewise
+constexpr long long MBAR_WAIT_CYCLES = 400000000ll;   // bounded spin on mbarriers: ~0.2 s at 1.9 GHz
+constexpr uint32_t MAX_GROUPS = MFB_MAX_EXPERTS + 1;
 
 // ------------------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -48,7 +55,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Bounded wait: returns false when the limit runs out (the caller records it and unwinds).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    const long long t0 = clock64();
+    for (;;) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -56,26 +64,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
+        if (clock64() - t0 > MBAR_WAIT_CYCLES) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void fence_barrier_init() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -86,6 +90,29 @@ __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t r;
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
+}
+// Loads that bypass L1: for buffers other CTAs write during the same launch (fused stack kernel) a line left in
+// this SM's L1 by an earlier layer would be stale.  volatile keeps them from being merged across layers.
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint16_t ld_cg_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const void* p) { return __uint_as_float(ld_cg_u32(p)); }
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 // ------------------------------------------------------------------------------------------ unpacking
@@ -100,13 +127,13 @@ template <>
 struct Unpack<4> {
     static constexpr int WORDS = 2;   // 32-bit words per lane per row per 64-element group
     __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t (&p)[8]) {
-        constexpr uint32_t MAGIC = 0x64006400u, K1024 = 0x64006400u, SIXTEENTH = 0x2C002C00u, M64 = 0xD400D400u;
+        constexpr uint32_t MAGIC = 0x64006400u, SIXTEENTH = 0x2C002C00u, M64 = 0xD400D400u;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t lo = w[i], hi = w[i] >> 8;
-            p[4 * i + 0] = h2_sub((lo & 0x000F000Fu) | MAGIC, K1024);
+            p[4 * i + 0] = h2_sub((lo & 0x000F000Fu) | MAGIC, MAGIC);
             p[4 * i + 1] = h2_fma((lo & 0x00F000F0u) | MAGIC, SIXTEENTH, M64);
-            p[4 * i + 2] = h2_sub((hi & 0x000F000Fu) | MAGIC, K1024);
+            p[4 * i + 2] = h2_sub((hi & 0x000F000Fu) | MAGIC, MAGIC);
             p[4 * i + 3] = h2_fma((hi & 0x00F000F0u) | MAGIC, SIXTEENTH, M64);
         }
     }
@@ -150,24 +177,6 @@ __host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits) {
 
 namespace {
 
-// Loads that bypass L1: for buffers other CTAs write during the same launch (fused stack kernel) a line left in
-// this SM's L1 by an earlier layer would be stale.
-__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint16_t ld_cg_u16(const void* p) {
-    uint16_t v;
-    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
-    uint32_t v;
-    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-
 struct GroupRef {
     const uint8_t* blob;
     mfb_expert_offsets off;
@@ -194,24 +203,6 @@ __device__ __forceinline__ GroupRef group_ref(const FastParams& P, uint32_t g) {
         v.off = P.routed_off; v.bits = P.bits;
     }
     return v;
-}
-
-// B fragments: activations of token column g of the tile for NG consecutive 64-element groups starting at k0.
-template <int NG>
-__device__ __forceinline__ void load_bfrags(const __half* row_ptr /* nullptr: column unused */, uint32_t k0, uint32_t lane,
-                                            uint32_t (&bf)[NG][8]) {
-    const uint32_t t = lane & 3;
-#pragma unroll
-    for (int gi = 0; gi < NG; ++gi) {
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-        if (row_ptr) {
-            const __half* src = row_ptr + k0 + gi * 64 + t * 16;
-            lo = ld_cg_u4(src);
-            hi = ld_cg_u4(src + 8);
-        }
-        bf[gi][0] = lo.x; bf[gi][1] = lo.y; bf[gi][2] = lo.z; bf[gi][3] = lo.w;
-        bf[gi][4] = hi.x; bf[gi][5] = hi.y; bf[gi][6] = hi.z; bf[gi][7] = hi.w;
-    }
 }
 
 // sum(x) over one 64-element group for this lane's two token columns (2t, 2t+1): four MMAs against an all-ones
@@ -251,15 +242,14 @@ __device__ __forceinline__ void group_mma(const uint8_t* row_lo, const uint8_t* 
     acc[3] = fmaf(s_hi, dsum[3], acc[3]); acc[3] = fmaf(b_hi, sx.y, acc[3]);
 }
 
-// NG consecutive 16-bit scales (or biases) of one row with the widest load that fits; element i afterwards by
-// scale_at.
-template <int NG>
+// N consecutive 16-bit scales (or biases) of one row with the widest load that fits.
+template <int N>
 struct ScaleRow {
-    uint32_t w[(NG + 1) / 2];
+    uint32_t w[(N + 1) / 2];
     __device__ __forceinline__ void load(const uint16_t* p) {
-        if (NG == 8) { const uint4 v = *reinterpret_cast<const uint4*>(p); w[0] = v.x; w[(NG > 2) ? 1 : 0] = v.y; w[(NG > 4) ? 2 : 0] = v.z; w[(NG > 6) ? 3 : 0] = v.w; }
-        else if (NG == 4) { const uint2 v = *reinterpret_cast<const uint2*>(p); w[0] = v.x; w[(NG > 2) ? 1 : 0] = v.y; }
-        else if (NG == 2) w[0] = *reinterpret_cast<const uint32_t*>(p);
+        if (N == 8) { const uint4 v = *reinterpret_cast<const uint4*>(p); w[0] = v.x; w[(N > 2) ? 1 : 0] = v.y; w[(N > 4) ? 2 : 0] = v.z; w[(N > 6) ? 3 : 0] = v.w; }
+        else if (N == 4) { const uint2 v = *reinterpret_cast<const uint2*>(p); w[0] = v.x; w[(N > 2) ? 1 : 0] = v.y; }
+        else if (N == 2) w[0] = *reinterpret_cast<const uint32_t*>(p);
         else w[0] = *p;
     }
     __device__ __forceinline__ float at(int i, int dtype) const {
@@ -268,243 +258,350 @@ struct ScaleRow {
     }
 };
 
+// ------------------------------------------------------------------------------------------ work lists
+// A unit of work is one (group, token tile of up to 8 rows[, 32-row tile of gate/up]).  Exclusive prefix sums of
+// the units of each group, by one warp: pref1[g] counts phase-1 units, pref2[g] phase-2 units.
+__device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32_t n_groups, uint32_t tiles_per_group,
+                                                 uint32_t* pref1, uint32_t* pref2, uint32_t lane) {
+    const uint32_t per = (n_groups + 31) / 32, g0 = lane * per;
+    uint32_t local = 0;
+    for (uint32_t j = 0; j < per; ++j)
+        if (g0 + j < n_groups) local += (groups[g0 + j].pair_count + 7) / 8;
+    uint32_t incl = local;
+    for (uint32_t off = 1; off < 32; off <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (lane >= off) incl += n;
+    }
+    uint32_t run = incl - local;
+    for (uint32_t j = 0; j < per; ++j)
+        if (g0 + j < n_groups) {
+            pref2[g0 + j] = run;
+            pref1[g0 + j] = run * tiles_per_group;
+            run += (groups[g0 + j].pair_count + 7) / 8;
+        }
+    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+    if (lane == 0) { pref2[n_groups] = total; pref1[n_groups] = total * tiles_per_group; }
+    __syncwarp();
+}
+
+// Advances `g` until unit u lies in group g (units are visited in increasing order).
+__device__ __forceinline__ void seek_group(const uint32_t* pref, uint32_t n_groups, uint32_t u, uint32_t& g) {
+    while (g + 1 < n_groups && pref[g + 1] <= u) ++g;
+}
+
 // ------------------------------------------------------------------------------------------ phase 1
-// Work item = (group, tile of TILE_ROWS rows of gate and up).  Warp w of the 8 compute warps owns k range
-// [ks*512, ks*512+512) (ks = w % KS) of row tile rt = w / KS; partial sums of the KS warps of a row tile meet in
-// shared memory.  Warp 8 issues the bulk copies: one per row (padded destination rows), one per scale block.
+// Stage = 32 rows of gate and 32 rows of up of one expert (+ their scales and biases).  Warp w of the 16 compute
+// warps owns k range [ks*d/8, (ks+1)*d/8) (ks = w % 8) of row tile rt = w / 8; the partial sums of the eight k
+// splits meet in shared memory in a fixed order.  The 17th warp issues the bulk copies: one per row (padded
+// destination rows), one per scale block.
 struct F1Geom {
-    uint32_t ks_count, rt_count, tile_rows, tiles_per_group, row_stride_max, stage_bytes, groups_per_row;
+    uint32_t tile_rows, tiles_per_group, row_stride_max, stage_bytes, groups_per_row, k_per_warp;
 };
 
 __host__ __device__ inline F1Geom f1_geom(uint32_t d, uint32_t f, uint32_t max_bits) {
     F1Geom g;
-    g.ks_count = d / 512;
-    g.rt_count = CW / g.ks_count;
-    g.tile_rows = 16 * g.rt_count;
+    g.tile_rows = 16 * RT;
     g.tiles_per_group = f / g.tile_rows;
     g.row_stride_max = d * max_bits / 8 + ROW_PAD;
     g.groups_per_row = d / 64;
+    g.k_per_warp = d / KS;
     g.stage_bytes = 2 * g.tile_rows * g.row_stride_max + 4 * g.tile_rows * g.groups_per_row * 2;
     return g;
 }
 
-template <int BITS>
-__device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& G, const F1Geom& geo, const uint8_t* stage,
-                                           uint32_t tile, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
+struct Phase1Ctx {
+    uint8_t* stages;
+    uint64_t* full;     // [F1_STAGES]
+    uint64_t* empty;    // [F1_STAGES]
+    float* red;         // [2][CW*32*8]
+    const uint32_t* pref1;
+};
+
+// Copy-issuing side of one unit (all 32 lanes of the issuing warp call this).
+__device__ __forceinline__ bool f1_produce(const FastParams& P, const F1Geom& geo, const Phase1Ctx& C, const GroupRef& G,
+                                           uint32_t tile, uint32_t seq, uint32_t lane) {
+    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
+    if (!mbar_wait(&C.empty[s], ph ^ 1u)) return false;
+    if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
+        if (lane == 0) mbar_arrive(&C.full[s]);
+        return true;
+    }
+    const uint32_t row0 = tile * geo.tile_rows;
+    const uint32_t row_bytes = P.d * G.bits / 8, row_stride = row_bytes + ROW_PAD, gpr = geo.groups_per_row;
+    uint8_t* st = C.stages + s * geo.stage_bytes;
+    const uint32_t scale_block = geo.tile_rows * gpr * 2;
+    if (lane == 0) mbar_expect_tx(&C.full[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
+    __syncwarp();
+    for (uint32_t r = lane; r < 2 * geo.tile_rows; r += 32) {
+        const bool up = r >= geo.tile_rows;
+        const uint32_t rr = up ? r - geo.tile_rows : r;
+        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + rr) * row_bytes;
+        bulk_g2s(st + (up ? geo.tile_rows * geo.row_stride_max : 0) + rr * row_stride, src, row_bytes, &C.full[s]);
+    }
+    if (lane < 4) {
+        const uint32_t o = lane == 0 ? G.off.gate_s : (lane == 1 ? G.off.gate_b : (lane == 2 ? G.off.up_s : G.off.up_b));
+        bulk_g2s(st + 2 * geo.tile_rows * geo.row_stride_max + lane * scale_block, G.blob + o + (size_t)row0 * gpr * 2,
+                 scale_block, &C.full[s]);
+    }
+    return true;
+}
+
+// B fragments of this warp's k range for token column g of a token tile (registers, loaded from L2 or, in the
+// single-token mode of the fused kernel, from shared memory).
+template <int NGW>
+__device__ __forceinline__ void f1_load_x(const FastParams& P, const GroupRef& G, uint32_t tt, uint32_t k0, uint32_t lane,
+                                          uint32_t (&bf)[NGW][8]) {
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t ks = warp % geo.ks_count, rt = warp / geo.ks_count;
-    const uint32_t row_bytes = P.d * BITS / 8, row_stride = row_bytes + ROW_PAD;
+    const uint32_t cols = min(8u, G.pair_count - tt * 8);
+    const __half* xsrc = (G.shared && P.shared_bits != P.bits) ? P.xp_shared : P.xp;
+    const __half* row = nullptr;
+    if (g < cols) row = xsrc + (size_t)P.sorted[G.pair_start + tt * 8 + g].token * P.d + k0 + t * 16;
+#pragma unroll
+    for (int gi = 0; gi < NGW; ++gi) {
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        if (row) {
+            if (P.x_in_smem) { lo = *reinterpret_cast<const uint4*>(row + gi * 64); hi = *reinterpret_cast<const uint4*>(row + gi * 64 + 8); }
+            else { lo = ld_cg_u4(row + gi * 64); hi = ld_cg_u4(row + gi * 64 + 8); }
+        }
+        bf[gi][0] = lo.x; bf[gi][1] = lo.y; bf[gi][2] = lo.z; bf[gi][3] = lo.w;
+        bf[gi][4] = hi.x; bf[gi][5] = hi.y; bf[gi][6] = hi.z; bf[gi][7] = hi.w;
+    }
+}
+
+template <int BITS, int NGW>
+__device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& G, const F1Geom& geo, const uint8_t* stage,
+                                           uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], uint32_t warp,
+                                           uint32_t lane, float* red, uint32_t& red_buf) {
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t ks = warp % KS, rt = warp / KS;
+    const uint32_t row_stride = P.d * BITS / 8 + ROW_PAD;
     const uint32_t gpr = geo.groups_per_row;
     const uint8_t* gate_rows = stage;
     const uint8_t* up_rows = stage + geo.tile_rows * geo.row_stride_max;
     const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + 2 * geo.tile_rows * geo.row_stride_max);
     const uint32_t blk = geo.tile_rows * gpr;
     const uint32_t r_lo = rt * 16 + g, r_hi = r_lo + 8;
-    const uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
-    const __half* xsrc = (G.shared && P.shared_bits != P.bits) ? P.xp_shared : P.xp;
+    constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
     const uint8_t* g_lo = gate_rows + r_lo * row_stride, *g_hi = gate_rows + r_hi * row_stride;
     const uint8_t* u_lo = up_rows + r_lo * row_stride, *u_hi = up_rows + r_hi * row_stride;
+    const uint32_t cols = min(8u, G.pair_count - tt * 8);
 
-    for (uint32_t tt = 0; tt < G.pair_count; tt += 8) {
-        const uint32_t cols = min(8u, G.pair_count - tt);
-        const __half* row_ptr = nullptr;
-        if (g < cols) row_ptr = xsrc + (size_t)P.sorted[G.pair_start + tt + g].token * P.d;
-        uint32_t bf[8][8];
-        load_bfrags<8>(row_ptr, ks * 512, lane, bf);
-        float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
+    float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
+    // scales and biases of this warp's NGW groups, rows r_lo / r_hi of gate_s, gate_b, up_s, up_b
+    ScaleRow<NGW> sr[8];
 #pragma unroll
-        for (int gp = 0; gp < 4; ++gp) {
-            // scales and biases of two consecutive groups, rows r_lo / r_hi of gate_s, gate_b, up_s, up_b
-            ScaleRow<2> sr[8];
+    for (int m = 0; m < 4; ++m) {
+        sr[2 * m].load(sc + m * blk + r_lo * gpr + ks * NGW);
+        sr[2 * m + 1].load(sc + m * blk + r_hi * gpr + ks * NGW);
+    }
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                sr[2 * m].load(sc + m * blk + r_lo * gpr + ks * 8 + gp * 2);
-                sr[2 * m + 1].load(sc + m * blk + r_hi * gpr + ks * 8 + gp * 2);
-            }
+    for (int gi = 0; gi < NGW; ++gi) {
+        const uint32_t boff = (ks * NGW + gi) * group_bytes + t * lane_bytes;
+        const float2 sxv = group_sum(bf[gi]);
+        group_mma<BITS>(g_lo, g_hi, boff, bf[gi], sr[0].at(gi, sdt), sr[2].at(gi, sdt), sr[1].at(gi, sdt), sr[3].at(gi, sdt), sxv, ag);
+        group_mma<BITS>(u_lo, u_hi, boff, bf[gi], sr[4].at(gi, sdt), sr[6].at(gi, sdt), sr[5].at(gi, sdt), sr[7].at(gi, sdt), sxv, au);
+    }
+    // partial sums of this warp -> shared memory, then a fixed-order sum over the k splits
+    float* rb = red + red_buf * (CW * 32 * 8);
+    float4* dst = reinterpret_cast<float4*>(rb + ((ks * RT + rt) * 32 + lane) * 8);
+    dst[0] = make_float4(ag[0], ag[1], ag[2], ag[3]);
+    dst[1] = make_float4(au[0], au[1], au[2], au[3]);
+    named_barrier(1, CW * 32);
+    const uint32_t o = warp * 32 + lane;
+    if (o < RT * 128) {
+        const uint32_t ort = o >> 7, row = (o & 127) >> 3, n = o & 7;
+        const uint32_t src_lane = (row & 7) * 4 + (n >> 1), reg = (row >> 3) * 2 + (n & 1);
+        float gsum = 0.0f, usum = 0.0f;
 #pragma unroll
-            for (int gj = 0; gj < 2; ++gj) {
-                const int gi = gp * 2 + gj;
-                const uint32_t boff = (ks * 8 + gi) * group_bytes + t * lane_bytes;
-                const float2 sxv = group_sum(bf[gi]);
-                group_mma<BITS>(g_lo, g_hi, boff, bf[gi], sr[0].at(gj, sdt), sr[2].at(gj, sdt), sr[1].at(gj, sdt), sr[3].at(gj, sdt), sxv, ag);
-                group_mma<BITS>(u_lo, u_hi, boff, bf[gi], sr[4].at(gj, sdt), sr[6].at(gj, sdt), sr[5].at(gj, sdt), sr[7].at(gj, sdt), sxv, au);
-            }
+        for (uint32_t k = 0; k < KS; ++k) {
+            const float* src = rb + ((k * RT + ort) * 32 + src_lane) * 8;
+            gsum += src[reg];
+            usum += src[4 + reg];
         }
-        // partial sums of this warp -> shared memory, then a fixed-order sum over the k splits
-        float* rb = red + red_buf * (CW * 32 * 8);
-        float4* dst = reinterpret_cast<float4*>(rb + ((ks * geo.rt_count + rt) * 32 + lane) * 8);
-        dst[0] = make_float4(ag[0], ag[1], ag[2], ag[3]);
-        dst[1] = make_float4(au[0], au[1], au[2], au[3]);
-        named_barrier(1, CW * 32);
-        const uint32_t tid = warp * 32 + lane;
-        for (uint32_t o = tid; o < geo.rt_count * 128; o += CW * 32) {
-            const uint32_t ort = o >> 7, row = (o & 127) >> 3, n = o & 7;
-            const uint32_t src_lane = (row & 7) * 4 + (n >> 1), reg = (row >> 3) * 2 + (n & 1);
-            float gsum = 0.0f, usum = 0.0f;
-            for (uint32_t k = 0; k < geo.ks_count; ++k) {
-                const float* src = rb + ((k * geo.rt_count + ort) * 32 + src_lane) * 8;
-                gsum += src[reg];
-                usum += src[4 + reg];
+        if (n < cols) {
+            if (!G.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+                gsum = fminf(gsum, P.limit);
+                usum = fminf(fmaxf(usum, -P.limit), P.limit);
             }
-            if (n < cols) {
-                if (!G.shared && P.limit > 0.0f) {
-                    gsum = fminf(gsum, P.limit);
-                    usum = fminf(fmaxf(usum, -P.limit), P.limit);
-                }
-                float a = hidden_act(gsum, (int)P.activation) * usum;
-                a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                const uint32_t r = tile * geo.tile_rows + ort * 16 + row;
-                const uint32_t pos = (r & ~15u) + perm_pos(r & 15u, G.bits);
-                P.actp[(size_t)(G.pair_start + tt + n) * P.f + pos] = __float2half_rn(a);
-            }
+            float a = hidden_act(gsum, (int)P.activation) * usum;
+            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+            const uint32_t r = tile * geo.tile_rows + ort * 16 + row;
+            const uint32_t pos = (r & ~15u) + perm_pos(r & 15u, G.bits);
+            P.actp[(size_t)(G.pair_start + tt * 8 + n) * P.f + pos] = __float2half_rn(a);
         }
-        red_buf ^= 1u;
     }
+    red_buf ^= 1u;
 }
 
-// Copy-issuing side of one work item (all 32 lanes of the issuing warp call this).  `seq` counts the items this
-// CTA has issued since its barriers were initialised.  Returns false if the stage never came free.
-__device__ __forceinline__ bool f1_produce(const FastParams& P, const F1Geom& geo, uint8_t* stages, uint64_t* full_bar,
-                                           uint64_t* empty_bar, uint32_t item, uint32_t seq, uint32_t lane) {
-    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
-    const GroupRef G = group_ref(P, item / geo.tiles_per_group);
-    if (!mbar_wait(&empty_bar[s], ph ^ 1u)) return false;
-    if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
-        if (lane == 0) mbar_arrive(&full_bar[s]);
-        return true;
-    }
-    const uint32_t tile = item % geo.tiles_per_group, row0 = tile * geo.tile_rows;
-    const uint32_t row_bytes = P.d * G.bits / 8, row_stride = row_bytes + ROW_PAD, gpr = geo.groups_per_row;
-    uint8_t* st = stages + s * geo.stage_bytes;
-    const uint32_t scale_block = geo.tile_rows * gpr * 2;
-    if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
-    __syncwarp();
-    for (uint32_t r = lane; r < 2 * geo.tile_rows; r += 32) {
-        const bool up = r >= geo.tile_rows;
-        const uint32_t rr = up ? r - geo.tile_rows : r;
-        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + rr) * row_bytes;
-        bulk_g2s(st + (up ? geo.tile_rows * geo.row_stride_max : 0) + rr * row_stride, src, row_bytes, &full_bar[s]);
-    }
-    if (lane < 4) {
-        const uint32_t o = lane == 0 ? G.off.gate_s : (lane == 1 ? G.off.gate_b : (lane == 2 ? G.off.up_s : G.off.up_b));
-        bulk_g2s(st + 2 * geo.tile_rows * geo.row_stride_max + lane * scale_block, G.blob + o + (size_t)row0 * gpr * 2,
-                 scale_block, &full_bar[s]);
-    }
-    return true;
-}
-
-// Compute side of one work item (every compute warp calls this with the same item and seq).
-__device__ __forceinline__ bool f1_consume(const FastParams& P, const F1Geom& geo, const uint8_t* stages, uint64_t* full_bar,
-                                           uint64_t* empty_bar, uint32_t item, uint32_t seq, uint32_t warp, uint32_t lane,
-                                           float* red, uint32_t& red_buf) {
-    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
-    const GroupRef G = group_ref(P, item / geo.tiles_per_group);
-    if (!mbar_wait(&full_bar[s], ph)) return false;
-    if (G.ok) {
-        const uint8_t* st = stages + s * geo.stage_bytes;
-        if (G.bits == 4) f1_compute<4>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, red, red_buf);
-        else f1_compute<2>(P, G, geo, st, item % geo.tiles_per_group, warp, lane, red, red_buf);
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);
-    return true;
-}
-
-__global__ void __launch_bounds__(F1_THREADS, 1) ffn1_mma_kernel(const FastParams P) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full_bar[F1_STAGES], empty_bar[F1_STAGES];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
-    const F1Geom geo = f1_geom(P.d, P.f, max_bits);
-    float* red = reinterpret_cast<float*>(smem + F1_STAGES * geo.stage_bytes);
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CW); }
-        fence_barrier_init();
-    }
-    __syncthreads();
-    const uint32_t n_items = *P.n_groups * geo.tiles_per_group;
-    const uint32_t per_cta = (n_items + gridDim.x - 1) / gridDim.x;
-    const uint32_t first = blockIdx.x * per_cta, last = min(first + per_cta, n_items);
-    uint32_t seq = 0, red_buf = 0;
+// Runs this CTA's share of phase 1: units [first, last) of the flattened (group, token tile, row tile) list.
+// `seq` is the number of units the CTA has processed since its barriers were initialised (all warps keep it).
+template <int NGW>
+__device__ __forceinline__ bool phase1(const FastParams& P, const F1Geom& geo, const Phase1Ctx& C, uint32_t n_groups,
+                                       uint32_t first, uint32_t last, uint32_t& seq, uint32_t warp, uint32_t lane) {
     bool ok = true;
+    uint32_t g = 0, local_seq = seq;
     if (warp == CW) {
-        for (uint32_t item = first; item < last && ok; ++item, ++seq) ok = f1_produce(P, geo, smem, full_bar, empty_bar, item, seq, lane);
+        fence_proxy_async();
+        for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
+            seek_group(C.pref1, n_groups, u, g);
+            const GroupRef G = group_ref(P, g);
+            ok = f1_produce(P, geo, C, G, (u - C.pref1[g]) % geo.tiles_per_group, local_seq, lane);
+        }
     } else {
-        for (uint32_t item = first; item < last && ok; ++item, ++seq)
-            ok = f1_consume(P, geo, smem, full_bar, empty_bar, item, seq, warp, lane, red, red_buf);
+        uint32_t bf[NGW][8];
+        uint32_t cached = 0xFFFFFFFFu, red_buf = 0;
+        const uint32_t k0 = (warp % KS) * geo.k_per_warp;
+        for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
+            seek_group(C.pref1, n_groups, u, g);
+            const GroupRef G = group_ref(P, g);
+            const uint32_t local = u - C.pref1[g], tt = local / geo.tiles_per_group, tile = local % geo.tiles_per_group;
+            const uint32_t key = g * 16 + tt;
+            if (G.ok && key != cached) { f1_load_x<NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
+            const uint32_t s = local_seq % F1_STAGES, ph = (local_seq / F1_STAGES) & 1u;
+            if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+            if (G.ok) {
+                const uint8_t* st = C.stages + s * geo.stage_bytes;
+                if (G.bits == 4) f1_compute<4, NGW>(P, G, geo, st, tile, tt, bf, warp, lane, C.red, red_buf);
+                else f1_compute<2, NGW>(P, G, geo, st, tile, tt, bf, warp, lane, C.red, red_buf);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&C.empty[s]);
+        }
     }
-    if (!ok) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+    seq += last > first ? last - first : 0;
+    return ok;
 }
 
 // ------------------------------------------------------------------------------------------ phase 2 + combine
-// One CTA per block of 16 output rows (columns of the hidden state).  Warp w walks groups w, w+8, ...: the group's
-// 16 down-projection rows are copied into a warp-private ring of stages, multiplied against the group's hidden
-// activations, and the 16 x (tokens) results land in a CTA-wide array indexed by (token, rank slot).  When every
-// group is done the CTA applies the routing weights in rank order, residual first, and writes its 16 columns of
-// every token row:  moe_phase2_down_reduce_k8 (moe.metal:349-404) without a partials buffer in global memory.
-constexpr int F2_STAGES = 3;
-constexpr int F2_THREADS = CW * 32;
+// One CTA per block of 16 output rows (columns of the hidden state).  Units (group, token tile) flow through a
+// ring of slots: the copy warp deposits the group's 16 down rows, their scales and the token tile's hidden
+// activation rows; compute warp u % 16 multiplies them and leaves 16 x (tokens) results in a CTA-wide array
+// indexed by (token, rank slot).  When every unit is done the CTA applies the routing weights in rank order,
+// residual first, and writes its 16 columns of every token row: moe_phase2_down_reduce_k8 (moe.metal:349-404)
+// without a partials buffer in global memory.
+struct F2Geom {
+    uint32_t row_stride_max, gpr, act_stride, scale_off, act_off, slot_bytes;
+};
+
+__host__ __device__ inline F2Geom f2_geom(uint32_t f, uint32_t max_bits) {
+    F2Geom g;
+    g.row_stride_max = f * max_bits / 8 + ROW_PAD;
+    g.gpr = f / 64;
+    g.act_stride = f * 2 + ACT_PAD;
+    g.scale_off = 16 * g.row_stride_max;
+    g.act_off = g.scale_off + 2 * 16 * g.gpr * 2;
+    g.slot_bytes = (g.act_off + 8 * g.act_stride + 127u) & ~127u;
+    return g;
+}
+
+struct Phase2Ctx {
+    uint8_t* slots;
+    uint64_t* full;    // [F2_SLOTS]
+    uint64_t* empty;   // [F2_SLOTS]
+    float* part;       // [n_tokens][top_k + 1][16]
+    const uint32_t* pref2;
+};
+
+__device__ __forceinline__ bool f2_produce(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, const GroupRef& G,
+                                           uint32_t tt, uint32_t row0, uint32_t seq, uint32_t lane) {
+    const uint32_t s = seq % F2_SLOTS, ph = (seq / F2_SLOTS) & 1u;
+    if (!mbar_wait(&C.empty[s], ph ^ 1u)) return false;
+    if (!G.ok) { if (lane == 0) mbar_arrive(&C.full[s]); return true; }
+    const uint32_t row_bytes = P.f * G.bits / 8, row_stride = row_bytes + ROW_PAD, scale_block = 16 * geo.gpr * 2;
+    const uint32_t cols = min(8u, G.pair_count - tt * 8);
+    uint8_t* st = C.slots + s * geo.slot_bytes;
+    if (lane == 0) mbar_expect_tx(&C.full[s], 16 * row_bytes + 2 * scale_block + cols * P.f * 2);
+    __syncwarp();
+    if (lane < 16) bulk_g2s(st + lane * row_stride, G.blob + G.off.down_w + (size_t)(row0 + lane) * row_bytes, row_bytes, &C.full[s]);
+    else if (lane < 18)
+        bulk_g2s(st + geo.scale_off + (lane - 16) * scale_block,
+                 G.blob + (lane == 16 ? G.off.down_s : G.off.down_b) + (size_t)row0 * geo.gpr * 2, scale_block, &C.full[s]);
+    else if (lane - 18 < cols)
+        bulk_g2s(st + geo.act_off + (lane - 18) * geo.act_stride, P.actp + (size_t)(G.pair_start + tt * 8 + lane - 18) * P.f,
+                 P.f * 2, &C.full[s]);
+    return true;
+}
 
 template <int BITS, int NG>
-__device__ __forceinline__ void f2_compute(const FastParams& P, const GroupRef& G, const uint8_t* st, uint32_t row_stride_max,
-                                           uint32_t lane, float* part, uint32_t slots) {
+__device__ __forceinline__ void f2_compute(const FastParams& P, const F2Geom& geo, const GroupRef& G, uint32_t tt,
+                                           const uint8_t* st, uint32_t lane, float* part, uint32_t slots) {
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t row_stride = P.f * BITS / 8 + ROW_PAD, gpr = P.f / 64;
-    const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + 16 * row_stride_max);
-    const uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
+    const uint32_t row_stride = P.f * BITS / 8 + ROW_PAD;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + geo.scale_off);
+    constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
     ScaleRow<NG> s_lo, s_hi, b_lo, b_hi;
-    s_lo.load(sc + g * gpr); s_hi.load(sc + (g + 8) * gpr);
-    b_lo.load(sc + 16 * gpr + g * gpr); b_hi.load(sc + 16 * gpr + (g + 8) * gpr);
-    for (uint32_t tt = 0; tt < G.pair_count; tt += 8) {
-        const uint32_t cols = min(8u, G.pair_count - tt);
-        const __half* row_ptr = g < cols ? P.actp + (size_t)(G.pair_start + tt + g) * P.f : nullptr;
-        uint32_t bf[NG][8];
-        load_bfrags<NG>(row_ptr, 0, lane, bf);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    s_lo.load(sc + g * NG); s_hi.load(sc + (g + 8) * NG);
+    b_lo.load(sc + 16 * NG + g * NG); b_hi.load(sc + 16 * NG + (g + 8) * NG);
+    const uint32_t cols = min(8u, G.pair_count - tt * 8);
+    const uint8_t* act_row = st + geo.act_off + g * geo.act_stride + t * 32;   // columns >= cols hold stale rows: unused
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int gi = 0; gi < NG; ++gi)
-            group_mma<BITS>(st + g * row_stride, st + (g + 8) * row_stride, gi * group_bytes + t * lane_bytes, bf[gi],
-                            s_lo.at(gi, sdt), b_lo.at(gi, sdt), s_hi.at(gi, sdt), b_hi.at(gi, sdt), group_sum(bf[gi]), acc);
+    for (int gi = 0; gi < NG; ++gi) {
+        uint32_t bf[8];
+        const uint4 lo = *reinterpret_cast<const uint4*>(act_row + gi * 128);
+        const uint4 hi = *reinterpret_cast<const uint4*>(act_row + gi * 128 + 16);
+        bf[0] = lo.x; bf[1] = lo.y; bf[2] = lo.z; bf[3] = lo.w; bf[4] = hi.x; bf[5] = hi.y; bf[6] = hi.z; bf[7] = hi.w;
+        group_mma<BITS>(st + g * row_stride, st + (g + 8) * row_stride, gi * group_bytes + t * lane_bytes, bf,
+                        s_lo.at(gi, sdt), b_lo.at(gi, sdt), s_hi.at(gi, sdt), b_hi.at(gi, sdt), group_sum(bf), acc);
+    }
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const uint32_t n = 2 * t + c;
-            if (n < cols) {
-                const mfb_pair pr = P.sorted[G.pair_start + tt + n];
-                float* dst = part + ((size_t)pr.token * slots + pr.rank) * 16;
-                dst[g] = acc[c];
-                dst[g + 8] = acc[2 + c];
-            }
+    for (int c = 0; c < 2; ++c) {
+        const uint32_t n = 2 * t + c;
+        if (n < cols) {
+            const mfb_pair pr = P.sorted[G.pair_start + tt * 8 + n];
+            float* dst = part + ((size_t)pr.token * slots + pr.rank) * 16;
+            dst[g] = acc[c];
+            dst[g + 8] = acc[2 + c];
         }
     }
 }
 
 template <int BITS>
-__device__ __forceinline__ void f2_dispatch(const FastParams& P, const GroupRef& G, const uint8_t* st, uint32_t row_stride_max,
-                                            uint32_t lane, float* part, uint32_t slots) {
-    switch (P.f / 64) {
-        case 8: f2_compute<BITS, 8>(P, G, st, row_stride_max, lane, part, slots); break;
-        case 4: f2_compute<BITS, 4>(P, G, st, row_stride_max, lane, part, slots); break;
-        case 2: f2_compute<BITS, 2>(P, G, st, row_stride_max, lane, part, slots); break;
-        default: f2_compute<BITS, 1>(P, G, st, row_stride_max, lane, part, slots); break;
+__device__ __forceinline__ void f2_dispatch(const FastParams& P, const F2Geom& geo, const GroupRef& G, uint32_t tt,
+                                            const uint8_t* st, uint32_t lane, float* part, uint32_t slots) {
+    switch (geo.gpr) {
+        case 8: f2_compute<BITS, 8>(P, geo, G, tt, st, lane, part, slots); break;
+        case 4: f2_compute<BITS, 4>(P, geo, G, tt, st, lane, part, slots); break;
+        case 2: f2_compute<BITS, 2>(P, geo, G, tt, st, lane, part, slots); break;
+        default: f2_compute<BITS, 1>(P, geo, G, tt, st, lane, part, slots); break;
     }
 }
 
-// Issues the copies of one group's 16 down rows + scales into a warp-private stage (all lanes of the warp call).
-__device__ __forceinline__ void f2_issue(const FastParams& P, uint8_t* st, uint64_t* bar, uint32_t gidx, uint32_t row0,
-                                         uint32_t row_stride_max, uint32_t lane) {
-    const GroupRef G = group_ref(P, gidx);
-    if (!G.ok) { if (lane == 0) mbar_arrive(bar); return; }
-    const uint32_t gpr = P.f / 64;
-    const uint32_t row_bytes = P.f * G.bits / 8, row_stride = row_bytes + ROW_PAD, scale_block = 16 * gpr * 2;
-    fence_proxy_async();
-    if (lane == 0) mbar_expect_tx(bar, 16 * row_bytes + 2 * scale_block);
-    __syncwarp();
-    if (lane < 16) bulk_g2s(st + lane * row_stride, G.blob + G.off.down_w + (size_t)(row0 + lane) * row_bytes, row_bytes, bar);
-    else if (lane < 18)
-        bulk_g2s(st + 16 * row_stride_max + (lane - 16) * scale_block,
-                 G.blob + (lane == 16 ? G.off.down_s : G.off.down_b) + (size_t)row0 * gpr * 2, scale_block, bar);
+// Runs phase 2 for the 16 output rows starting at row0 over all units; `seq` as in phase1.
+__device__ __forceinline__ bool phase2(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, uint32_t n_groups,
+                                       uint32_t row0, uint32_t& seq, uint32_t warp, uint32_t lane) {
+    const uint32_t n_units = C.pref2[n_groups], slots = P.top_k + 1;
+    bool ok = true;
+    uint32_t g = 0;
+    if (warp == CW) {
+        fence_proxy_async();
+        for (uint32_t u = 0; u < n_units && ok; ++u) {
+            seek_group(C.pref2, n_groups, u, g);
+            ok = f2_produce(P, geo, C, group_ref(P, g), u - C.pref2[g], row0, seq + u, lane);
+        }
+    } else if (warp < (uint32_t)F2_SLOTS) {
+        // Compute warp w serves slot w only, so its waits on that slot's barriers follow each other in phase order.
+        // (A parity wait is only meaningful one phase ahead: a warp that started a whole lap ahead of its slot would
+        // see the not-yet-started previous phase as complete.)
+        const uint32_t u0 = (warp + F2_SLOTS - seq % F2_SLOTS) % F2_SLOTS;
+        for (uint32_t u = u0; u < n_units && ok; u += F2_SLOTS) {
+            seek_group(C.pref2, n_groups, u, g);
+            const GroupRef G = group_ref(P, g);
+            const uint32_t s = (seq + u) % F2_SLOTS, ph = ((seq + u) / F2_SLOTS) & 1u;
+            if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+            if (G.ok) {
+                const uint8_t* st = C.slots + s * geo.slot_bytes;
+                if (G.bits == 4) f2_dispatch<4>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
+                else f2_dispatch<2>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&C.empty[s]);
+        }
+    }
+    seq += n_units;
+    return ok;
 }
 
 // Rank-ordered weighted combine of this CTA's 16 columns: residual first, shared expert, then ranks ascending.
@@ -521,45 +618,60 @@ __device__ __forceinline__ void f2_combine(const FastParams& P, const float* par
     }
 }
 
-__global__ void __launch_bounds__(F2_THREADS, 1) ffn2_mma_kernel(const FastParams P) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full_bar[CW][F2_STAGES];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
-    const uint32_t row_stride_max = P.f * max_bits / 8 + ROW_PAD, gpr = P.f / 64;
-    const uint32_t stage_bytes = 16 * row_stride_max + 2 * 16 * gpr * 2;
-    const uint32_t slots = P.top_k + 1;
-    uint8_t* my_stages = smem + warp * F2_STAGES * stage_bytes;
-    float* part = reinterpret_cast<float*>(smem + CW * F2_STAGES * stage_bytes);
-    const uint32_t row0 = blockIdx.x * 16;
+// ------------------------------------------------------------------------------------------ separate kernels
+struct FastShared {
+    uint64_t full1[F1_STAGES], empty1[F1_STAGES], full2[F2_SLOTS], empty2[F2_SLOTS];
+    uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1];
+    uint32_t flag, n_groups;
+    float red[32];
+};
 
-    if (lane == 0) {
-        for (int s = 0; s < F2_STAGES; ++s) mbar_init(&full_bar[warp][s], 1);
+__device__ __forceinline__ void init_barriers(FastShared& S) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW); }
+        for (int s = 0; s < F2_SLOTS; ++s) { mbar_init(&S.full2[s], 1); mbar_init(&S.empty2[s], 1); }
         fence_barrier_init();
     }
-    for (uint32_t i = threadIdx.x; i < P.n_tokens * slots * 16; i += F2_THREADS) part[i] = 0.0f;
     __syncthreads();
+}
 
+template <int NGW>
+__global__ void __launch_bounds__(FAST_THREADS, 1) ffn1_mma_kernel(const FastParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ FastShared S;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
+    const F1Geom geo = f1_geom(P.d, P.f, max_bits);
+    init_barriers(S);
     const uint32_t n_groups = *P.n_groups;
-    uint32_t n_mine = 0;
-    for (uint32_t gidx = warp; gidx < n_groups; gidx += CW) ++n_mine;
-    for (uint32_t i = 0; i < n_mine && i < (uint32_t)F2_STAGES; ++i)
-        f2_issue(P, my_stages + i * stage_bytes, &full_bar[warp][i], warp + i * CW, row0, row_stride_max, lane);
-    for (uint32_t i = 0; i < n_mine; ++i) {
-        const uint32_t s = i % F2_STAGES, ph = (i / F2_STAGES) & 1u;
-        const GroupRef G = group_ref(P, warp + i * CW);
-        if (!mbar_wait(&full_bar[warp][s], ph)) { atomicOr(P.status, STATUS_MBAR_TIMEOUT); break; }
-        if (G.ok) {
-            const uint8_t* st = my_stages + s * stage_bytes;
-            if (G.bits == 4) f2_dispatch<4>(P, G, st, row_stride_max, lane, part, slots);
-            else f2_dispatch<2>(P, G, st, row_stride_max, lane, part, slots);
-        }
-        __syncwarp();
-        if (i + F2_STAGES < n_mine)
-            f2_issue(P, my_stages + s * stage_bytes, &full_bar[warp][s], warp + (i + F2_STAGES) * CW, row0, row_stride_max, lane);
-    }
+    if (warp == 0) warp_unit_prefix(P.groups, n_groups, geo.tiles_per_group, S.pref1, S.pref2, lane);
     __syncthreads();
-    f2_combine(P, part, slots, row0, P.shared_blob != nullptr);
+    Phase1Ctx C{smem, S.full1, S.empty1, reinterpret_cast<float*>(smem + F1_STAGES * geo.stage_bytes), S.pref1};
+    const uint32_t n_units = S.pref1[n_groups];
+    const uint32_t per_cta = (n_units + gridDim.x - 1) / gridDim.x;
+    const uint32_t first = min(blockIdx.x * per_cta, n_units), last = min(first + per_cta, n_units);
+    uint32_t seq = 0;
+    if (!phase1<NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+}
+
+__global__ void __launch_bounds__(FAST_THREADS, 1) ffn2_mma_kernel(const FastParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ FastShared S;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
+    const F2Geom geo = f2_geom(P.f, max_bits);
+    const uint32_t slots = P.top_k + 1;
+    float* part = reinterpret_cast<float*>(smem + F2_SLOTS * geo.slot_bytes);
+    init_barriers(S);
+    const uint32_t n_groups = *P.n_groups;
+    if (warp == 0) warp_unit_prefix(P.groups, n_groups, 1, S.pref1, S.pref2, lane);
+    for (uint32_t i = threadIdx.x; i < P.n_tokens * slots * 16; i += blockDim.x) part[i] = 0.0f;
+    __syncthreads();
+    Phase2Ctx C{smem, S.full2, S.empty2, part, S.pref2};
+    uint32_t seq = 0;
+    if (!phase2(P, geo, C, n_groups, blockIdx.x * 16, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+    __syncthreads();
+    f2_combine(P, part, slots, blockIdx.x * 16, P.shared_blob != nullptr);
 }
 
 // ------------------------------------------------------------------------------------------ prep: RMSNorm + layouts
@@ -603,8 +715,6 @@ __global__ void prep_kernel(const void* __restrict__ h, int dtype, const __nv_bf
     }
 }
 
-}  // namespace
-
 // ------------------------------------------------------------------------------------------ fused stack kernel
 // All layers of a decode step in ONE cooperative launch: RMSNorm, gate GEMV, top-k, sort, phase 1, phase 2 and
 // the weighted combine, with grid-wide barriers between dependent phases.  At batch 1 a layer moves 17 MB, which
@@ -613,26 +723,10 @@ __global__ void prep_kernel(const void* __restrict__ h, int dtype, const __nv_bf
 //
 // Every wait is bounded: a barrier or mbarrier that does not complete within its limit sets the abort word and
 // the device status, every CTA then falls through its remaining barriers and returns; nothing spins for ever.
-namespace {
-
-constexpr long long GRID_WAIT_CYCLES = 4000000000ll;   // ~2 s at 1.9 GHz
-
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float ld_cg_f32(const void* p) { return __uint_as_float(ld_cg_u32(p)); }
-
-struct MegaShared {
-    uint64_t full1[F1_STAGES], empty1[F1_STAGES], full2[CW][2];
-    uint32_t flag;          // barrier outcome broadcast: 1 = proceed, 0 = abort
-    uint32_t n_groups;
-    float red[32];
-};
+constexpr long long GRID_WAIT_CYCLES = 1500000000ll;   // ~0.8 s at 1.9 GHz
 
 // Arrive-and-wait over all CTAs.  `epoch` counts the arrivals this CTA expects to have been made in total.
-__device__ __forceinline__ bool grid_barrier(const MegaParams& M, MegaShared& S, uint32_t& epoch) {
+__device__ __forceinline__ bool grid_barrier(const MegaParams& M, FastShared& S, uint32_t& epoch) {
     __syncthreads();
     if (threadIdx.x == 0) {
         epoch += gridDim.x;
@@ -657,17 +751,19 @@ __device__ __forceinline__ bool grid_barrier(const MegaParams& M, MegaShared& S,
 }
 
 // RMSNorm of one row by the first 256 threads of the CTA, arithmetic and order of rmsnorm_kernel (glue.cu).
-// Writes the row in the activation dtype and in the permuted fp16 layout(s).
-__device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLayer& Ly, MegaShared& S, const void* h,
-                                              uint32_t tok) {
+// Writes the row in the activation dtype and in the permuted fp16 layout(s); the outputs may be global or shared.
+__device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLayer& Ly, FastShared& S, const void* h,
+                                              uint32_t tok, uint16_t* xn_out, __half* xp_out, __half* xp2_out) {
     const uint32_t d = M.d, tid = threadIdx.x;
-    const size_t row = (size_t)tok * d;
+    const uint16_t* src = (const uint16_t*)h + (size_t)tok * d;
     float ss = 0.0f;
-    if (tid < 256)
+    if (tid < 256) {
+#pragma unroll 8
         for (uint32_t i = tid; i < d; i += 256) {
-            const float v = widen16(ld_cg_u16((const uint16_t*)h + row + i), M.x_dtype);
+            const float v = widen16(ld_cg_u16(src + i), M.x_dtype);
             ss = fmaf(v, v, ss);
         }
+    }
     for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
     if (tid < 256 && (tid & 31) == 0) S.red[tid >> 5] = ss;
     __syncthreads();
@@ -678,30 +774,33 @@ __device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLay
     }
     __syncthreads();
     const float inv = rsqrtf(S.red[8] / (float)d + M.eps);
-    if (tid < 256)
+    if (tid < 256) {
+#pragma unroll 8
         for (uint32_t i = tid; i < d; i += 256) {
-            float v = widen16(ld_cg_u16((const uint16_t*)h + row + i), M.x_dtype);
+            float v = widen16(ld_cg_u16(src + i), M.x_dtype);
             const float gw = Ly.norm_w ? __bfloat162float(Ly.norm_w[i]) : 1.0f;
             v = v * inv * gw;
             const uint16_t bits = narrow16(v, M.x_dtype);
-            ((uint16_t*)M.xn)[row + i] = bits;
+            xn_out[i] = bits;
             v = fminf(fmaxf(widen16(bits, M.x_dtype), -65504.0f), 65504.0f);
             const __half hv = __float2half_rn(v);
-            M.xp[row + (i & ~15u) + perm_pos(i & 15u, M.bits)] = hv;
-            if (M.xp2) M.xp2[row + (i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = hv;
+            xp_out[(i & ~15u) + perm_pos(i & 15u, M.bits)] = hv;
+            if (xp2_out) xp2_out[(i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = hv;
         }
+    }
     __syncthreads();
 }
 
 // logits[t, e] for the experts this CTA owns (e = blockIdx.x, + gridDim.x, ...), every token, in the fixed
 // summation order of router_logits_kernel: lane l takes k = l, l+32, ... ascending, then a xor butterfly.
 // `stage` is free shared memory: up to two gate rows as fp32, then one activation row per warp as raw 16-bit.
+// With x_smem the single activation row is already in shared memory.
 constexpr uint32_t MEGA_ROWS_PER_PASS = 2;
 
-__device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage) {
+__device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage, const uint16_t* x_smem) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5, d = M.d;
-    float* w_rows = reinterpret_cast<float*>(stage);                                   // [2][d]
-    uint16_t* x_row = reinterpret_cast<uint16_t*>(stage + MEGA_ROWS_PER_PASS * d * 4) + warp * d;   // [warps][d]
+    float* w_rows = reinterpret_cast<float*>(stage);                                                   // [2][d]
+    uint16_t* x_stage = reinterpret_cast<uint16_t*>(stage + MEGA_ROWS_PER_PASS * d * 4) + warp * d;    // [warps][d]
     for (uint32_t e0 = blockIdx.x; e0 < M.num_experts; e0 += MEGA_ROWS_PER_PASS * gridDim.x) {
         __syncthreads();
         uint32_t ne = 0;
@@ -721,10 +820,14 @@ __device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer
         }
         __syncthreads();
         for (uint32_t t = warp; t < M.n_tokens; t += warps) {
-            const uint16_t* x = (const uint16_t*)M.xn + (size_t)t * d;
-            __syncwarp();
-            for (uint32_t i = lane; i < d / 8; i += 32) *reinterpret_cast<uint4*>(x_row + i * 8) = ld_cg_u4(x + i * 8);
-            __syncwarp();
+            const uint16_t* x_row = x_smem;
+            if (!x_smem) {
+                const uint16_t* x = (const uint16_t*)M.xn + (size_t)t * d;
+                __syncwarp();
+                for (uint32_t i = lane; i < d / 8; i += 32) *reinterpret_cast<uint4*>(x_stage + i * 8) = ld_cg_u4(x + i * 8);
+                __syncwarp();
+                x_row = x_stage;
+            }
             float acc[MEGA_ROWS_PER_PASS] = {0.0f, 0.0f};
 #pragma unroll 8
             for (uint32_t i = lane; i < d; i += 32) {
@@ -747,28 +850,40 @@ __device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer
     __syncthreads();
 }
 
-// Counting sort of the routing table into shared memory, identical order to group.cu / route_small_kernel:
-// every CTA builds the same lists.  idx_s holds the table, run_s is scratch of num_experts entries.
-__device__ __forceinline__ void mega_group(const MegaParams& M, MegaShared& S, const uint32_t* idx_s, const uint16_t* w_s,
+// Counting sort of the routing table into shared memory, identical order to group.cu / route_small_kernel; every
+// CTA builds the same lists.  run_s is scratch of num_experts entries.  Warp 0 does the scans with shuffles.
+__device__ __forceinline__ void mega_group(const MegaParams& M, FastShared& S, const uint32_t* idx_s, const uint16_t* w_s,
                                            uint32_t* run_s, mfb_pair* sorted_s, mfb_group* groups_s, bool shared) {
     const uint32_t n_pairs = M.n_tokens * M.top_k, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) run_s[e] = 0;
     __syncthreads();
     for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&run_s[idx_s[p]], 1u);
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t run = 0, ng = 0;
-        for (uint32_t e = 0; e < M.num_experts; ++e) {
-            const uint32_t c = run_s[e];
-            run_s[e] = run;
-            if (c) { groups_s[ng].expert = e; groups_s[ng].pair_start = run; groups_s[ng].pair_count = c; ++ng; }
-            run += c;
-        }
-        if (shared) { groups_s[ng].expert = M.num_experts; groups_s[ng].pair_start = run; groups_s[ng].pair_count = M.n_tokens; ++ng; }
-        S.n_groups = ng;
-    }
-    __syncthreads();
     if (warp == 0) {
+        const uint32_t per = (M.num_experts + 31) / 32, e0 = lane * per;
+        uint32_t cnt = 0, nz = 0;
+        for (uint32_t j = 0; j < per; ++j)
+            if (e0 + j < M.num_experts) { const uint32_t c = run_s[e0 + j]; cnt += c; nz += c ? 1u : 0u; }
+        uint32_t cnt_incl = cnt, nz_incl = nz;
+        for (uint32_t off = 1; off < 32; off <<= 1) {
+            const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, cnt_incl, off), b = __shfl_up_sync(0xFFFFFFFFu, nz_incl, off);
+            if (lane >= off) { cnt_incl += a; nz_incl += b; }
+        }
+        uint32_t run = cnt_incl - cnt, gi = nz_incl - nz;
+        for (uint32_t j = 0; j < per; ++j)
+            if (e0 + j < M.num_experts) {
+                const uint32_t c = run_s[e0 + j];
+                run_s[e0 + j] = run;
+                if (c) { groups_s[gi].expert = e0 + j; groups_s[gi].pair_start = run; groups_s[gi].pair_count = c; ++gi; }
+                run += c;
+            }
+        uint32_t ng = __shfl_sync(0xFFFFFFFFu, nz_incl, 31);
+        if (lane == 0) {
+            if (shared) { groups_s[ng].expert = M.num_experts; groups_s[ng].pair_start = n_pairs; groups_s[ng].pair_count = M.n_tokens; ++ng; }
+            S.n_groups = ng;
+        }
+        __syncwarp();
+        // ordered scatter: 32 pairs per round in (token, rank) order
         for (uint32_t p0 = 0; p0 < n_pairs; p0 += 32) {
             const uint32_t p = p0 + lane;
             const uint32_t e = p < n_pairs ? idx_s[p] : 0xFFFFFFFFu;
@@ -795,44 +910,39 @@ __device__ __forceinline__ void mega_group(const MegaParams& M, MegaShared& S, c
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaParams M) {
+template <int NGW>
+__global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaParams M) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ MegaShared S;
+    __shared__ FastShared S;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool has_shared_cfg = M.shared_bits != 0;
-    const uint32_t max_bits = has_shared_cfg && M.shared_bits > M.bits ? M.shared_bits : M.bits;
-    const F1Geom geo = f1_geom(M.d, M.f, max_bits);
+    const uint32_t max_bits = M.shared_bits > M.bits ? M.shared_bits : M.bits;
+    const F1Geom geo1 = f1_geom(M.d, M.f, max_bits);
+    const F2Geom geo2 = f2_geom(M.f, max_bits);
     const uint32_t slots = M.top_k + 1, n_pairs = M.n_tokens * M.top_k;
-    // ---- shared memory carve-up.  Region A serves phase 1 (two stages) and is reused by phase 2 (per-warp
-    // stages + the per-(token, slot) partial rows); the routing lists and small scratch follow it.
+    const bool single = M.n_tokens == 1;
+    // ---- shared memory carve-up.  Region A holds the two phase-1 stages and the k-split exchange buffer; phase 2
+    // reuses it for its slot ring and the per-(token, slot) partial rows.  The routing lists follow it.
     uint8_t* region_a = smem;
-    const uint32_t region_a_bytes = F1_STAGES * geo.stage_bytes;
-    float* red = reinterpret_cast<float*>(smem + region_a_bytes);
-    mfb_pair* sorted_s = reinterpret_cast<mfb_pair*>(red + 2 * CW * 32 * 8);
+    const uint32_t region_a_bytes = F1_STAGES * geo1.stage_bytes + 2 * CW * 32 * 8 * 4;
+    float* red = reinterpret_cast<float*>(smem + F1_STAGES * geo1.stage_bytes);
+    float* part = reinterpret_cast<float*>(region_a + F2_SLOTS * geo2.slot_bytes);
+    mfb_pair* sorted_s = reinterpret_cast<mfb_pair*>(smem + region_a_bytes);
     mfb_group* groups_s = reinterpret_cast<mfb_group*>(sorted_s + (n_pairs + M.n_tokens));
     uint32_t* idx_s = reinterpret_cast<uint32_t*>(groups_s + (M.num_experts + 1));
     uint16_t* w_s = reinterpret_cast<uint16_t*>(idx_s + n_pairs);
     uint32_t* run_s = reinterpret_cast<uint32_t*>(w_s + ((n_pairs + 1) & ~1u));
-    // phase 2 view of region A
-    const uint32_t row_stride2_max = M.f * max_bits / 8 + ROW_PAD, gpr2 = M.f / 64;
-    const uint32_t stage2_bytes = 16 * row_stride2_max + 2 * 16 * gpr2 * 2;
-    uint8_t* my_stages2 = region_a + warp * 2 * stage2_bytes;
-    float* part = reinterpret_cast<float*>(region_a + CW * 2 * stage2_bytes);
+    // single-token mode keeps the normalised row in shared memory (16-byte aligned)
+    uint16_t* xn_s = reinterpret_cast<uint16_t*>((reinterpret_cast<uintptr_t>(run_s + M.num_experts) + 15) & ~(uintptr_t)15);
+    __half* xp_s = reinterpret_cast<__half*>(xn_s + M.d);
+    __half* xp2_s = xp_s + M.d;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW); }
-        for (int w = 0; w < CW; ++w) for (int s = 0; s < 2; ++s) mbar_init(&S.full2[w][s], 1);
-        fence_barrier_init();
-    }
-    __syncthreads();
-
-    uint32_t epoch = 0, it1 = 0, it2 = 0;
+    init_barriers(S);
+    uint32_t epoch = 0, seq1 = 0, seq2 = 0;
     bool alive = true;
     for (uint32_t l = 0; l < M.n_layers && alive; ++l) {
         const MegaLayer Ly = M.layers[l];
         void* h = (uint8_t*)M.hidden + (size_t)l * M.layer_stride * 2;   // 16-bit activations
         const bool shared = Ly.shared_blob != nullptr;
-
         uint64_t* trace = M.trace ? M.trace + (size_t)l * 8 : nullptr;
         auto stamp = [&](int slot) {
             if (trace && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -842,20 +952,16 @@ __global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaPar
             }
         };
         stamp(0);
-        // ---- phase 0a: RMSNorm, token t by CTA t % grid
-        for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x) mega_norm_row(M, Ly, S, h, t);
-        if (!(alive = grid_barrier(M, S, epoch))) break;
-
-        stamp(1);
-        // ---- phase 0b: gate logits, expert e by CTA e % grid
-        mega_logits(M, Ly, region_a);
-        if (!(alive = grid_barrier(M, S, epoch))) break;
-
-        stamp(2);
-        // ---- phase 0c: selection, token t by warp 0 of CTA t % grid
-        for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x) {
-            float* lg_s = red;   // the row is copied to shared memory with L2-coherent loads first
-            for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) lg_s[e] = ld_cg_f32(M.logits + (size_t)t * M.num_experts + e);
+        if (single) {
+            // every CTA normalises the one row itself (no barrier), computes the logits of its experts, and after
+            // the barrier every CTA repeats the selection: two grid barriers fewer per layer
+            mega_norm_row(M, Ly, S, h, 0, xn_s, xp_s, M.xp2 ? xp2_s : nullptr);
+            stamp(1);
+            mega_logits(M, Ly, region_a, xn_s);
+            if (!(alive = grid_barrier(M, S, epoch))) break;
+            stamp(2);
+            float* lg_s = red;
+            for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) lg_s[e] = ld_cg_f32(M.logits + e);
             __syncthreads();
             if (warp == 0) {
                 uint32_t e = 0;
@@ -863,22 +969,66 @@ __global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaPar
                 select_row(lg_s, M.num_experts, M.top_k, M.router_mode, Ly.per_expert_scale, Ly.correction_bias, M.route_scale,
                            lane, e, wgt);
                 if (lane < M.top_k) {
-                    M.idx[(size_t)t * M.top_k + lane] = e;
-                    M.route_w[(size_t)t * M.top_k + lane] = wgt;
+                    w_s[lane] = wgt;
+                    groups_s[lane].expert = e; groups_s[lane].pair_start = lane; groups_s[lane].pair_count = 1;
+                    mfb_pair pr; pr.token = 0; pr.expert = e; pr.rank = lane; pr.weight_bits = wgt;
+                    sorted_s[lane] = pr;
+                    if (blockIdx.x == 0) { M.idx[lane] = e; M.route_w[lane] = wgt; }
+                }
+                if (lane == 0) {
+                    uint32_t ng = M.top_k;
+                    if (shared) {
+                        groups_s[ng].expert = M.num_experts; groups_s[ng].pair_start = ng; groups_s[ng].pair_count = 1;
+                        mfb_pair pr; pr.token = 0; pr.expert = M.num_experts; pr.rank = M.top_k; pr.weight_bits = 0x3C00u;
+                        sorted_s[ng] = pr;
+                        ++ng;
+                    }
+                    S.n_groups = ng;
                 }
             }
             __syncthreads();
+            stamp(3);
+        } else {
+            // ---- RMSNorm, token t by CTA t % grid
+            for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x)
+                mega_norm_row(M, Ly, S, h, t, (uint16_t*)M.xn + (size_t)t * M.d, M.xp + (size_t)t * M.d,
+                              M.xp2 ? M.xp2 + (size_t)t * M.d : nullptr);
+            if (!(alive = grid_barrier(M, S, epoch))) break;
+            stamp(1);
+            // ---- gate logits, expert e by CTA e % grid
+            mega_logits(M, Ly, region_a, nullptr);
+            if (!(alive = grid_barrier(M, S, epoch))) break;
+            stamp(2);
+            // ---- selection, token t by warp 0 of CTA t % grid
+            for (uint32_t t = blockIdx.x; t < M.n_tokens; t += gridDim.x) {
+                float* lg_s = red;   // the row is copied to shared memory with L2-coherent loads first
+                for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) lg_s[e] = ld_cg_f32(M.logits + (size_t)t * M.num_experts + e);
+                __syncthreads();
+                if (warp == 0) {
+                    uint32_t e = 0;
+                    uint16_t wgt = 0;
+                    select_row(lg_s, M.num_experts, M.top_k, M.router_mode, Ly.per_expert_scale, Ly.correction_bias, M.route_scale,
+                               lane, e, wgt);
+                    if (lane < M.top_k) {
+                        M.idx[(size_t)t * M.top_k + lane] = e;
+                        M.route_w[(size_t)t * M.top_k + lane] = wgt;
+                    }
+                }
+                __syncthreads();
+            }
+            if (!(alive = grid_barrier(M, S, epoch))) break;
+            stamp(3);
+            // ---- sort of the routing table, redundantly in every CTA (no barrier needed)
+            for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+                idx_s[p] = ld_cg_u32(M.idx + p);
+                w_s[p] = ld_cg_u16(M.route_w + p);
+            }
+            __syncthreads();
+            mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
-        if (!(alive = grid_barrier(M, S, epoch))) break;
-
-        stamp(3);
-        // ---- sort of the routing table, redundantly in every CTA (no barrier needed)
-        for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-            idx_s[p] = ld_cg_u32(M.idx + p);
-            w_s[p] = ld_cg_u16(M.route_w + p);
-        }
+        const uint32_t n_groups = S.n_groups;
+        if (warp == 0) warp_unit_prefix(groups_s, n_groups, geo1.tiles_per_group, S.pref1, S.pref2, lane);
         __syncthreads();
-        mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
 
         FastParams P;
         P.pool = Ly.pool; P.slot_stride = Ly.slot_stride; P.slot_of = Ly.slot_of; P.shared_blob = Ly.shared_blob;
@@ -886,60 +1036,35 @@ __global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaPar
         P.d = M.d; P.f = M.f; P.num_experts = M.num_experts; P.top_k = M.top_k; P.bits = M.bits; P.shared_bits = M.shared_bits;
         P.scale_dtype = M.scale_dtype; P.activation = M.activation; P.limit = M.limit;
         P.sorted = sorted_s; P.groups = groups_s; P.n_groups = &S.n_groups;
-        P.xp = M.xp; P.xp_shared = M.xp2 ? M.xp2 : M.xp; P.actp = M.actp; P.route_w = w_s;
+        P.xp = single ? xp_s : M.xp; P.xp_shared = single ? (M.xp2 ? xp2_s : xp_s) : (M.xp2 ? M.xp2 : M.xp);
+        P.x_in_smem = single ? 1 : 0;
+        P.actp = M.actp; P.route_w = w_s;
         P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
-
         stamp(4);
-        // ---- phase 1
-        const uint32_t n_groups = S.n_groups;
-        const uint32_t n_items = n_groups * geo.tiles_per_group;
-        const uint32_t per_cta = (n_items + gridDim.x - 1) / gridDim.x;
-        const uint32_t first = blockIdx.x * per_cta, last = min(first + per_cta, n_items);
-        bool bad = false;
-        if (warp == CW) {
-            fence_proxy_async();
-            for (uint32_t item = first; item < last; ++item, ++it1)
-                if (!f1_produce(P, geo, region_a, S.full1, S.empty1, item, it1, lane)) { bad = true; break; }
-        } else {
-            uint32_t red_buf = 0;
-            for (uint32_t item = first; item < last; ++item, ++it1)
-                if (!f1_consume(P, geo, region_a, S.full1, S.empty1, item, it1, warp, lane, red, red_buf)) { bad = true; break; }
-        }
-        if (bad) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
-        __syncthreads();   // region A is free again: phase 2 may stage into it before the grid barrier
 
-        // ---- phase 2: issue the first copies now so that they fly during the barrier, compute after it
-        const bool p2_cta = blockIdx.x < M.d / 16;
-        const uint32_t row0 = blockIdx.x * 16;
-        uint32_t n_mine = 0;
-        if (p2_cta && warp < CW) {
-            for (uint32_t gidx = warp; gidx < n_groups; gidx += CW) ++n_mine;
-            for (uint32_t i = 0; i < n_mine && i < 2; ++i)
-                f2_issue(P, my_stages2 + ((it2 + i) & 1u) * stage2_bytes, &S.full2[warp][(it2 + i) & 1u], warp + i * CW, row0,
-                         row_stride2_max, lane);
-            for (uint32_t i = threadIdx.x; i < M.n_tokens * slots * 16; i += CW * 32) part[i] = 0.0f;
+        // ---- phase 1: this CTA's contiguous share of the (group, token tile, row tile) units
+        {
+            Phase1Ctx C{region_a, S.full1, S.empty1, red, S.pref1};
+            const uint32_t n_units = S.pref1[n_groups];
+            const uint32_t per_cta = (n_units + gridDim.x - 1) / gridDim.x;
+            const uint32_t first = min(blockIdx.x * per_cta, n_units), last = min(first + per_cta, n_units);
+            if (!phase1<NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
         }
+        fence_proxy_async();   // hidden activations written here are read by other CTAs' bulk copies after the barrier
         stamp(5);
         if (!(alive = grid_barrier(M, S, epoch))) break;
         stamp(6);
 
-        if (p2_cta && warp < CW) {
-            for (uint32_t i = 0; i < n_mine; ++i, ++it2) {
-                const uint32_t s = it2 & 1u, ph = (it2 >> 1) & 1u;
-                const GroupRef G = group_ref(P, warp + i * CW);
-                if (!mbar_wait(&S.full2[warp][s], ph)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); break; }
-                if (G.ok) {
-                    const uint8_t* st = my_stages2 + s * stage2_bytes;
-                    if (G.bits == 4) f2_dispatch<4>(P, G, st, row_stride2_max, lane, part, slots);
-                    else f2_dispatch<2>(P, G, st, row_stride2_max, lane, part, slots);
-                }
-                __syncwarp();
-                if (i + 2 < n_mine)
-                    f2_issue(P, my_stages2 + s * stage2_bytes, &S.full2[warp][s], warp + (i + 2) * CW, row0, row_stride2_max, lane);
-            }
+        // ---- phase 2 + combine on the CTAs that own a block of 16 output columns
+        const bool p2_cta = blockIdx.x < M.d / 16;
+        if (p2_cta) {
+            for (uint32_t i = threadIdx.x; i < M.n_tokens * slots * 16; i += blockDim.x) part[i] = 0.0f;
+            __syncthreads();
+            Phase2Ctx C{region_a, S.full2, S.empty2, part, S.pref2};
+            if (!phase2(P, geo2, C, n_groups, blockIdx.x * 16, seq2, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+            __syncthreads();
+            f2_combine(P, part, slots, blockIdx.x * 16, shared);
         }
-        __syncthreads();
-        if (p2_cta) f2_combine(P, part, slots, row0, shared);
         stamp(7);
         if (!(alive = grid_barrier(M, S, epoch))) break;
     }
@@ -948,50 +1073,51 @@ __global__ void __launch_bounds__(F1_THREADS, 1) stack_mega_kernel(const MegaPar
 }  // namespace
 
 // ------------------------------------------------------------------------------------------ host side
+static uint32_t cfg_max_bits(const mfb_moe_config& c) { return c.shared_bits > c.bits ? c.shared_bits : c.bits; }
+
 bool fast_supported(const mfb_moe_config& c) {
-    const uint32_t ks = c.d / 512;
-    if (c.d % 512 || !(ks == 1 || ks == 2 || ks == 4 || ks == 8)) return false;
-    if (c.f % 64 || c.f > 512) return false;            // phase 2 keeps a whole row's activations in registers
+    if (!(c.d == 512 || c.d == 1024 || c.d == 2048)) return false;   // 1, 2 or 4 groups per warp in phase 1
     const uint32_t ng = c.f / 64;
-    if (!(ng == 1 || ng == 2 || ng == 4 || ng == 8)) return false;
-    const uint32_t tile_rows = 16 * (CW / ks);
-    if (c.f % tile_rows || c.d % 16) return false;
+    if (c.f % 64 || !(ng == 1 || ng == 2 || ng == 4 || ng == 8)) return false;
+    if (c.f % (16 * RT)) return false;
     if (c.top_k + 1 > 32) return false;
     return true;
 }
 
 size_t fast_smem1(const mfb_moe_config& c) {
-    const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
-    const F1Geom g = f1_geom(c.d, c.f, max_bits);
+    const F1Geom g = f1_geom(c.d, c.f, cfg_max_bits(c));
     return (size_t)F1_STAGES * g.stage_bytes + 2 * CW * 32 * 8 * sizeof(float);
 }
 
 size_t fast_smem2(const mfb_moe_config& c, uint32_t n_tokens) {
-    const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
-    const uint32_t row_stride_max = c.f * max_bits / 8 + ROW_PAD, gpr = c.f / 64;
-    const size_t stage_bytes = 16 * row_stride_max + 2 * 16 * gpr * 2;
-    return (size_t)CW * F2_STAGES * stage_bytes + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
+    const F2Geom g = f2_geom(c.f, cfg_max_bits(c));
+    return (size_t)F2_SLOTS * g.slot_bytes + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
 }
 
 size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
     const size_t pairs = (size_t)n_tokens * c.top_k;
     const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
-                         ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4;
-    const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
-    const uint32_t row_stride_max = c.f * max_bits / 8 + ROW_PAD, gpr = c.f / 64;
-    const size_t stage2 = 16 * row_stride_max + 2 * 16 * gpr * 2;
-    const size_t phase2 = (size_t)CW * 2 * stage2 + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
-    const size_t region_a = fast_smem1(c) - 2 * CW * 32 * 8 * sizeof(float);
-    if (phase2 > region_a || (size_t)c.d * 26 > region_a) return (size_t)1 << 30;   // does not fit: caller falls back
-    return fast_smem1(c) + lists + 64;
+                         ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 6 : 0);
+    const size_t region_a = fast_smem1(c);
+    if (fast_smem2(c, n_tokens) > region_a || (size_t)c.d * (MEGA_ROWS_PER_PASS * 4 + (CW + 1) * 2) > region_a)
+        return (size_t)1 << 30;   // does not fit: the caller falls back to the per-layer launches
+    return region_a + lists + 64;
+}
+
+template <int NGW>
+static cudaError_t fast_init_ngw() {
+    cudaError_t e = cudaFuncSetAttribute(ffn1_mma_kernel<NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    return e;
 }
 
 // One-time opt-in to large dynamic shared memory for the fast kernels (called when a handle is created, so that no
 // attribute call happens while a caller captures a CUDA graph).
 cudaError_t fast_init() {
-    cudaError_t e = cudaFuncSetAttribute(ffn1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(ffn2_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(ffn2_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = fast_init_ngw<1>();
+    if (e == cudaSuccess) e = fast_init_ngw<2>();
+    if (e == cudaSuccess) e = fast_init_ngw<4>();
     return e;
 }
 
@@ -1004,14 +1130,18 @@ cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __n
 }
 
 cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups) {
-    const uint32_t max_bits = c.shared_bits > c.bits ? c.shared_bits : c.bits;
-    const F1Geom g = f1_geom(c.d, c.f, max_bits);
-    const uint32_t max_items = max_groups * g.tiles_per_group;
-    const uint32_t grid = max_items < (uint32_t)sm_count ? max_items : (uint32_t)sm_count;
-    ffn1_mma_kernel<<<grid, F1_THREADS, fast_smem1(c), s>>>(P);
+    const F1Geom g = f1_geom(c.d, c.f, cfg_max_bits(c));
+    const uint32_t max_units = max_groups * g.tiles_per_group * ((P.n_tokens + 7) / 8);
+    const uint32_t grid = max_units < (uint32_t)sm_count ? max_units : (uint32_t)sm_count;
+    switch (c.d / (64 * KS)) {
+        case 1: ffn1_mma_kernel<1><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
+        case 2: ffn1_mma_kernel<2><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
+        case 4: ffn1_mma_kernel<4><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
+        default: return cudaErrorInvalidValue;
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    ffn2_mma_kernel<<<P.d / 16, F2_THREADS, fast_smem2(c, P.n_tokens), s>>>(P);
+    ffn2_mma_kernel<<<P.d / 16, FAST_THREADS, fast_smem2(c, P.n_tokens), s>>>(P);
     count_launches(2);
     return cudaGetLastError();
 }
@@ -1021,8 +1151,14 @@ cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe
     if (e != cudaSuccess) return e;
     MegaParams copy = M;
     void* args[] = {&copy};
-    e = cudaLaunchCooperativeKernel((const void*)stack_mega_kernel, dim3((unsigned)sm_count), dim3(F1_THREADS), args,
-                                    fast_smem_stack(c, M.n_tokens), s);
+    const void* fn = nullptr;
+    switch (c.d / (64 * KS)) {
+        case 1: fn = (const void*)stack_mega_kernel<1>; break;
+        case 2: fn = (const void*)stack_mega_kernel<2>; break;
+        case 4: fn = (const void*)stack_mega_kernel<4>; break;
+        default: return cudaErrorInvalidValue;
+    }
+    e = cudaLaunchCooperativeKernel(fn, dim3((unsigned)sm_count), dim3(FAST_THREADS), args, fast_smem_stack(c, M.n_tokens), s);
     count_launches(1);
     return e;
 }

@@ -18,6 +18,7 @@ struct FastParams {
     const uint32_t* n_groups;
     const __half* xp;         // [tokens, d] fp16 activations, permuted for `bits`
     const __half* xp_shared;  // the same permuted for `shared_bits` (== xp when the widths agree)
+    int x_in_smem;            // xp / xp_shared point into shared memory (single-token mode of the fused kernel)
     __half* actp;             // [sorted pairs (+ tokens), f] fp16 hidden activations, permuted per group width
     const uint16_t* route_w;  // [tokens, top_k] fp16 bits
     const void* residual;     // [tokens, d] or NULL
@@ -63,6 +64,7 @@ struct MegaParams {
     uint64_t* trace;          // optional [n_layers][8] global-timer stamps of the phase boundaries (CTA 0)
 };
 
+constexpr size_t FAST_SMEM_LIMIT = 220 * 1024;   // dynamic shared memory the fast kernels may ask for (static use on top)
 constexpr uint32_t FAST_MAX_TOKENS = 64;   // phase 2 keeps (token, slot) x 16 partial rows in shared memory
 
 __host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits);
