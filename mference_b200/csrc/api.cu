@@ -96,7 +96,7 @@ FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens
     P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.top_k = c.top_k; P.bits = c.bits; P.shared_bits = c.shared_bits;
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
     P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
-    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.actp = a.actp; P.route_w = route_w;
+    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.dbg = nullptr; P.actp = a.actp; P.route_w = route_w;
     P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
     return P;
 }

@@ -35,8 +35,7 @@ constexpr int KS = 8;                       // k splits of a phase-1 row tile
 constexpr int RT = CW / KS;                 // 16-row tiles per phase-1 stage
 constexpr int F1_STAGES = 2;
 constexpr int F2_SLOTS = 10;                // ring depth of phase 2 (one slot = one (group, token tile))
-constexpr uint32_t ROW_PAD = 32;            // bytes added to each staged weight row: 8-byte fragment loads stay conflict free
-constexpr uint32_t ACT_PAD = 16;            // bytes added to each staged activation row: 16-byte fragment loads likewise
+constexpr uint32_t ROW_PAD = 32;            // bytes after each 8-row block of a phase-1 tile (bank stagger)
 constexpr long long MBAR_WAIT_CYCLES = 400000000ll;   // bounded spin on mbarriers: ~0.2 s at 1.9 GHz
 constexpr uint32_t MAX_GROUPS = MFB_MAX_EXPERTS + 1;
 
@@ -65,6 +64,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
         if (clock64() - t0 > MBAR_WAIT_CYCLES) return false;
+        __nanosleep(32);   // a waiting warp should not take issue slots from the computing ones
     }
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -284,6 +284,11 @@ __device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32
     __syncwarp();
 }
 
+// Optional cycle accounting of CTA 0 (attached with the phase trace): counter k of warp w at dbg[w*8 + k].
+__device__ __forceinline__ void dbg_add(unsigned long long* dbg, uint32_t warp, uint32_t lane, int k, long long t0) {
+    if (dbg && blockIdx.x == 0 && lane == 0) dbg[warp * 8 + k] += (unsigned long long)(clock64() - t0);
+}
+
 // Advances `g` until unit u lies in group g (units are visited in increasing order).
 __device__ __forceinline__ void seek_group(const uint32_t* pref, uint32_t n_groups, uint32_t u, uint32_t& g) {
     while (g + 1 < n_groups && pref[g + 1] <= u) ++g;
@@ -295,17 +300,21 @@ __device__ __forceinline__ void seek_group(const uint32_t* pref, uint32_t n_grou
 // splits meet in shared memory in a fixed order.  The 17th warp issues the bulk copies: one per row (padded
 // destination rows), one per scale block.
 struct F1Geom {
-    uint32_t tile_rows, tiles_per_group, row_stride_max, stage_bytes, groups_per_row, k_per_warp;
+    uint32_t tile_rows, tiles_per_group, blk_stride, mat_bytes, stage_bytes, groups_per_row, k_per_warp;
 };
 
 __host__ __device__ inline F1Geom f1_geom(uint32_t d, uint32_t f, uint32_t max_bits) {
     F1Geom g;
     g.tile_rows = 16 * RT;
     g.tiles_per_group = f / g.tile_rows;
-    g.row_stride_max = d * max_bits / 8 + ROW_PAD;
+    // a matrix tile of 32 rows is staged as four blocks of eight consecutive rows, one bulk copy each (the copy
+    // unit sustains only a handful of copies in flight, so copies must be kilobytes, not rows); 32 pad bytes
+    // after each block put the four rows that one shared-memory load phase touches into different banks
+    g.blk_stride = 8 * (d * max_bits / 8) + ROW_PAD;
+    g.mat_bytes = 4 * g.blk_stride;
     g.groups_per_row = d / 64;
     g.k_per_warp = d / KS;
-    g.stage_bytes = 2 * g.tile_rows * g.row_stride_max + 4 * g.tile_rows * g.groups_per_row * 2;
+    g.stage_bytes = 2 * g.mat_bytes + 4 * g.tile_rows * g.groups_per_row * 2;
     return g;
 }
 
@@ -327,21 +336,20 @@ __device__ __forceinline__ bool f1_produce(const FastParams& P, const F1Geom& ge
         return true;
     }
     const uint32_t row0 = tile * geo.tile_rows;
-    const uint32_t row_bytes = P.d * G.bits / 8, row_stride = row_bytes + ROW_PAD, gpr = geo.groups_per_row;
+    const uint32_t row_bytes = P.d * G.bits / 8, gpr = geo.groups_per_row;
     uint8_t* st = C.stages + s * geo.stage_bytes;
     const uint32_t scale_block = geo.tile_rows * gpr * 2;
     if (lane == 0) mbar_expect_tx(&C.full[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
     __syncwarp();
-    for (uint32_t r = lane; r < 2 * geo.tile_rows; r += 32) {
-        const bool up = r >= geo.tile_rows;
-        const uint32_t rr = up ? r - geo.tile_rows : r;
-        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + rr) * row_bytes;
-        bulk_g2s(st + (up ? geo.tile_rows * geo.row_stride_max : 0) + rr * row_stride, src, row_bytes, &C.full[s]);
-    }
-    if (lane < 4) {
-        const uint32_t o = lane == 0 ? G.off.gate_s : (lane == 1 ? G.off.gate_b : (lane == 2 ? G.off.up_s : G.off.up_b));
-        bulk_g2s(st + 2 * geo.tile_rows * geo.row_stride_max + lane * scale_block, G.blob + o + (size_t)row0 * gpr * 2,
-                 scale_block, &C.full[s]);
+    if (lane < 8) {          // blocks 0-3 of gate, 0-3 of up: eight consecutive rows each
+        const bool up = lane >= 4;
+        const uint32_t b = lane & 3;
+        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + 8 * b) * row_bytes;
+        bulk_g2s(st + (up ? geo.mat_bytes : 0) + b * geo.blk_stride, src, 8 * row_bytes, &C.full[s]);
+    } else if (lane < 12) {
+        const uint32_t m = lane - 8;
+        const uint32_t o = m == 0 ? G.off.gate_s : (m == 1 ? G.off.gate_b : (m == 2 ? G.off.up_s : G.off.up_b));
+        bulk_g2s(st + 2 * geo.mat_bytes + m * scale_block, G.blob + o + (size_t)row0 * gpr * 2, scale_block, &C.full[s]);
     }
     return true;
 }
@@ -368,23 +376,30 @@ __device__ __forceinline__ void f1_load_x(const FastParams& P, const GroupRef& G
     }
 }
 
+// Row of a 32-row stage tile that MMA row (row tile rt, lane group g, upper half hi) works on.
+__device__ __forceinline__ uint32_t tile_row(uint32_t rt, uint32_t g, uint32_t hi) {
+    return (g & 3) * 8 + rt * 4 + hi * 2 + (g >> 2);
+}
+
 template <int BITS, int NGW>
 __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& G, const F1Geom& geo, const uint8_t* stage,
-                                           uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], uint32_t warp,
-                                           uint32_t lane, float* red, uint32_t& red_buf) {
+                                           uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], float2 (&sx)[NGW],
+                                           bool fresh_x, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t ks = warp % KS, rt = warp / KS;
-    const uint32_t row_stride = P.d * BITS / 8 + ROW_PAD;
+    const uint32_t row_bytes = P.d * BITS / 8;
     const uint32_t gpr = geo.groups_per_row;
     const uint8_t* gate_rows = stage;
-    const uint8_t* up_rows = stage + geo.tile_rows * geo.row_stride_max;
-    const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + 2 * geo.tile_rows * geo.row_stride_max);
+    const uint8_t* up_rows = stage + geo.mat_bytes;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + 2 * geo.mat_bytes);
     const uint32_t blk = geo.tile_rows * gpr;
-    const uint32_t r_lo = rt * 16 + g, r_hi = r_lo + 8;
+    // MMA row (rt, g, +8) -> row of the 32-row tile: block g % 4, then rt, upper half, g / 4 inside the block
+    const uint32_t r_lo = tile_row(rt, g, 0), r_hi = tile_row(rt, g, 1);
+    const uint32_t a_lo = (g & 3) * geo.blk_stride + (r_lo & 7) * row_bytes, a_hi = a_lo + 2 * row_bytes;
     constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
-    const uint8_t* g_lo = gate_rows + r_lo * row_stride, *g_hi = gate_rows + r_hi * row_stride;
-    const uint8_t* u_lo = up_rows + r_lo * row_stride, *u_hi = up_rows + r_hi * row_stride;
+    const uint8_t* g_lo = gate_rows + a_lo, *g_hi = gate_rows + a_hi;
+    const uint8_t* u_lo = up_rows + a_lo, *u_hi = up_rows + a_hi;
     const uint32_t cols = min(8u, G.pair_count - tt * 8);
 
     float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
@@ -398,7 +413,8 @@ __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& 
 #pragma unroll
     for (int gi = 0; gi < NGW; ++gi) {
         const uint32_t boff = (ks * NGW + gi) * group_bytes + t * lane_bytes;
-        const float2 sxv = group_sum(bf[gi]);
+        if (fresh_x) sx[gi] = group_sum(bf[gi]);   // the sums stay valid for every row tile of this token tile
+        const float2 sxv = sx[gi];
         group_mma<BITS>(g_lo, g_hi, boff, bf[gi], sr[0].at(gi, sdt), sr[2].at(gi, sdt), sr[1].at(gi, sdt), sr[3].at(gi, sdt), sxv, ag);
         group_mma<BITS>(u_lo, u_hi, boff, bf[gi], sr[4].at(gi, sdt), sr[6].at(gi, sdt), sr[5].at(gi, sdt), sr[7].at(gi, sdt), sxv, au);
     }
@@ -426,7 +442,7 @@ __device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& 
             }
             float a = hidden_act(gsum, (int)P.activation) * usum;
             a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-            const uint32_t r = tile * geo.tile_rows + ort * 16 + row;
+            const uint32_t r = tile * geo.tile_rows + tile_row(ort, row & 7, row >> 3);
             const uint32_t pos = (r & ~15u) + perm_pos(r & 15u, G.bits);
             P.actp[(size_t)(G.pair_start + tt * 8 + n) * P.f + pos] = __float2half_rn(a);
         }
@@ -446,10 +462,13 @@ __device__ __forceinline__ bool phase1(const FastParams& P, const F1Geom& geo, c
         for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
             seek_group(C.pref1, n_groups, u, g);
             const GroupRef G = group_ref(P, g);
+            const long long t0 = clock64();
             ok = f1_produce(P, geo, C, G, (u - C.pref1[g]) % geo.tiles_per_group, local_seq, lane);
+            dbg_add(P.dbg, warp, lane, 0, t0);
         }
     } else {
         uint32_t bf[NGW][8];
+        float2 sx[NGW];
         uint32_t cached = 0xFFFFFFFFu, red_buf = 0;
         const uint32_t k0 = (warp % KS) * geo.k_per_warp;
         for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
@@ -457,15 +476,20 @@ __device__ __forceinline__ bool phase1(const FastParams& P, const F1Geom& geo, c
             const GroupRef G = group_ref(P, g);
             const uint32_t local = u - C.pref1[g], tt = local / geo.tiles_per_group, tile = local % geo.tiles_per_group;
             const uint32_t key = g * 16 + tt;
-            if (G.ok && key != cached) { f1_load_x<NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
+            const bool fresh_x = G.ok && key != cached;
+            if (fresh_x) { f1_load_x<NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
             const uint32_t s = local_seq % F1_STAGES, ph = (local_seq / F1_STAGES) & 1u;
+            long long t0 = clock64();
             if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+            dbg_add(P.dbg, warp, lane, 0, t0);
+            t0 = clock64();
             if (G.ok) {
                 const uint8_t* st = C.stages + s * geo.stage_bytes;
-                if (G.bits == 4) f1_compute<4, NGW>(P, G, geo, st, tile, tt, bf, warp, lane, C.red, red_buf);
-                else f1_compute<2, NGW>(P, G, geo, st, tile, tt, bf, warp, lane, C.red, red_buf);
+                if (G.bits == 4) f1_compute<4, NGW>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                else f1_compute<2, NGW>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
             }
             __syncwarp();
+            dbg_add(P.dbg, warp, lane, 1, t0);
             if (lane == 0) mbar_arrive(&C.empty[s]);
         }
     }
@@ -486,9 +510,9 @@ struct F2Geom {
 
 __host__ __device__ inline F2Geom f2_geom(uint32_t f, uint32_t max_bits) {
     F2Geom g;
-    g.row_stride_max = f * max_bits / 8 + ROW_PAD;
+    g.row_stride_max = f * max_bits / 8;   // rows stay contiguous: one warp computes a unit, so bank conflicts cost little
     g.gpr = f / 64;
-    g.act_stride = f * 2 + ACT_PAD;
+    g.act_stride = f * 2;
     g.scale_off = 16 * g.row_stride_max;
     g.act_off = g.scale_off + 2 * 16 * g.gpr * 2;
     g.slot_bytes = (g.act_off + 8 * g.act_stride + 127u) & ~127u;
@@ -503,31 +527,55 @@ struct Phase2Ctx {
     const uint32_t* pref2;
 };
 
-__device__ __forceinline__ bool f2_produce(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, const GroupRef& G,
-                                           uint32_t tt, uint32_t row0, uint32_t seq, uint32_t lane) {
-    const uint32_t s = seq % F2_SLOTS, ph = (seq / F2_SLOTS) & 1u;
-    if (!mbar_wait(&C.empty[s], ph ^ 1u)) return false;
-    if (!G.ok) { if (lane == 0) mbar_arrive(&C.full[s]); return true; }
-    const uint32_t row_bytes = P.f * G.bits / 8, row_stride = row_bytes + ROW_PAD, scale_block = 16 * geo.gpr * 2;
-    const uint32_t cols = min(8u, G.pair_count - tt * 8);
-    uint8_t* st = C.slots + s * geo.slot_bytes;
-    if (lane == 0) mbar_expect_tx(&C.full[s], 16 * row_bytes + 2 * scale_block + cols * P.f * 2);
-    __syncwarp();
-    if (lane < 16) bulk_g2s(st + lane * row_stride, G.blob + G.off.down_w + (size_t)(row0 + lane) * row_bytes, row_bytes, &C.full[s]);
-    else if (lane < 18)
-        bulk_g2s(st + geo.scale_off + (lane - 16) * scale_block,
-                 G.blob + (lane == 16 ? G.off.down_s : G.off.down_b) + (size_t)row0 * geo.gpr * 2, scale_block, &C.full[s]);
-    else if (lane - 18 < cols)
-        bulk_g2s(st + geo.act_off + (lane - 18) * geo.act_stride, P.actp + (size_t)(G.pair_start + tt * 8 + lane - 18) * P.f,
-                 P.f * 2, &C.full[s]);
-    return true;
+// Copy-issuing side of up to eight consecutive units at once: lanes 4j..4j+3 of the issuing warp serve unit
+// first_unit + j (wait for its slot, post the byte count, then one copy per lane: the 16 contiguous rows, their
+// scales, their biases, the token tile's activation rows).  Issuing is latency bound per unit, so the eight units
+// of a pass overlap their waits and address arithmetic.  `g` is this lane's group cursor.
+__device__ __forceinline__ bool f2_produce8(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, uint32_t n_groups,
+                                            uint32_t n_units, uint32_t first_unit, uint32_t row0, uint32_t seq, uint32_t lane,
+                                            uint32_t& g) {
+    const uint32_t u = first_unit + (lane >> 2), role = lane & 3;
+    const bool active = u < n_units;
+    bool ok = true, copy = false;
+    GroupRef G;
+    uint32_t s = 0, tt = 0;
+    if (active) {
+        seek_group(C.pref2, n_groups, u, g);
+        G = group_ref(P, g);
+        tt = u - C.pref2[g];
+        s = (seq + u) % F2_SLOTS;
+        ok = mbar_wait(&C.empty[s], (((seq + u) / F2_SLOTS) & 1u) ^ 1u);
+        copy = ok && G.ok;
+        if (ok && role == 0) {
+            if (G.ok) {
+                const uint32_t cols = min(8u, G.pair_count - tt * 8);
+                mbar_expect_tx(&C.full[s], 16 * (P.f * G.bits / 8) + 2 * (16 * geo.gpr * 2) + cols * P.f * 2);
+            } else {
+                mbar_arrive(&C.full[s]);   // nothing to copy: complete the phase so the consumer moves on
+            }
+        }
+    }
+    __syncwarp();   // every byte count is posted before any copy of this pass is issued
+    if (copy) {
+        const uint32_t row_bytes = P.f * G.bits / 8, scale_block = 16 * geo.gpr * 2;
+        uint8_t* st = C.slots + s * geo.slot_bytes;
+        if (role == 0) bulk_g2s(st, G.blob + G.off.down_w + (size_t)row0 * row_bytes, 16 * row_bytes, &C.full[s]);
+        else if (role < 3)
+            bulk_g2s(st + geo.scale_off + (role - 1) * scale_block,
+                     G.blob + (role == 1 ? G.off.down_s : G.off.down_b) + (size_t)row0 * geo.gpr * 2, scale_block, &C.full[s]);
+        else {
+            const uint32_t cols = min(8u, G.pair_count - tt * 8);
+            bulk_g2s(st + geo.act_off, P.actp + (size_t)(G.pair_start + tt * 8) * P.f, cols * P.f * 2, &C.full[s]);
+        }
+    }
+    return __all_sync(0xFFFFFFFFu, ok);
 }
 
 template <int BITS, int NG>
 __device__ __forceinline__ void f2_compute(const FastParams& P, const F2Geom& geo, const GroupRef& G, uint32_t tt,
                                            const uint8_t* st, uint32_t lane, float* part, uint32_t slots) {
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t row_stride = P.f * BITS / 8 + ROW_PAD;
+    const uint32_t row_stride = P.f * BITS / 8;
     const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + geo.scale_off);
     constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
@@ -577,9 +625,10 @@ __device__ __forceinline__ bool phase2(const FastParams& P, const F2Geom& geo, c
     uint32_t g = 0;
     if (warp == CW) {
         fence_proxy_async();
-        for (uint32_t u = 0; u < n_units && ok; ++u) {
-            seek_group(C.pref2, n_groups, u, g);
-            ok = f2_produce(P, geo, C, group_ref(P, g), u - C.pref2[g], row0, seq + u, lane);
+        for (uint32_t u = 0; u < n_units && ok; u += 8) {
+            const long long t0 = clock64();
+            ok = f2_produce8(P, geo, C, n_groups, n_units, u, row0, seq, lane, g);
+            dbg_add(P.dbg, warp, lane, 2, t0);
         }
     } else if (warp < (uint32_t)F2_SLOTS) {
         // Compute warp w serves slot w only, so its waits on that slot's barriers follow each other in phase order.
@@ -590,13 +639,17 @@ __device__ __forceinline__ bool phase2(const FastParams& P, const F2Geom& geo, c
             seek_group(C.pref2, n_groups, u, g);
             const GroupRef G = group_ref(P, g);
             const uint32_t s = (seq + u) % F2_SLOTS, ph = ((seq + u) / F2_SLOTS) & 1u;
+            long long t0 = clock64();
             if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+            dbg_add(P.dbg, warp, lane, 2, t0);
+            t0 = clock64();
             if (G.ok) {
                 const uint8_t* st = C.slots + s * geo.slot_bytes;
                 if (G.bits == 4) f2_dispatch<4>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
                 else f2_dispatch<2>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
             }
             __syncwarp();
+            dbg_add(P.dbg, warp, lane, 3, t0);
             if (lane == 0) mbar_arrive(&C.empty[s]);
         }
     }
@@ -1039,6 +1092,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         P.xp = single ? xp_s : M.xp; P.xp_shared = single ? (M.xp2 ? xp2_s : xp_s) : (M.xp2 ? M.xp2 : M.xp);
         P.x_in_smem = single ? 1 : 0;
         P.actp = M.actp; P.route_w = w_s;
+        P.dbg = M.trace ? reinterpret_cast<unsigned long long*>(M.trace + (size_t)M.n_layers * 8) : nullptr;
         P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
         stamp(4);
 

@@ -26,6 +26,7 @@ struct FastParams {
     int x_dtype;
     uint32_t n_tokens;
     uint32_t* status;
+    unsigned long long* dbg;  // optional cycle counters of CTA 0: [17 warps][8] (wait / compute per phase), or NULL
 };
 
 // Per-layer weights as the fused stack kernel reads them (device array, one entry per layer).
@@ -61,7 +62,8 @@ struct MegaParams {
     uint32_t* bar_counter;    // [2]: arrivals, abort word (zeroed before every launch)
     uint32_t* abort;
     uint32_t* status;
-    uint64_t* trace;          // optional [n_layers][8] global-timer stamps of the phase boundaries (CTA 0)
+    uint64_t* trace;          // optional [n_layers][8] global-timer stamps of the phase boundaries (CTA 0), followed by
+                              // [17][8] cycle counters (per warp of CTA 0: phase-1 wait, phase-1 compute, phase-2 wait, phase-2 compute)
 };
 
 constexpr size_t FAST_SMEM_LIMIT = 220 * 1024;   // dynamic shared memory the fast kernels may ask for (static use on top)
