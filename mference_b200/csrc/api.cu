@@ -96,7 +96,7 @@ FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens
     P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.top_k = c.top_k; P.bits = c.bits; P.shared_bits = c.shared_bits;
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
     P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
-    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.dbg = nullptr; P.actp = a.actp; P.route_w = route_w;
+    P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.dbg = nullptr; P.actp = a.actp; P.partial = a.partial; P.route_w = route_w;
     P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
     return P;
 }
@@ -354,6 +354,8 @@ extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_we
                               a.offsets, a.counts, a.groups, a.n_groups, nullptr));
         const FastParams P = fast_params(moe, w, n_tokens, route_w, residual, y);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        MFB_CUDA(launch_combine(s, a.partial, route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, residual, y,
+                                (int)c.x_dtype));
         return MFB_OK;
     }
     int32_t rc = mfb_moe_experts(moe, stream, w, x, ldx, n_tokens, idx, route_w, nullptr, 0, 1);
@@ -383,6 +385,8 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
                                     a.idx, a.route_w, a.sorted, a.groups, a.n_groups));
         const FastParams P = fast_params(moe, w, n_tokens, a.route_w, h_in, h_out);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        MFB_CUDA(launch_combine(s, a.partial, a.route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, h_in, h_out,
+                                (int)c.x_dtype));
         return MFB_OK;
     }
     MFB_CUDA(launch_rmsnorm(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, a.xn, (int)c.x_dtype));
@@ -445,7 +449,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
         M.scale_dtype = c.scale_dtype; M.activation = c.activation; M.router_mode = (int)c.router_mode; M.x_dtype = (int)c.x_dtype;
         M.limit = c.swiglu_limit; M.route_scale = c.route_scale; M.eps = c.rms_eps;
         M.hidden = rows; M.layer_stride = layer_stride; M.n_tokens = n_tokens;
-        M.xn = a.xn; M.xp = a.xp; M.xp2 = a.xp2; M.logits = a.logits; M.idx = a.idx; M.route_w = a.route_w; M.actp = a.actp;
+        M.xn = a.xn; M.xp = a.xp; M.xp2 = a.xp2; M.logits = a.logits; M.idx = a.idx; M.route_w = a.route_w; M.actp = a.actp; M.partial = a.partial;
         M.bar_counter = moe->mega_bar; M.abort = moe->mega_bar + 1; M.status = a.status; M.trace = moe->trace;
         MFB_CUDA(launch_stack_mega(s, M, c, moe->sm_count));
         return MFB_OK;

@@ -29,13 +29,12 @@ namespace mfb {
 
 namespace {
 
-constexpr int CW = 16;                      // compute warps per CTA
+constexpr int CW = 8;                       // compute warps per CTA
 constexpr int FAST_THREADS = (CW + 1) * 32; // + one copy-issuing warp
-constexpr int KS = 8;                       // k splits of a phase-1 row tile
-constexpr int RT = CW / KS;                 // 16-row tiles per phase-1 stage
-constexpr int F1_STAGES = 2;
-constexpr int F2_SLOTS = 10;                // ring depth of phase 2 (one slot = one (group, token tile))
-constexpr uint32_t ROW_PAD = 32;            // bytes after each 8-row block of a phase-1 tile (bank stagger)
+constexpr int MAX_STAGES = 4;               // ring depth limit of a phase
+constexpr uint32_t RING_BYTES = 150 * 1024; // shared memory of the stage ring (both phases use the same region)
+constexpr uint32_t RED_BYTES = 2 * CW * 2 * 2 * 128 * 4;   // two exchange buffers for the k-split partial sums
+constexpr uint32_t ROW_PAD = 32;            // bytes after each block of staged rows (bank stagger)
 constexpr long long MBAR_WAIT_CYCLES = 400000000ll;   // bounded spin on mbarriers: ~0.2 s at 1.9 GHz
 constexpr uint32_t MAX_GROUPS = MFB_MAX_EXPERTS + 1;
 
@@ -261,8 +260,8 @@ struct ScaleRow {
 // ------------------------------------------------------------------------------------------ work lists
 // A unit of work is one (group, token tile of up to 8 rows[, 32-row tile of gate/up]).  Exclusive prefix sums of
 // the units of each group, by one warp: pref1[g] counts phase-1 units, pref2[g] phase-2 units.
-__device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32_t n_groups, uint32_t tiles_per_group,
-                                                 uint32_t* pref1, uint32_t* pref2, uint32_t lane) {
+__device__ __forceinline__ void warp_unit_prefix2(const mfb_group* groups, uint32_t n_groups, uint32_t tiles1, uint32_t tiles2,
+                                                  uint32_t* pref1, uint32_t* pref2, uint32_t lane) {
     const uint32_t per = (n_groups + 31) / 32, g0 = lane * per;
     uint32_t local = 0;
     for (uint32_t j = 0; j < per; ++j)
@@ -275,13 +274,17 @@ __device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32
     uint32_t run = incl - local;
     for (uint32_t j = 0; j < per; ++j)
         if (g0 + j < n_groups) {
-            pref2[g0 + j] = run;
-            pref1[g0 + j] = run * tiles_per_group;
+            pref1[g0 + j] = run * tiles1;
+            pref2[g0 + j] = run * tiles2;
             run += (groups[g0 + j].pair_count + 7) / 8;
         }
     const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-    if (lane == 0) { pref2[n_groups] = total; pref1[n_groups] = total * tiles_per_group; }
+    if (lane == 0) { pref1[n_groups] = total * tiles1; pref2[n_groups] = total * tiles2; }
     __syncwarp();
+}
+__device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32_t n_groups, uint32_t tiles, uint32_t* pref1,
+                                                 uint32_t* pref2, uint32_t lane) {
+    warp_unit_prefix2(groups, n_groups, tiles, tiles, pref1, pref2, lane);
 }
 
 // Optional cycle accounting of CTA 0 (attached with the phase trace): counter k of warp w at dbg[w*8 + k].
@@ -294,81 +297,111 @@ __device__ __forceinline__ void seek_group(const uint32_t* pref, uint32_t n_grou
     while (g + 1 < n_groups && pref[g + 1] <= u) ++g;
 }
 
-// ------------------------------------------------------------------------------------------ phase 1
-// Stage = 32 rows of gate and 32 rows of up of one expert (+ their scales and biases).  Warp w of the 16 compute
-// warps owns k range [ks*d/8, (ks+1)*d/8) (ks = w % 8) of row tile rt = w / 8; the partial sums of the eight k
-// splits meet in shared memory in a fixed order.  The 17th warp issues the bulk copies: one per row (padded
-// destination rows), one per scale block.
-struct F1Geom {
-    uint32_t tile_rows, tiles_per_group, blk_stride, mat_bytes, stage_bytes, groups_per_row, k_per_warp;
+// ------------------------------------------------------------------------------------------ one FFN phase
+// Both matrix phases of the expert FFN run through the same machinery:
+//   phase 1  NMAT = 2 (gate, up), contraction over d, rows = f, epilogue act(gate) * up -> fp16 hidden activations
+//   phase 2  NMAT = 1 (down),     contraction over f, rows = d, epilogue -> fp32 rows of the (token, slot) partials
+// A unit of work is one (group, token tile of <= 8 rows, tile of `tile_rows` matrix rows).  The copy warp stages the
+// tile: each matrix as four blocks of consecutive rows, one bulk copy per block (kilobytes each: the copy unit
+// sustains only a few copies in flight), 32 pad bytes after a block so that the four rows one shared-memory load
+// phase touches fall into different banks; plus one copy per scale / bias block.  The eight compute warps split
+// the tile as (k split) x (row group); every warp works on RPW = 2 sixteen-row MMA tiles with the same activation
+// fragments, which gives the scheduler independent MMA chains to interleave.  Partial sums of the k splits meet
+// in shared memory and are added in a fixed order.
+constexpr int RPW = 2;   // 16-row MMA tiles per warp
+
+struct PhaseGeom {
+    uint32_t k, n_rows, ksplit, row_groups, tile_rows, tiles, blk_rows, blk_stride, mat_bytes, gpr, scale_block,
+        stage_bytes, k_per_warp, n_stages;
 };
 
-__host__ __device__ inline F1Geom f1_geom(uint32_t d, uint32_t f, uint32_t max_bits) {
-    F1Geom g;
-    g.tile_rows = 16 * RT;
-    g.tiles_per_group = f / g.tile_rows;
-    // a matrix tile of 32 rows is staged as four blocks of eight consecutive rows, one bulk copy each (the copy
-    // unit sustains only a handful of copies in flight, so copies must be kilobytes, not rows); 32 pad bytes
-    // after each block put the four rows that one shared-memory load phase touches into different banks
-    g.blk_stride = 8 * (d * max_bits / 8) + ROW_PAD;
+__host__ __device__ inline PhaseGeom phase_geom(uint32_t nmat, uint32_t k, uint32_t n_rows, uint32_t ngw, uint32_t max_bits,
+                                                uint32_t ring_bytes) {
+    PhaseGeom g;
+    g.k = k; g.n_rows = n_rows;
+    g.gpr = k / 64;
+    g.ksplit = g.gpr / ngw;
+    g.row_groups = CW / g.ksplit;
+    g.tile_rows = 16 * RPW * g.row_groups;
+    g.tiles = n_rows / g.tile_rows;
+    g.blk_rows = g.tile_rows / 4;
+    g.blk_stride = g.blk_rows * (k * max_bits / 8) + ROW_PAD;
     g.mat_bytes = 4 * g.blk_stride;
-    g.groups_per_row = d / 64;
-    g.k_per_warp = d / KS;
-    g.stage_bytes = 2 * g.mat_bytes + 4 * g.tile_rows * g.groups_per_row * 2;
+    g.scale_block = g.tile_rows * g.gpr * 2;
+    g.stage_bytes = nmat * g.mat_bytes + 2 * nmat * g.scale_block;
+    g.k_per_warp = ngw * 64;
+    const uint32_t fit = ring_bytes / g.stage_bytes;
+    g.n_stages = fit > MAX_STAGES ? MAX_STAGES : fit;
     return g;
 }
 
-struct Phase1Ctx {
-    uint8_t* stages;
-    uint64_t* full;     // [F1_STAGES]
-    uint64_t* empty;    // [F1_STAGES]
-    float* red;         // [2][CW*32*8]
-    const uint32_t* pref1;
+struct PhaseCtx {
+    uint8_t* ring;       // n_stages * stage_bytes
+    uint64_t* full;      // [MAX_STAGES]
+    uint64_t* empty;     // [MAX_STAGES]
+    float* red;          // [2][CW * RPW * 2 * 128]
+    const uint32_t* pref;   // exclusive prefix of units per group, pref[n_groups] = total
 };
 
+// Row of a stage tile that MMA row (row tile rtile of the stage, lane group g, upper half hi) works on:
+// block g % 4, then four rows per row tile inside the block.
+__device__ __forceinline__ uint32_t tile_row(uint32_t blk_rows, uint32_t rtile, uint32_t g, uint32_t hi) {
+    return (g & 3) * blk_rows + rtile * 4 + hi * 2 + (g >> 2);
+}
+
 // Copy-issuing side of one unit (all 32 lanes of the issuing warp call this).
-__device__ __forceinline__ bool f1_produce(const FastParams& P, const F1Geom& geo, const Phase1Ctx& C, const GroupRef& G,
-                                           uint32_t tile, uint32_t seq, uint32_t lane) {
-    const uint32_t s = seq % F1_STAGES, ph = (seq / F1_STAGES) & 1u;
+template <int NMAT>
+__device__ __forceinline__ bool phase_produce(const FastParams& P, const PhaseGeom& geo, const PhaseCtx& C, const GroupRef& G,
+                                              uint32_t tile, uint32_t seq, uint32_t lane) {
+    const uint32_t s = seq % geo.n_stages, ph = (seq / geo.n_stages) & 1u;
     if (!mbar_wait(&C.empty[s], ph ^ 1u)) return false;
     if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
         if (lane == 0) mbar_arrive(&C.full[s]);
         return true;
     }
-    const uint32_t row0 = tile * geo.tile_rows;
-    const uint32_t row_bytes = P.d * G.bits / 8, gpr = geo.groups_per_row;
-    uint8_t* st = C.stages + s * geo.stage_bytes;
-    const uint32_t scale_block = geo.tile_rows * gpr * 2;
-    if (lane == 0) mbar_expect_tx(&C.full[s], 2 * geo.tile_rows * row_bytes + 4 * scale_block);
+    const uint32_t row0 = tile * geo.tile_rows, row_bytes = geo.k * G.bits / 8;
+    uint8_t* st = C.ring + s * geo.stage_bytes;
+    if (lane == 0) mbar_expect_tx(&C.full[s], NMAT * geo.tile_rows * row_bytes + 2 * NMAT * geo.scale_block);
     __syncwarp();
-    if (lane < 8) {          // blocks 0-3 of gate, 0-3 of up: eight consecutive rows each
-        const bool up = lane >= 4;
-        const uint32_t b = lane & 3;
-        const uint8_t* src = G.blob + (up ? G.off.up_w : G.off.gate_w) + (size_t)(row0 + 8 * b) * row_bytes;
-        bulk_g2s(st + (up ? geo.mat_bytes : 0) + b * geo.blk_stride, src, 8 * row_bytes, &C.full[s]);
-    } else if (lane < 12) {
-        const uint32_t m = lane - 8;
-        const uint32_t o = m == 0 ? G.off.gate_s : (m == 1 ? G.off.gate_b : (m == 2 ? G.off.up_s : G.off.up_b));
-        bulk_g2s(st + 2 * geo.mat_bytes + m * scale_block, G.blob + o + (size_t)row0 * gpr * 2, scale_block, &C.full[s]);
+    const uint32_t* off = &G.off.gate_w;   // gate W,S,B, up W,S,B, down W,S,B
+    if (lane < 4 * NMAT) {
+        const uint32_t m = lane >> 2, b = lane & 3;
+        const uint32_t w_off = NMAT == 2 ? off[3 * m] : off[6];
+        bulk_g2s(st + m * geo.mat_bytes + b * geo.blk_stride, G.blob + w_off + (size_t)(row0 + b * geo.blk_rows) * row_bytes,
+                 geo.blk_rows * row_bytes, &C.full[s]);
+    } else if (lane < 6 * NMAT) {
+        const uint32_t i = lane - 4 * NMAT, m = i >> 1, sb = i & 1;    // scale / bias of matrix m
+        const uint32_t s_off = NMAT == 2 ? off[3 * m + 1 + sb] : off[7 + sb];
+        bulk_g2s(st + NMAT * geo.mat_bytes + i * geo.scale_block, G.blob + s_off + (size_t)row0 * geo.gpr * 2, geo.scale_block,
+                 &C.full[s]);
     }
     return true;
 }
 
-// B fragments of this warp's k range for token column g of a token tile (registers, loaded from L2 or, in the
-// single-token mode of the fused kernel, from shared memory).
-template <int NGW>
-__device__ __forceinline__ void f1_load_x(const FastParams& P, const GroupRef& G, uint32_t tt, uint32_t k0, uint32_t lane,
-                                          uint32_t (&bf)[NGW][8]) {
+// B fragments of this warp's k range for token column g of a token tile: registers, loaded from L2 (or from shared
+// memory in the single-token mode of the fused kernel).  Phase 1 reads the permuted activations of the group's
+// tokens, phase 2 the hidden activations phase 1 left for the group's sorted pairs.
+template <int NMAT, int NGW>
+__device__ __forceinline__ void phase_load_x(const FastParams& P, const GroupRef& G, uint32_t tt, uint32_t k0, uint32_t lane,
+                                             uint32_t (&bf)[NGW][8]) {
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t cols = min(8u, G.pair_count - tt * 8);
-    const __half* xsrc = (G.shared && P.shared_bits != P.bits) ? P.xp_shared : P.xp;
     const __half* row = nullptr;
-    if (g < cols) row = xsrc + (size_t)P.sorted[G.pair_start + tt * 8 + g].token * P.d + k0 + t * 16;
+    bool smem_src = false;
+    if (g < cols) {
+        if (NMAT == 2) {
+            const __half* xsrc = (G.shared && P.shared_bits != P.bits) ? P.xp_shared : P.xp;
+            row = xsrc + (size_t)P.sorted[G.pair_start + tt * 8 + g].token * P.d + k0 + t * 16;
+            smem_src = P.x_in_smem != 0;
+        } else {
+            row = P.actp + (size_t)(G.pair_start + tt * 8 + g) * P.f + k0 + t * 16;
+        }
+    }
 #pragma unroll
     for (int gi = 0; gi < NGW; ++gi) {
         uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
         if (row) {
-            if (P.x_in_smem) { lo = *reinterpret_cast<const uint4*>(row + gi * 64); hi = *reinterpret_cast<const uint4*>(row + gi * 64 + 8); }
+            if (smem_src) { lo = *reinterpret_cast<const uint4*>(row + gi * 64); hi = *reinterpret_cast<const uint4*>(row + gi * 64 + 8); }
             else { lo = ld_cg_u4(row + gi * 64); hi = ld_cg_u4(row + gi * 64 + 8); }
         }
         bf[gi][0] = lo.x; bf[gi][1] = lo.y; bf[gi][2] = lo.z; bf[gi][3] = lo.w;
@@ -376,120 +409,140 @@ __device__ __forceinline__ void f1_load_x(const FastParams& P, const GroupRef& G
     }
 }
 
-// Row of a 32-row stage tile that MMA row (row tile rt, lane group g, upper half hi) works on.
-__device__ __forceinline__ uint32_t tile_row(uint32_t rt, uint32_t g, uint32_t hi) {
-    return (g & 3) * 8 + rt * 4 + hi * 2 + (g >> 2);
-}
-
-template <int BITS, int NGW>
-__device__ __forceinline__ void f1_compute(const FastParams& P, const GroupRef& G, const F1Geom& geo, const uint8_t* stage,
-                                           uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], float2 (&sx)[NGW],
-                                           bool fresh_x, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
+// Compute side of one unit by one warp: RPW row tiles x NMAT matrices x NGW groups of this warp's k range, then the
+// exchange of the k-split partial sums and the epilogue.
+template <int NMAT, int NGW, int BITS>
+__device__ __forceinline__ void phase_compute(const FastParams& P, const GroupRef& G, const PhaseGeom& geo, const uint8_t* stage,
+                                              uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], float2 (&sx)[NGW],
+                                              bool fresh_x, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t ks = warp % KS, rt = warp / KS;
-    const uint32_t row_bytes = P.d * BITS / 8;
-    const uint32_t gpr = geo.groups_per_row;
-    const uint8_t* gate_rows = stage;
-    const uint8_t* up_rows = stage + geo.mat_bytes;
-    const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + 2 * geo.mat_bytes);
-    const uint32_t blk = geo.tile_rows * gpr;
-    // MMA row (rt, g, +8) -> row of the 32-row tile: block g % 4, then rt, upper half, g / 4 inside the block
-    const uint32_t r_lo = tile_row(rt, g, 0), r_hi = tile_row(rt, g, 1);
-    const uint32_t a_lo = (g & 3) * geo.blk_stride + (r_lo & 7) * row_bytes, a_hi = a_lo + 2 * row_bytes;
+    const uint32_t ksi = warp % geo.ksplit, rg = warp / geo.ksplit;
+    const uint32_t row_bytes = geo.k * BITS / 8, gpr = geo.gpr;
+    const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + NMAT * geo.mat_bytes);
+    const uint32_t sblk = geo.tile_rows * gpr;
     constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
     const int sdt = (int)P.scale_dtype;
-    const uint8_t* g_lo = gate_rows + a_lo, *g_hi = gate_rows + a_hi;
-    const uint8_t* u_lo = up_rows + a_lo, *u_hi = up_rows + a_hi;
     const uint32_t cols = min(8u, G.pair_count - tt * 8);
 
-    float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
-    // scales and biases of this warp's NGW groups, rows r_lo / r_hi of gate_s, gate_b, up_s, up_b
-    ScaleRow<NGW> sr[8];
+    if (fresh_x) {
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        sr[2 * m].load(sc + m * blk + r_lo * gpr + ks * NGW);
-        sr[2 * m + 1].load(sc + m * blk + r_hi * gpr + ks * NGW);
+        for (int gi = 0; gi < NGW; ++gi) sx[gi] = group_sum(bf[gi]);   // valid for every row tile of this token tile
     }
+    float acc[RPW][NMAT][4];
 #pragma unroll
-    for (int gi = 0; gi < NGW; ++gi) {
-        const uint32_t boff = (ks * NGW + gi) * group_bytes + t * lane_bytes;
-        if (fresh_x) sx[gi] = group_sum(bf[gi]);   // the sums stay valid for every row tile of this token tile
-        const float2 sxv = sx[gi];
-        group_mma<BITS>(g_lo, g_hi, boff, bf[gi], sr[0].at(gi, sdt), sr[2].at(gi, sdt), sr[1].at(gi, sdt), sr[3].at(gi, sdt), sxv, ag);
-        group_mma<BITS>(u_lo, u_hi, boff, bf[gi], sr[4].at(gi, sdt), sr[6].at(gi, sdt), sr[5].at(gi, sdt), sr[7].at(gi, sdt), sxv, au);
-    }
-    // partial sums of this warp -> shared memory, then a fixed-order sum over the k splits
-    float* rb = red + red_buf * (CW * 32 * 8);
-    float4* dst = reinterpret_cast<float4*>(rb + ((ks * RT + rt) * 32 + lane) * 8);
-    dst[0] = make_float4(ag[0], ag[1], ag[2], ag[3]);
-    dst[1] = make_float4(au[0], au[1], au[2], au[3]);
-    named_barrier(1, CW * 32);
-    const uint32_t o = warp * 32 + lane;
-    if (o < RT * 128) {
-        const uint32_t ort = o >> 7, row = (o & 127) >> 3, n = o & 7;
-        const uint32_t src_lane = (row & 7) * 4 + (n >> 1), reg = (row >> 3) * 2 + (n & 1);
-        float gsum = 0.0f, usum = 0.0f;
+    for (int j = 0; j < RPW; ++j) {
+        const uint32_t rtile = rg * RPW + j;
+        const uint32_t r_lo = tile_row(geo.blk_rows, rtile, g, 0), r_hi = r_lo + 2;
+        const uint32_t a_lo = (g & 3) * geo.blk_stride + (r_lo - (g & 3) * geo.blk_rows) * row_bytes, a_hi = a_lo + 2 * row_bytes;
+        ScaleRow<NGW> sr[NMAT][4];   // [matrix][scale lo, scale hi, bias lo, bias hi] for this warp's groups
 #pragma unroll
-        for (uint32_t k = 0; k < KS; ++k) {
-            const float* src = rb + ((k * RT + ort) * 32 + src_lane) * 8;
-            gsum += src[reg];
-            usum += src[4 + reg];
+        for (int m = 0; m < NMAT; ++m) {
+            sr[m][0].load(sc + (2 * m) * sblk + r_lo * gpr + ksi * NGW);
+            sr[m][1].load(sc + (2 * m) * sblk + r_hi * gpr + ksi * NGW);
+            sr[m][2].load(sc + (2 * m + 1) * sblk + r_lo * gpr + ksi * NGW);
+            sr[m][3].load(sc + (2 * m + 1) * sblk + r_hi * gpr + ksi * NGW);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[j][m][c] = 0.0f;
         }
-        if (n < cols) {
+#pragma unroll
+        for (int gi = 0; gi < NGW; ++gi) {
+            const uint32_t boff = (ksi * NGW + gi) * group_bytes + t * lane_bytes;
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+                group_mma<BITS>(stage + m * geo.mat_bytes + a_lo, stage + m * geo.mat_bytes + a_hi, boff, bf[gi],
+                                sr[m][0].at(gi, sdt), sr[m][2].at(gi, sdt), sr[m][1].at(gi, sdt), sr[m][3].at(gi, sdt), sx[gi],
+                                acc[j][m]);
+        }
+    }
+    // partial sums of this warp -> shared memory; fixed-order sum over the k splits by whoever owns the output
+    constexpr uint32_t PER_TILE = NMAT * 128;    // floats one (k split, row tile) leaves: [matrix][lane][4]
+    const uint32_t n_rtiles = geo.row_groups * RPW;
+    float* rb = red + red_buf * (CW * RPW * 2 * 128);
+#pragma unroll
+    for (int j = 0; j < RPW; ++j)
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+            *reinterpret_cast<float4*>(rb + ((ksi * n_rtiles + rg * RPW + j) * PER_TILE) + m * 128 + lane * 4) =
+                make_float4(acc[j][m][0], acc[j][m][1], acc[j][m][2], acc[j][m][3]);
+    named_barrier(1, CW * 32);
+    for (uint32_t o = warp * 32 + lane; o < n_rtiles * 128; o += CW * 32) {
+        const uint32_t rtile = o >> 7, row16 = (o & 127) >> 3, n = o & 7;
+        if (n >= cols) continue;
+        const uint32_t src = ((row16 & 7) * 4 + (n >> 1)) * 4 + (row16 >> 3) * 2 + (n & 1);
+        float v[NMAT];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) v[m] = 0.0f;
+        for (uint32_t k = 0; k < geo.ksplit; ++k)
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) v[m] += rb[(k * n_rtiles + rtile) * PER_TILE + m * 128 + src];
+        const uint32_t r = tile * geo.tile_rows + tile_row(geo.blk_rows, rtile, row16 & 7, row16 >> 3);
+        const uint32_t pair = G.pair_start + tt * 8 + n;
+        if (NMAT == 2) {
+            float gate = v[0], up = v[NMAT - 1];
             if (!G.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
-                gsum = fminf(gsum, P.limit);
-                usum = fminf(fmaxf(usum, -P.limit), P.limit);
+                gate = fminf(gate, P.limit);
+                up = fminf(fmaxf(up, -P.limit), P.limit);
             }
-            float a = hidden_act(gsum, (int)P.activation) * usum;
+            float a = hidden_act(gate, (int)P.activation) * up;
             a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-            const uint32_t r = tile * geo.tile_rows + tile_row(ort, row & 7, row >> 3);
-            const uint32_t pos = (r & ~15u) + perm_pos(r & 15u, G.bits);
-            P.actp[(size_t)(G.pair_start + tt * 8 + n) * P.f + pos] = __float2half_rn(a);
+            P.actp[(size_t)pair * P.f + (r & ~15u) + perm_pos(r & 15u, G.bits)] = __float2half_rn(a);
+        } else {
+            const mfb_pair pr = P.sorted[pair];
+            P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + r] = v[0];
         }
     }
     red_buf ^= 1u;
 }
 
-// Runs this CTA's share of phase 1: units [first, last) of the flattened (group, token tile, row tile) list.
-// `seq` is the number of units the CTA has processed since its barriers were initialised (all warps keep it).
-template <int NGW>
-__device__ __forceinline__ bool phase1(const FastParams& P, const F1Geom& geo, const Phase1Ctx& C, uint32_t n_groups,
-                                       uint32_t first, uint32_t last, uint32_t& seq, uint32_t warp, uint32_t lane) {
+// Runs this CTA's share of one phase: units [first, last) of the flattened (group, token tile, row tile) list.
+// `seq` counts the units the CTA has pushed through this ring since its barriers were initialised.
+template <int NMAT, int NGW>
+__device__ __forceinline__ bool run_phase(const FastParams& P, const PhaseGeom& geo, const PhaseCtx& C, uint32_t n_groups,
+                                          uint32_t first, uint32_t last, uint32_t& seq, uint32_t warp, uint32_t lane) {
     bool ok = true;
     uint32_t g = 0, local_seq = seq;
+    constexpr int DBG = NMAT == 2 ? 0 : 2;
     if (warp == CW) {
         fence_proxy_async();
         for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
-            seek_group(C.pref1, n_groups, u, g);
+            seek_group(C.pref, n_groups, u, g);
             const GroupRef G = group_ref(P, g);
             const long long t0 = clock64();
-            ok = f1_produce(P, geo, C, G, (u - C.pref1[g]) % geo.tiles_per_group, local_seq, lane);
-            dbg_add(P.dbg, warp, lane, 0, t0);
+            ok = phase_produce<NMAT>(P, geo, C, G, (u - C.pref[g]) % geo.tiles, local_seq, lane);
+            dbg_add(P.dbg, warp, lane, DBG, t0);
         }
     } else {
         uint32_t bf[NGW][8];
         float2 sx[NGW];
         uint32_t cached = 0xFFFFFFFFu, red_buf = 0;
-        const uint32_t k0 = (warp % KS) * geo.k_per_warp;
+        const uint32_t k0 = (warp % geo.ksplit) * geo.k_per_warp;
         for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
-            seek_group(C.pref1, n_groups, u, g);
+            seek_group(C.pref, n_groups, u, g);
             const GroupRef G = group_ref(P, g);
-            const uint32_t local = u - C.pref1[g], tt = local / geo.tiles_per_group, tile = local % geo.tiles_per_group;
+            const uint32_t local = u - C.pref[g], tt = local / geo.tiles, tile = local % geo.tiles;
             const uint32_t key = g * 16 + tt;
             const bool fresh_x = G.ok && key != cached;
-            if (fresh_x) { f1_load_x<NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
-            const uint32_t s = local_seq % F1_STAGES, ph = (local_seq / F1_STAGES) & 1u;
+            if (fresh_x) { phase_load_x<NMAT, NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
+            const uint32_t s = local_seq % geo.n_stages, ph = (local_seq / geo.n_stages) & 1u;
             long long t0 = clock64();
             if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
-            dbg_add(P.dbg, warp, lane, 0, t0);
+            dbg_add(P.dbg, warp, lane, DBG, t0);
             t0 = clock64();
             if (G.ok) {
-                const uint8_t* st = C.stages + s * geo.stage_bytes;
-                if (G.bits == 4) f1_compute<4, NGW>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
-                else f1_compute<2, NGW>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                const uint8_t* st = C.ring + s * geo.stage_bytes;
+                if (G.bits == 4) phase_compute<NMAT, NGW, 4>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                else phase_compute<NMAT, NGW, 2>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+            } else if (NMAT == 1) {
+                // an expert that is not resident contributes nothing: its rows of the partials are cleared
+                const mfb_group grp = P.groups[g];
+                const uint32_t cols = min(8u, grp.pair_count - tt * 8);
+                for (uint32_t o = warp * 32 + lane; o < geo.tile_rows * cols; o += CW * 32) {
+                    const mfb_pair pr = P.sorted[grp.pair_start + tt * 8 + o / geo.tile_rows];
+                    P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + tile * geo.tile_rows + o % geo.tile_rows] = 0.0f;
+                }
             }
             __syncwarp();
-            dbg_add(P.dbg, warp, lane, 1, t0);
+            dbg_add(P.dbg, warp, lane, DBG + 1, t0);
             if (lane == 0) mbar_arrive(&C.empty[s]);
         }
     }
@@ -497,183 +550,25 @@ __device__ __forceinline__ bool phase1(const FastParams& P, const F1Geom& geo, c
     return ok;
 }
 
-// ------------------------------------------------------------------------------------------ phase 2 + combine
-// One CTA per block of 16 output rows (columns of the hidden state).  Units (group, token tile) flow through a
-// ring of slots: the copy warp deposits the group's 16 down rows, their scales and the token tile's hidden
-// activation rows; compute warp u % 16 multiplies them and leaves 16 x (tokens) results in a CTA-wide array
-// indexed by (token, rank slot).  When every unit is done the CTA applies the routing weights in rank order,
-// residual first, and writes its 16 columns of every token row: moe_phase2_down_reduce_k8 (moe.metal:349-404)
-// without a partials buffer in global memory.
-struct F2Geom {
-    uint32_t row_stride_max, gpr, act_stride, scale_off, act_off, slot_bytes;
-};
-
-__host__ __device__ inline F2Geom f2_geom(uint32_t f, uint32_t max_bits) {
-    F2Geom g;
-    g.row_stride_max = f * max_bits / 8;   // rows stay contiguous: one warp computes a unit, so bank conflicts cost little
-    g.gpr = f / 64;
-    g.act_stride = f * 2;
-    g.scale_off = 16 * g.row_stride_max;
-    g.act_off = g.scale_off + 2 * 16 * g.gpr * 2;
-    g.slot_bytes = (g.act_off + 8 * g.act_stride + 127u) & ~127u;
-    return g;
-}
-
-struct Phase2Ctx {
-    uint8_t* slots;
-    uint64_t* full;    // [F2_SLOTS]
-    uint64_t* empty;   // [F2_SLOTS]
-    float* part;       // [n_tokens][top_k + 1][16]
-    const uint32_t* pref2;
-};
-
-// Copy-issuing side of up to eight consecutive units at once: lanes 4j..4j+3 of the issuing warp serve unit
-// first_unit + j (wait for its slot, post the byte count, then one copy per lane: the 16 contiguous rows, their
-// scales, their biases, the token tile's activation rows).  Issuing is latency bound per unit, so the eight units
-// of a pass overlap their waits and address arithmetic.  `g` is this lane's group cursor.
-__device__ __forceinline__ bool f2_produce8(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, uint32_t n_groups,
-                                            uint32_t n_units, uint32_t first_unit, uint32_t row0, uint32_t seq, uint32_t lane,
-                                            uint32_t& g) {
-    const uint32_t u = first_unit + (lane >> 2), role = lane & 3;
-    const bool active = u < n_units;
-    bool ok = true, copy = false;
-    GroupRef G;
-    uint32_t s = 0, tt = 0;
-    if (active) {
-        seek_group(C.pref2, n_groups, u, g);
-        G = group_ref(P, g);
-        tt = u - C.pref2[g];
-        s = (seq + u) % F2_SLOTS;
-        ok = mbar_wait(&C.empty[s], (((seq + u) / F2_SLOTS) & 1u) ^ 1u);
-        copy = ok && G.ok;
-        if (ok && role == 0) {
-            if (G.ok) {
-                const uint32_t cols = min(8u, G.pair_count - tt * 8);
-                mbar_expect_tx(&C.full[s], 16 * (P.f * G.bits / 8) + 2 * (16 * geo.gpr * 2) + cols * P.f * 2);
-            } else {
-                mbar_arrive(&C.full[s]);   // nothing to copy: complete the phase so the consumer moves on
-            }
-        }
-    }
-    __syncwarp();   // every byte count is posted before any copy of this pass is issued
-    if (copy) {
-        const uint32_t row_bytes = P.f * G.bits / 8, scale_block = 16 * geo.gpr * 2;
-        uint8_t* st = C.slots + s * geo.slot_bytes;
-        if (role == 0) bulk_g2s(st, G.blob + G.off.down_w + (size_t)row0 * row_bytes, 16 * row_bytes, &C.full[s]);
-        else if (role < 3)
-            bulk_g2s(st + geo.scale_off + (role - 1) * scale_block,
-                     G.blob + (role == 1 ? G.off.down_s : G.off.down_b) + (size_t)row0 * geo.gpr * 2, scale_block, &C.full[s]);
-        else {
-            const uint32_t cols = min(8u, G.pair_count - tt * 8);
-            bulk_g2s(st + geo.act_off, P.actp + (size_t)(G.pair_start + tt * 8) * P.f, cols * P.f * 2, &C.full[s]);
-        }
-    }
-    return __all_sync(0xFFFFFFFFu, ok);
-}
-
-template <int BITS, int NG>
-__device__ __forceinline__ void f2_compute(const FastParams& P, const F2Geom& geo, const GroupRef& G, uint32_t tt,
-                                           const uint8_t* st, uint32_t lane, float* part, uint32_t slots) {
-    const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t row_stride = P.f * BITS / 8;
-    const uint16_t* sc = reinterpret_cast<const uint16_t*>(st + geo.scale_off);
-    constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
-    const int sdt = (int)P.scale_dtype;
-    ScaleRow<NG> s_lo, s_hi, b_lo, b_hi;
-    s_lo.load(sc + g * NG); s_hi.load(sc + (g + 8) * NG);
-    b_lo.load(sc + 16 * NG + g * NG); b_hi.load(sc + 16 * NG + (g + 8) * NG);
-    const uint32_t cols = min(8u, G.pair_count - tt * 8);
-    const uint8_t* act_row = st + geo.act_off + g * geo.act_stride + t * 32;   // columns >= cols hold stale rows: unused
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int gi = 0; gi < NG; ++gi) {
-        uint32_t bf[8];
-        const uint4 lo = *reinterpret_cast<const uint4*>(act_row + gi * 128);
-        const uint4 hi = *reinterpret_cast<const uint4*>(act_row + gi * 128 + 16);
-        bf[0] = lo.x; bf[1] = lo.y; bf[2] = lo.z; bf[3] = lo.w; bf[4] = hi.x; bf[5] = hi.y; bf[6] = hi.z; bf[7] = hi.w;
-        group_mma<BITS>(st + g * row_stride, st + (g + 8) * row_stride, gi * group_bytes + t * lane_bytes, bf,
-                        s_lo.at(gi, sdt), b_lo.at(gi, sdt), s_hi.at(gi, sdt), b_hi.at(gi, sdt), group_sum(bf), acc);
-    }
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        const uint32_t n = 2 * t + c;
-        if (n < cols) {
-            const mfb_pair pr = P.sorted[G.pair_start + tt * 8 + n];
-            float* dst = part + ((size_t)pr.token * slots + pr.rank) * 16;
-            dst[g] = acc[c];
-            dst[g + 8] = acc[2 + c];
-        }
-    }
-}
-
-template <int BITS>
-__device__ __forceinline__ void f2_dispatch(const FastParams& P, const F2Geom& geo, const GroupRef& G, uint32_t tt,
-                                            const uint8_t* st, uint32_t lane, float* part, uint32_t slots) {
-    switch (geo.gpr) {
-        case 8: f2_compute<BITS, 8>(P, geo, G, tt, st, lane, part, slots); break;
-        case 4: f2_compute<BITS, 4>(P, geo, G, tt, st, lane, part, slots); break;
-        case 2: f2_compute<BITS, 2>(P, geo, G, tt, st, lane, part, slots); break;
-        default: f2_compute<BITS, 1>(P, geo, G, tt, st, lane, part, slots); break;
-    }
-}
-
-// Runs phase 2 for the 16 output rows starting at row0 over all units; `seq` as in phase1.
-__device__ __forceinline__ bool phase2(const FastParams& P, const F2Geom& geo, const Phase2Ctx& C, uint32_t n_groups,
-                                       uint32_t row0, uint32_t& seq, uint32_t warp, uint32_t lane) {
-    const uint32_t n_units = C.pref2[n_groups], slots = P.top_k + 1;
-    bool ok = true;
-    uint32_t g = 0;
-    if (warp == CW) {
-        fence_proxy_async();
-        for (uint32_t u = 0; u < n_units && ok; u += 8) {
-            const long long t0 = clock64();
-            ok = f2_produce8(P, geo, C, n_groups, n_units, u, row0, seq, lane, g);
-            dbg_add(P.dbg, warp, lane, 2, t0);
-        }
-    } else if (warp < (uint32_t)F2_SLOTS) {
-        // Compute warp w serves slot w only, so its waits on that slot's barriers follow each other in phase order.
-        // (A parity wait is only meaningful one phase ahead: a warp that started a whole lap ahead of its slot would
-        // see the not-yet-started previous phase as complete.)
-        const uint32_t u0 = (warp + F2_SLOTS - seq % F2_SLOTS) % F2_SLOTS;
-        for (uint32_t u = u0; u < n_units && ok; u += F2_SLOTS) {
-            seek_group(C.pref2, n_groups, u, g);
-            const GroupRef G = group_ref(P, g);
-            const uint32_t s = (seq + u) % F2_SLOTS, ph = ((seq + u) / F2_SLOTS) & 1u;
-            long long t0 = clock64();
-            if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
-            dbg_add(P.dbg, warp, lane, 2, t0);
-            t0 = clock64();
-            if (G.ok) {
-                const uint8_t* st = C.slots + s * geo.slot_bytes;
-                if (G.bits == 4) f2_dispatch<4>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
-                else f2_dispatch<2>(P, geo, G, u - C.pref2[g], st, lane, C.part, slots);
-            }
-            __syncwarp();
-            dbg_add(P.dbg, warp, lane, 3, t0);
-            if (lane == 0) mbar_arrive(&C.empty[s]);
-        }
-    }
-    seq += n_units;
-    return ok;
-}
-
-// Rank-ordered weighted combine of this CTA's 16 columns: residual first, shared expert, then ranks ascending.
-__device__ __forceinline__ void f2_combine(const FastParams& P, const float* part, uint32_t slots, uint32_t row0, bool with_shared) {
-    for (uint32_t o = threadIdx.x; o < P.n_tokens * 16; o += blockDim.x) {
-        const uint32_t tok = o >> 4, r = o & 15;
-        const float* pt = part + (size_t)tok * slots * 16;
+// Rank-ordered weighted combine of a slice of (token, column) outputs from the fp32 partial rows: residual first,
+// shared expert, then ranks ascending (moe_phase2_down_reduce_k8, moe.metal:349-404; same order as combine_kernel).
+__device__ __forceinline__ void combine_slice(const FastParams& P, uint32_t begin, uint32_t end, bool with_shared) {
+    const uint32_t slots = P.top_k + 1;
+    for (uint32_t o = begin + threadIdx.x; o < end; o += blockDim.x) {
+        const uint32_t tok = o / P.d, c = o % P.d;
+        const float* pt = P.partial + (size_t)tok * slots * P.d + c;
         float acc = 0.0f;
-        if (P.residual) acc = widen16(ld_cg_u16((const uint16_t*)P.residual + (size_t)tok * P.d + row0 + r), P.x_dtype);
-        if (with_shared) acc += pt[P.top_k * 16 + r];
+        if (P.residual) acc = widen16(ld_cg_u16((const uint16_t*)P.residual + o), P.x_dtype);
+        if (with_shared) acc += ld_cg_f32(pt + (size_t)P.top_k * P.d);
         for (uint32_t k = 0; k < P.top_k; ++k)
-            acc = fmaf(__half2float(__ushort_as_half(P.route_w[(size_t)tok * P.top_k + k])), pt[k * 16 + r], acc);
-        store_act(P.y, (size_t)tok * P.d + row0 + r, acc, P.x_dtype);
+            acc = fmaf(__half2float(__ushort_as_half(P.route_w[(size_t)tok * P.top_k + k])), ld_cg_f32(pt + (size_t)k * P.d), acc);
+        store_act(P.y, o, acc, P.x_dtype);
     }
 }
 
 // ------------------------------------------------------------------------------------------ separate kernels
 struct FastShared {
-    uint64_t full1[F1_STAGES], empty1[F1_STAGES], full2[F2_SLOTS], empty2[F2_SLOTS];
+    uint64_t full1[MAX_STAGES], empty1[MAX_STAGES], full2[MAX_STAGES], empty2[MAX_STAGES];
     uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1];
     uint32_t flag, n_groups;
     float red[32];
@@ -681,50 +576,38 @@ struct FastShared {
 
 __device__ __forceinline__ void init_barriers(FastShared& S) {
     if (threadIdx.x == 0) {
-        for (int s = 0; s < F1_STAGES; ++s) { mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW); }
-        for (int s = 0; s < F2_SLOTS; ++s) { mbar_init(&S.full2[s], 1); mbar_init(&S.empty2[s], 1); }
+        for (int s = 0; s < MAX_STAGES; ++s) {
+            mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW);
+            mbar_init(&S.full2[s], 1); mbar_init(&S.empty2[s], CW);
+        }
         fence_barrier_init();
     }
     __syncthreads();
 }
 
-template <int NGW>
-__global__ void __launch_bounds__(FAST_THREADS, 1) ffn1_mma_kernel(const FastParams P) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ FastShared S;
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
-    const F1Geom geo = f1_geom(P.d, P.f, max_bits);
-    init_barriers(S);
-    const uint32_t n_groups = *P.n_groups;
-    if (warp == 0) warp_unit_prefix(P.groups, n_groups, geo.tiles_per_group, S.pref1, S.pref2, lane);
-    __syncthreads();
-    Phase1Ctx C{smem, S.full1, S.empty1, reinterpret_cast<float*>(smem + F1_STAGES * geo.stage_bytes), S.pref1};
-    const uint32_t n_units = S.pref1[n_groups];
+__device__ __forceinline__ void unit_range(uint32_t n_units, uint32_t& first, uint32_t& last) {
     const uint32_t per_cta = (n_units + gridDim.x - 1) / gridDim.x;
-    const uint32_t first = min(blockIdx.x * per_cta, n_units), last = min(first + per_cta, n_units);
-    uint32_t seq = 0;
-    if (!phase1<NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+    first = min(blockIdx.x * per_cta, n_units);
+    last = min(first + per_cta, n_units);
 }
 
-__global__ void __launch_bounds__(FAST_THREADS, 1) ffn2_mma_kernel(const FastParams P) {
+// Phase 1 (NMAT = 2) or phase 2 (NMAT = 1) over the groups of one layer call, as a kernel of its own.
+template <int NMAT, int NGW>
+__global__ void __launch_bounds__(FAST_THREADS, 1) ffn_phase_kernel(const FastParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ FastShared S;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t max_bits = P.shared_blob && P.shared_bits > P.bits ? P.shared_bits : P.bits;
-    const F2Geom geo = f2_geom(P.f, max_bits);
-    const uint32_t slots = P.top_k + 1;
-    float* part = reinterpret_cast<float*>(smem + F2_SLOTS * geo.slot_bytes);
+    const PhaseGeom geo = NMAT == 2 ? phase_geom(2, P.d, P.f, NGW, max_bits, RING_BYTES)
+                                    : phase_geom(1, P.f, P.d, NGW, max_bits, RING_BYTES);
     init_barriers(S);
     const uint32_t n_groups = *P.n_groups;
-    if (warp == 0) warp_unit_prefix(P.groups, n_groups, 1, S.pref1, S.pref2, lane);
-    for (uint32_t i = threadIdx.x; i < P.n_tokens * slots * 16; i += blockDim.x) part[i] = 0.0f;
+    if (warp == 0) warp_unit_prefix(P.groups, n_groups, geo.tiles, S.pref1, S.pref2, lane);
     __syncthreads();
-    Phase2Ctx C{smem, S.full2, S.empty2, part, S.pref2};
-    uint32_t seq = 0;
-    if (!phase2(P, geo, C, n_groups, blockIdx.x * 16, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
-    __syncthreads();
-    f2_combine(P, part, slots, blockIdx.x * 16, P.shared_blob != nullptr);
+    PhaseCtx C{smem, S.full1, S.empty1, reinterpret_cast<float*>(smem + RING_BYTES), S.pref1};
+    uint32_t first, last, seq = 0;
+    unit_range(S.pref1[n_groups], first, last);
+    if (!run_phase<NMAT, NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
 }
 
 // ------------------------------------------------------------------------------------------ prep: RMSNorm + layouts
@@ -969,16 +852,15 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     __shared__ FastShared S;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t max_bits = M.shared_bits > M.bits ? M.shared_bits : M.bits;
-    const F1Geom geo1 = f1_geom(M.d, M.f, max_bits);
-    const F2Geom geo2 = f2_geom(M.f, max_bits);
-    const uint32_t slots = M.top_k + 1, n_pairs = M.n_tokens * M.top_k;
+    const PhaseGeom geo1 = phase_geom(2, M.d, M.f, NGW, max_bits, RING_BYTES);
+    const PhaseGeom geo2 = phase_geom(1, M.f, M.d, 4, max_bits, RING_BYTES);
+    const uint32_t n_pairs = M.n_tokens * M.top_k;
     const bool single = M.n_tokens == 1;
-    // ---- shared memory carve-up.  Region A holds the two phase-1 stages and the k-split exchange buffer; phase 2
-    // reuses it for its slot ring and the per-(token, slot) partial rows.  The routing lists follow it.
+    // ---- shared memory carve-up.  Region A holds the stage ring of whichever phase runs plus the k-split exchange
+    // buffers; during the router phase it stages gate rows.  The routing lists follow it.
     uint8_t* region_a = smem;
-    const uint32_t region_a_bytes = F1_STAGES * geo1.stage_bytes + 2 * CW * 32 * 8 * 4;
-    float* red = reinterpret_cast<float*>(smem + F1_STAGES * geo1.stage_bytes);
-    float* part = reinterpret_cast<float*>(region_a + F2_SLOTS * geo2.slot_bytes);
+    const uint32_t region_a_bytes = RING_BYTES + RED_BYTES;
+    float* red = reinterpret_cast<float*>(smem + RING_BYTES);
     mfb_pair* sorted_s = reinterpret_cast<mfb_pair*>(smem + region_a_bytes);
     mfb_group* groups_s = reinterpret_cast<mfb_group*>(sorted_s + (n_pairs + M.n_tokens));
     uint32_t* idx_s = reinterpret_cast<uint32_t*>(groups_s + (M.num_experts + 1));
@@ -1080,7 +962,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
         const uint32_t n_groups = S.n_groups;
-        if (warp == 0) warp_unit_prefix(groups_s, n_groups, geo1.tiles_per_group, S.pref1, S.pref2, lane);
+        if (warp == 0) warp_unit_prefix2(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, lane);
         __syncthreads();
 
         FastParams P;
@@ -1091,35 +973,36 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         P.sorted = sorted_s; P.groups = groups_s; P.n_groups = &S.n_groups;
         P.xp = single ? xp_s : M.xp; P.xp_shared = single ? (M.xp2 ? xp2_s : xp_s) : (M.xp2 ? M.xp2 : M.xp);
         P.x_in_smem = single ? 1 : 0;
-        P.actp = M.actp; P.route_w = w_s;
+        P.actp = M.actp; P.partial = M.partial; P.route_w = w_s;
         P.dbg = M.trace ? reinterpret_cast<unsigned long long*>(M.trace + (size_t)M.n_layers * 8) : nullptr;
         P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
         stamp(4);
 
         // ---- phase 1: this CTA's contiguous share of the (group, token tile, row tile) units
         {
-            Phase1Ctx C{region_a, S.full1, S.empty1, red, S.pref1};
-            const uint32_t n_units = S.pref1[n_groups];
-            const uint32_t per_cta = (n_units + gridDim.x - 1) / gridDim.x;
-            const uint32_t first = min(blockIdx.x * per_cta, n_units), last = min(first + per_cta, n_units);
-            if (!phase1<NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+            PhaseCtx C{region_a, S.full1, S.empty1, red, S.pref1};
+            uint32_t first, last;
+            unit_range(S.pref1[n_groups], first, last);
+            if (!run_phase<2, NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
         }
-        fence_proxy_async();   // hidden activations written here are read by other CTAs' bulk copies after the barrier
         stamp(5);
         if (!(alive = grid_barrier(M, S, epoch))) break;
         stamp(6);
-
-        // ---- phase 2 + combine on the CTAs that own a block of 16 output columns
-        const bool p2_cta = blockIdx.x < M.d / 16;
-        if (p2_cta) {
-            for (uint32_t i = threadIdx.x; i < M.n_tokens * slots * 16; i += blockDim.x) part[i] = 0.0f;
-            __syncthreads();
-            Phase2Ctx C{region_a, S.full2, S.empty2, part, S.pref2};
-            if (!phase2(P, geo2, C, n_groups, blockIdx.x * 16, seq2, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
-            __syncthreads();
-            f2_combine(P, part, slots, blockIdx.x * 16, shared);
+        // ---- phase 2: down projections of every (group, token tile, 128-row block) into the fp32 partial rows
+        {
+            PhaseCtx C{region_a, S.full2, S.empty2, red, S.pref2};
+            uint32_t first, last;
+            unit_range(S.pref2[n_groups], first, last);
+            if (!run_phase<1, 4>(P, geo2, C, n_groups, first, last, seq2, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
         }
+        if (!(alive = grid_barrier(M, S, epoch))) break;
         stamp(7);
+        // ---- rank-ordered weighted combine, a contiguous slice of (token, column) outputs per CTA
+        {
+            const uint32_t total = M.n_tokens * M.d, per = (total + gridDim.x - 1) / gridDim.x;
+            const uint32_t begin = min(blockIdx.x * per, total);
+            combine_slice(P, begin, min(begin + per, total), shared);
+        }
         if (!(alive = grid_barrier(M, S, epoch))) break;
     }
 }
@@ -1130,37 +1013,30 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
 static uint32_t cfg_max_bits(const mfb_moe_config& c) { return c.shared_bits > c.bits ? c.shared_bits : c.bits; }
 
 bool fast_supported(const mfb_moe_config& c) {
-    if (!(c.d == 512 || c.d == 1024 || c.d == 2048)) return false;   // 1, 2 or 4 groups per warp in phase 1
-    const uint32_t ng = c.f / 64;
-    if (c.f % 64 || !(ng == 1 || ng == 2 || ng == 4 || ng == 8)) return false;
-    if (c.f % (16 * RT)) return false;
+    if (!(c.d == 512 || c.d == 1024 || c.d == 2048)) return false;   // 1, 2 or 4 groups per warp in phase 1 (k split 8)
+    if (!(c.f == 256 || c.f == 512)) return false;                   // 4 groups per warp in phase 2 (k split 1 or 2)
     if (c.top_k + 1 > 32) return false;
-    return true;
+    const PhaseGeom g1 = phase_geom(2, c.d, c.f, c.d / 512, cfg_max_bits(c), RING_BYTES);
+    const PhaseGeom g2 = phase_geom(1, c.f, c.d, 4, cfg_max_bits(c), RING_BYTES);
+    if (c.f % g1.tile_rows || c.d % g2.tile_rows) return false;
+    return g1.n_stages >= 2 && g2.n_stages >= 2;
 }
 
-size_t fast_smem1(const mfb_moe_config& c) {
-    const F1Geom g = f1_geom(c.d, c.f, cfg_max_bits(c));
-    return (size_t)F1_STAGES * g.stage_bytes + 2 * CW * 32 * 8 * sizeof(float);
-}
-
-size_t fast_smem2(const mfb_moe_config& c, uint32_t n_tokens) {
-    const F2Geom g = f2_geom(c.f, cfg_max_bits(c));
-    return (size_t)F2_SLOTS * g.slot_bytes + (size_t)n_tokens * (c.top_k + 1) * 16 * sizeof(float);
-}
+size_t fast_smem1(const mfb_moe_config&) { return (size_t)RING_BYTES + RED_BYTES; }
+size_t fast_smem2(const mfb_moe_config&, uint32_t) { return (size_t)RING_BYTES + RED_BYTES; }
 
 size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
     const size_t pairs = (size_t)n_tokens * c.top_k;
     const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
                          ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 6 : 0);
-    const size_t region_a = fast_smem1(c);
-    if (fast_smem2(c, n_tokens) > region_a || (size_t)c.d * (MEGA_ROWS_PER_PASS * 4 + (CW + 1) * 2) > region_a)
-        return (size_t)1 << 30;   // does not fit: the caller falls back to the per-layer launches
-    return region_a + lists + 64;
+    if ((size_t)c.d * (MEGA_ROWS_PER_PASS * 4 + (CW + 1) * 2) > (size_t)RING_BYTES + RED_BYTES)
+        return (size_t)1 << 30;   // the router staging does not fit: the caller falls back to the per-layer launches
+    return (size_t)RING_BYTES + RED_BYTES + lists + 64;
 }
 
 template <int NGW>
 static cudaError_t fast_init_ngw() {
-    cudaError_t e = cudaFuncSetAttribute(ffn1_mma_kernel<NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(ffn_phase_kernel<2, NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     return e;
 }
@@ -1168,7 +1044,7 @@ static cudaError_t fast_init_ngw() {
 // One-time opt-in to large dynamic shared memory for the fast kernels (called when a handle is created, so that no
 // attribute call happens while a caller captures a CUDA graph).
 cudaError_t fast_init() {
-    cudaError_t e = cudaFuncSetAttribute(ffn2_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(ffn_phase_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     if (e == cudaSuccess) e = fast_init_ngw<1>();
     if (e == cudaSuccess) e = fast_init_ngw<2>();
     if (e == cudaSuccess) e = fast_init_ngw<4>();
@@ -1183,19 +1059,23 @@ cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __n
     return cudaGetLastError();
 }
 
+// Phase 1 and phase 2 as two launches; the caller follows with the combine kernel over P.partial.
 cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups) {
-    const F1Geom g = f1_geom(c.d, c.f, cfg_max_bits(c));
-    const uint32_t max_units = max_groups * g.tiles_per_group * ((P.n_tokens + 7) / 8);
-    const uint32_t grid = max_units < (uint32_t)sm_count ? max_units : (uint32_t)sm_count;
-    switch (c.d / (64 * KS)) {
-        case 1: ffn1_mma_kernel<1><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
-        case 2: ffn1_mma_kernel<2><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
-        case 4: ffn1_mma_kernel<4><<<grid, FAST_THREADS, fast_smem1(c), s>>>(P); break;
+    const uint32_t max_bits = cfg_max_bits(c), tts = (P.n_tokens + 7) / 8;
+    const PhaseGeom g1 = phase_geom(2, c.d, c.f, c.d / 512, max_bits, RING_BYTES);
+    const PhaseGeom g2 = phase_geom(1, c.f, c.d, 4, max_bits, RING_BYTES);
+    const size_t smem = (size_t)RING_BYTES + RED_BYTES;
+    const uint32_t u1 = max_groups * g1.tiles * tts, u2 = max_groups * g2.tiles * tts;
+    const uint32_t grid1 = u1 < (uint32_t)sm_count ? u1 : (uint32_t)sm_count, grid2 = u2 < (uint32_t)sm_count ? u2 : (uint32_t)sm_count;
+    switch (c.d / 512) {
+        case 1: ffn_phase_kernel<2, 1><<<grid1, FAST_THREADS, smem, s>>>(P); break;
+        case 2: ffn_phase_kernel<2, 2><<<grid1, FAST_THREADS, smem, s>>>(P); break;
+        case 4: ffn_phase_kernel<2, 4><<<grid1, FAST_THREADS, smem, s>>>(P); break;
         default: return cudaErrorInvalidValue;
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    ffn2_mma_kernel<<<P.d / 16, FAST_THREADS, fast_smem2(c, P.n_tokens), s>>>(P);
+    ffn_phase_kernel<1, 4><<<grid2, FAST_THREADS, smem, s>>>(P);
     count_launches(2);
     return cudaGetLastError();
 }
@@ -1206,7 +1086,7 @@ cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe
     MegaParams copy = M;
     void* args[] = {&copy};
     const void* fn = nullptr;
-    switch (c.d / (64 * KS)) {
+    switch (c.d / 512) {
         case 1: fn = (const void*)stack_mega_kernel<1>; break;
         case 2: fn = (const void*)stack_mega_kernel<2>; break;
         case 4: fn = (const void*)stack_mega_kernel<4>; break;

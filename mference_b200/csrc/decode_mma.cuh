@@ -20,6 +20,7 @@ struct FastParams {
     const __half* xp_shared;  // the same permuted for `shared_bits` (== xp when the widths agree)
     int x_in_smem;            // xp / xp_shared point into shared memory (single-token mode of the fused kernel)
     __half* actp;             // [sorted pairs (+ tokens), f] fp16 hidden activations, permuted per group width
+    float* partial;           // [tokens, top_k + 1, d] fp32 down-projection rows per (token, rank slot)
     const uint16_t* route_w;  // [tokens, top_k] fp16 bits
     const void* residual;     // [tokens, d] or NULL
     void* y;                  // [tokens, d]
@@ -59,6 +60,7 @@ struct MegaParams {
     uint32_t* idx;
     uint16_t* route_w;
     __half* actp;
+    float* partial;
     uint32_t* bar_counter;    // [2]: arrivals, abort word (zeroed before every launch)
     uint32_t* abort;
     uint32_t* status;
