@@ -2,7 +2,7 @@
 """Benchmark of the MoE feed-forward hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--rows fresh|chained] [--layers L]
-                    [--impl ours|reference]
+                    [--launch fused|layers] [--impl ours|reference]
 
 One step = one pass of the 40-layer Qwen3.6-A3B-shaped MoE FFN stack (hidden 2048, 256 experts top-8 + 1 shared,
 intermediate 512, 4-bit group-64 affine weights, bf16 activations, RMSNorm in front of every layer) over one decode
@@ -42,6 +42,9 @@ sys.path.insert(0, ROOT)
 D, F, E, K, LAYERS = 2048, 512, 256, 8, 40
 ROOT_SEED = 0xB2000001
 N_INPUTS = 4          # distinct input sets cycled through the steps
+# DRAM bytes (read + write) of one stack_mega_kernel launch from an ncu capture, keyed by (batch, rows, layers); the
+# capture of a 2-layer case is scaled by the layer count since every layer reads its own weights once
+TRAFFIC_PER_LAUNCH: dict = {}
 
 
 def measured_peaks():
@@ -178,6 +181,8 @@ def run_ours(args):
 
     layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(NL)]
     moe = MoE(D, F, E, K, max_tokens=B)
+    if args.launch == "layers":
+        moe.set_generic(2)
     stack = moe.make_stack(layers)
     n_sets = N_INPUTS
     if fresh:   # one [NL, B, D] set of independent rows per input set
@@ -207,14 +212,21 @@ def run_ours(args):
     torch.cuda.synchronize()
     work = [torch.empty_like(t) for t in inputs]
 
-    def step(i, src=None):
+    kev = []   # (start, end) events around the stack call alone
+
+    def step(i, src=None, timed=False):
         buf = work[i % n_sets]
         if src is None:
             buf.copy_(inputs[i % n_sets])
+        if timed:
+            kev.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+            kev[-1][0].record()
         if fresh:
             moe.encode_stack_rows(stack, buf)    # layer l on rows buf[l]; strictly one layer after the other
         else:
             moe.encode_stack(stack, buf)
+        if timed:
+            kev[-1][1].record()
         return buf
 
     def barrier():
@@ -232,12 +244,12 @@ def run_ours(args):
     barrier()
     ev[0].record()
     for i in range(args.steps):
-        step(i)
+        step(i, timed=True)
         ev[i + 1].record()
     barrier()
     launches = lib.mfb_launch_count() - launches0
     total_ms = ev[0].elapsed_time(ev[-1])
-    per_step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    stack_ms = [a.elapsed_time(b) for a, b in kev]   # the pass alone, without the refresh of its input rows
 
     # end to end through the C ABI with host buffers
     host_in = [t.cpu().pin_memory() for t in inputs]
@@ -271,7 +283,8 @@ def run_ours(args):
     e2e = world * B * args.steps / (e2e_ms * 1e-3)
     hbm_peak, _, peak_kind = measured_peaks()
     bytes_per_step = statistics.mean(step_bytes[i % n_sets] for i in range(args.steps))
-    achieved = bytes_per_step / (statistics.mean(per_step_ms) * 1e-3) / 1e9
+    achieved = bytes_per_step / (statistics.mean(stack_ms) * 1e-3) / 1e9
+    fused = args.launch == "fused"
     cpu_tok_s, cores, sample = cpu_port_tokens_per_s(B, 10.0, NL)
     io_bytes = inputs[0].numel() * 2
     out = {
@@ -286,8 +299,10 @@ def run_ours(args):
                    "l2": f"inputs larger than L2: {bytes_per_step / 1e6:.0f} MB of distinct weight bytes per step, "
                          f"{n_sets} input sets cycled"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "peak_kind": peak_kind, "traffic": None, "kernel": "whole step (all kernels of the pass)",
-                     "algorithmic_bytes_per_step": bytes_per_step},
+                     "peak_kind": peak_kind, "traffic": TRAFFIC_PER_LAUNCH.get((B, args.rows, NL)) if fused else None,
+                     "kernel": "stack_mega_kernel (one cooperative launch = the whole pass)" if fused
+                               else "all kernels of the pass, launched layer by layer",
+                     "launch_ms": statistics.mean(stack_ms), "algorithmic_bytes_per_launch": bytes_per_step},
         "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
         "gpu_launches": int(launches),
@@ -306,6 +321,8 @@ def main():
     ap.add_argument("--batch", type=int, default=64, help="decode batch (token rows per step per GPU): 1, 8 or 64")
     ap.add_argument("--rows", default=None, choices=["fresh", "chained"])
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers only for profiling a small case")
+    ap.add_argument("--launch", default="fused", choices=["fused", "layers"],
+                    help="layers: per-layer, per-phase launches of the same kernels (for profiling one phase alone)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -134,9 +134,11 @@ int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offs
 /* MoE.init / deinit (MoE.swift:65-151): builds the handle and its scratch arena. */
 int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out);
 int32_t mfb_moe_destroy(mfb_moe* moe);
-/* on != 0: run every call of this handle through the generic kernels (any supported shape, any slot subset)
+/* on == 1: run every call of this handle through the generic kernels (any supported shape, any slot subset)
  * instead of the shape-specialised fast kernels; the two agree within the documented tolerance.  Plays the part of
- * the reference's generic vs. specialised pipeline states (MoE.swift:77-135). */
+ * the reference's generic vs. specialised pipeline states (MoE.swift:77-135).
+ * on == 2: keep the fast kernels but launch a stack layer by layer and phase by phase instead of as one fused
+ * cooperative kernel (same results bit for bit; for profiling one phase alone).  on == 0: default selection. */
 int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on);
 /* Phase tracing of the fused stack kernel (the reference's MFERENCE_PHASES counters,
  * Sources/Mference/Runtime/Inference/RealForwardRunner.swift:395-398, 5478-5529): while a device buffer of

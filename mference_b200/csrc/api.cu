@@ -240,7 +240,8 @@ extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
 
 extern "C" int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on) {
     MFB_REQUIRE(moe != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
-    moe->force_generic = on != 0;
+    moe->force_generic = on == 1;
+    moe->no_fused = on == 2;
     return MFB_OK;
 }
 
@@ -435,7 +436,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
     if (n_layers == 0 || n_tokens == 0) return MFB_OK;
     const mfb_moe_config& c = moe->cfg;
     cudaStream_t s = (cudaStream_t)stream;
-    if (use_fast(moe, n_tokens) && moe->coop && fast_smem_stack(c, n_tokens) <= FAST_SMEM_LIMIT) {
+    if (use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens) <= FAST_SMEM_LIMIT) {
         for (uint32_t l = 0; l < n_layers; ++l) {
             rc = check_weights(moe, &layers[l], true);
             if (rc) return rc;

@@ -78,6 +78,7 @@ struct mfb_moe {
     uint64_t max_rows = 0;    // max_tokens * (top_k + 1)
     void* tma = nullptr;      // tensor-map cache of the tcgen05 path (opaque here)
     bool force_generic = false;  // route every call through the generic SIMT kernels (mfb_moe_set_generic)
+    bool no_fused = false;       // keep the fast kernels but launch them layer by layer, phase by phase
     // fused stack kernel: device copy of the per-layer weight table, its host mirror (to skip identical uploads),
     // the barrier words, and whether the device supports cooperative launches
     void* mega_dev = nullptr;

@@ -14,8 +14,8 @@
 //
 // Arithmetic is the reference's factored form (Sources/Mference/Metal/MoE/moe.metal:349-529, 902-1062):
 // per 64-element group  acc += scale * sum(code * x) + bias * sum(x), fp32; sum(code * x) is produced by four
-// k16 MMAs on exact small integers (codes) times fp16 activations with fp32 accumulation, sum(x) by four MMAs
-// against an all-ones fragment.
+// k16 MMAs on the codes (exact, as fp16 subnormals masked straight out of the packed words) times fp16
+// activations with fp32 accumulation, sum(x) by four MMAs against a constant fragment.
 //
 // The K dimension of an MMA may be permuted freely as long as both operands agree, so packed rows are consumed
 // as they lie in memory: lane (g, t) of a warp takes bytes [8t, 8t+8) of each 32-byte group of rows g and g+8
@@ -70,6 +70,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {   // L2-coherent (.cg): sees other CTAs' writes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void named_barrier(int id, int threads) {
@@ -79,16 +84,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                                          uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
 }
 // Loads that bypass L1: for buffers other CTAs write during the same launch (fused stack kernel) a line left in
 // this SM's L1 by an earlier layer would be stale.  volatile keeps them from being merged across layers.
@@ -115,10 +110,15 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
 }
 
 // ------------------------------------------------------------------------------------------ unpacking
-// Codes of a lane's 16-element segment as eight half2 registers of exact small integers.
+// Codes of a lane's 16-element segment as eight half2 registers, with no arithmetic at all: a code masked in place
+// inside a 16-bit lane IS an fp16 number - a subnormal, code * 2^(shift - 24) for a code whose lowest bit sits at
+// bit `shift` (all fields used here lie in the ten mantissa bits).  The tensor core multiplies subnormals exactly.
+// The per-register factor 2^shift is taken out again on the activation side (perm_scale: the activation that
+// meets a code at bit `shift` is stored divided by 2^shift), the common 2^-24 in the epilogue of a phase.
 // 4-bit: words w0 (codes 0-7) and w1 (codes 8-15); register i holds (q[e], q[e+4]) with e following
-// 0,1,2,3,8,9,10,11.  The OR with 0x6400 plants a code in the mantissa of 1024.0 (or of 1024 + 16 q for the
-// high nibble), one half2 subtract / fma then leaves the code itself.
+// 0,1,2,3,8,9,10,11; odd e are high nibbles (shift 4).
+constexpr float CODE_UNSCALE = 16777216.0f;   // 2^24
+
 template <int BITS>
 struct Unpack;
 
@@ -126,38 +126,38 @@ template <>
 struct Unpack<4> {
     static constexpr int WORDS = 2;   // 32-bit words per lane per row per 64-element group
     __device__ static __forceinline__ void run(const uint32_t (&w)[2], uint32_t (&p)[8]) {
-        constexpr uint32_t MAGIC = 0x64006400u, SIXTEENTH = 0x2C002C00u, M64 = 0xD400D400u;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t lo = w[i], hi = w[i] >> 8;
-            p[4 * i + 0] = h2_sub((lo & 0x000F000Fu) | MAGIC, MAGIC);
-            p[4 * i + 1] = h2_fma((lo & 0x00F000F0u) | MAGIC, SIXTEENTH, M64);
-            p[4 * i + 2] = h2_sub((hi & 0x000F000Fu) | MAGIC, MAGIC);
-            p[4 * i + 3] = h2_fma((hi & 0x00F000F0u) | MAGIC, SIXTEENTH, M64);
+            p[4 * i + 0] = lo & 0x000F000Fu;
+            p[4 * i + 1] = lo & 0x00F000F0u;
+            p[4 * i + 2] = hi & 0x000F000Fu;
+            p[4 * i + 3] = hi & 0x00F000F0u;
         }
     }
+    // all-ones counterpart of register i: the factor its activations were divided by
+    __device__ static __forceinline__ uint32_t unit(int i) { return (i & 1) ? 0x4C004C00u : 0x3C003C00u; }   // 16, 1
 };
 
-// 2-bit: one word holds the 16 codes; register i holds (q[i], q[i+8]).
+// 2-bit: one word holds the 16 codes; register i holds (q[i], q[i+8]); registers 0-4 come from the word itself
+// (shifts 0, 2, 4, 6, 8), registers 5-7 from the word shifted right by ten (shifts 0, 2, 4).
 template <>
 struct Unpack<2> {
     static constexpr int WORDS = 1;
     __device__ static __forceinline__ void run(const uint32_t (&w)[1], uint32_t (&p)[8]) {
-        constexpr uint32_t MAGIC = 0x64006400u;
-        // (1024 + 4^k q) * 4^-k - 1024 * 4^-k = q, exactly
-        constexpr uint32_t S1 = 0x34003400u, C1 = 0xDC00DC00u;   // 0.25, -256
-        constexpr uint32_t S2 = 0x2C002C00u, C2 = 0xD400D400u;   // 1/16, -64
-        constexpr uint32_t S3 = 0x24002400u, C3 = 0xCC00CC00u;   // 1/64, -16
-        constexpr uint32_t S4 = 0x1C001C00u, C4 = 0xC400C400u;   // 1/256, -4
         const uint32_t a = w[0], b = w[0] >> 10;
-        p[0] = h2_sub((a & 0x00030003u) | MAGIC, MAGIC);
-        p[1] = h2_fma((a & 0x000C000Cu) | MAGIC, S1, C1);
-        p[2] = h2_fma((a & 0x00300030u) | MAGIC, S2, C2);
-        p[3] = h2_fma((a & 0x00C000C0u) | MAGIC, S3, C3);
-        p[4] = h2_fma((a & 0x03000300u) | MAGIC, S4, C4);
-        p[5] = h2_sub((b & 0x00030003u) | MAGIC, MAGIC);
-        p[6] = h2_fma((b & 0x000C000Cu) | MAGIC, S1, C1);
-        p[7] = h2_fma((b & 0x00300030u) | MAGIC, S2, C2);
+        p[0] = a & 0x00030003u;
+        p[1] = a & 0x000C000Cu;
+        p[2] = a & 0x00300030u;
+        p[3] = a & 0x00C000C0u;
+        p[4] = a & 0x03000300u;
+        p[5] = b & 0x00030003u;
+        p[6] = b & 0x000C000Cu;
+        p[7] = b & 0x00300030u;
+    }
+    __device__ static __forceinline__ uint32_t unit(int i) {
+        const int k = i < 5 ? i : i - 5;   // 4^k as fp16 pairs
+        return k == 0 ? 0x3C003C00u : k == 1 ? 0x44004400u : k == 2 ? 0x4C004C00u : k == 3 ? 0x54005400u : 0x5C005C00u;
     }
 };
 
@@ -172,6 +172,14 @@ __host__ __device__ uint32_t perm_pos(uint32_t e, uint32_t bits) {
     }
     // layout: x0 x8 x1 x9 ... x7 x15
     return ((e & 7u) << 1) + (e >> 3);
+}
+
+// Factor the activation of element e (0..15) of a 16-element segment is stored with: 2^-shift of the code it meets
+// (see Unpack).  Powers of two, so the only rounding is that of values pushed into the fp16 subnormal range.
+__host__ __device__ float perm_scale(uint32_t e, uint32_t bits) {
+    if (bits == 4) return (e & 1u) ? 0.0625f : 1.0f;
+    const uint32_t i = e & 7u, k = i < 5u ? i : i - 5u;
+    return 1.0f / (float)(1u << (2u * k));
 }
 
 namespace {
@@ -204,14 +212,18 @@ __device__ __forceinline__ GroupRef group_ref(const FastParams& P, uint32_t g) {
     return v;
 }
 
-// sum(x) over one 64-element group for this lane's two token columns (2t, 2t+1): four MMAs against an all-ones
-// A fragment leave exactly those sums in c0 and c1 - no conversions, shuffles or shared memory.
+// sum(x) * 2^-24 over one 64-element group for this lane's two token columns (2t, 2t+1): four MMAs against a
+// constant A fragment that undoes the per-register storage factor leave the sums in c0 and c1 - no conversions,
+// shuffles or shared memory.  The 2^-24 matches the scale of the code sums (see Unpack).
+template <int BITS>
 __device__ __forceinline__ float2 group_sum(const uint32_t (&bf)[8]) {
-    constexpr uint32_t ONES = 0x3C003C00u;
     float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) mma16816(d, ONES, ONES, ONES, ONES, bf[2 * j], bf[2 * j + 1]);
-    return make_float2(d[0], d[1]);
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t u0 = Unpack<BITS>::unit(2 * j), u1 = Unpack<BITS>::unit(2 * j + 1);
+        mma16816(d, u0, u0, u1, u1, bf[2 * j], bf[2 * j + 1]);
+    }
+    return make_float2(d[0] * (1.0f / CODE_UNSCALE), d[1] * (1.0f / CODE_UNSCALE));
 }
 
 // One 64-element group of rows g and g+8 of one matrix: sum(code * x) by four MMAs, then the affine factors.
@@ -251,45 +263,82 @@ struct ScaleRow {
         else if (N == 2) w[0] = *reinterpret_cast<const uint32_t*>(p);
         else w[0] = *p;
     }
-    __device__ __forceinline__ float at(int i, int dtype) const {
-        const uint32_t h = (i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xFFFFu);
-        return widen16((uint16_t)h, dtype);
+    template <int SDT>
+    __device__ __forceinline__ float at(int i) const {
+        const uint32_t v = w[i >> 1];
+        if (SDT == MFB_DT_BF16) return __uint_as_float((i & 1) ? (v & 0xFFFF0000u) : (v << 16));
+        const __half2 h = *reinterpret_cast<const __half2*>(&v);
+        return (i & 1) ? __high2float(h) : __low2float(h);
     }
 };
 
 // ------------------------------------------------------------------------------------------ work lists
 // A unit of work is one (group, token tile of up to 8 rows[, 32-row tile of gate/up]).  Exclusive prefix sums of
 // the units of each group, by one warp: pref1[g] counts phase-1 units, pref2[g] phase-2 units.
+//
+// Units do not cost the same: the MMA work of a unit is fixed, its epilogue grows with the token columns in use.
+// wpref[g] is the exclusive prefix of the groups' weights, a token tile with c columns weighing UNIT_BASE + c (per
+// row tile); the CTAs cut the unit list at equal weight rather than at equal count (unit_range).
+constexpr uint32_t UNIT_BASE = 6;
+
+__device__ __forceinline__ uint32_t group_weight(uint32_t pair_count) {
+    const uint32_t full = pair_count / 8, rem = pair_count % 8;
+    return full * (UNIT_BASE + 8) + (rem ? UNIT_BASE + rem : 0);
+}
+
 __device__ __forceinline__ void warp_unit_prefix2(const mfb_group* groups, uint32_t n_groups, uint32_t tiles1, uint32_t tiles2,
-                                                  uint32_t* pref1, uint32_t* pref2, uint32_t lane) {
+                                                  uint32_t* pref1, uint32_t* pref2, uint32_t* wpref, uint32_t lane) {
     const uint32_t per = (n_groups + 31) / 32, g0 = lane * per;
-    uint32_t local = 0;
-    for (uint32_t j = 0; j < per; ++j)
-        if (g0 + j < n_groups) local += (groups[g0 + j].pair_count + 7) / 8;
-    uint32_t incl = local;
-    for (uint32_t off = 1; off < 32; off <<= 1) {
-        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-        if (lane >= off) incl += n;
-    }
-    uint32_t run = incl - local;
+    uint32_t local = 0, wlocal = 0;
     for (uint32_t j = 0; j < per; ++j)
         if (g0 + j < n_groups) {
+            const uint32_t c = groups[g0 + j].pair_count;
+            local += (c + 7) / 8;
+            wlocal += group_weight(c);
+        }
+    uint32_t incl = local, wincl = wlocal;
+    for (uint32_t off = 1; off < 32; off <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off), wn = __shfl_up_sync(0xFFFFFFFFu, wincl, off);
+        if (lane >= off) { incl += n; wincl += wn; }
+    }
+    uint32_t run = incl - local, wrun = wincl - wlocal;
+    for (uint32_t j = 0; j < per; ++j)
+        if (g0 + j < n_groups) {
+            const uint32_t c = groups[g0 + j].pair_count;
             pref1[g0 + j] = run * tiles1;
             pref2[g0 + j] = run * tiles2;
-            run += (groups[g0 + j].pair_count + 7) / 8;
+            wpref[g0 + j] = wrun;
+            run += (c + 7) / 8;
+            wrun += group_weight(c);
         }
-    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-    if (lane == 0) { pref1[n_groups] = total * tiles1; pref2[n_groups] = total * tiles2; }
+    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), wtotal = __shfl_sync(0xFFFFFFFFu, wincl, 31);
+    if (lane == 0) { pref1[n_groups] = total * tiles1; pref2[n_groups] = total * tiles2; wpref[n_groups] = wtotal; }
     __syncwarp();
 }
-__device__ __forceinline__ void warp_unit_prefix(const mfb_group* groups, uint32_t n_groups, uint32_t tiles, uint32_t* pref1,
-                                                 uint32_t* pref2, uint32_t lane) {
-    warp_unit_prefix2(groups, n_groups, tiles, tiles, pref1, pref2, lane);
+
+// First unit at or after weight position `cut` of `parts` equal cuts of the phase's total weight.  32-bit arithmetic
+// suffices: at most 64 tokens x (top_k + 1) pairs of weight <= UNIT_BASE + 1 each, times tiles, times parts.
+__device__ __forceinline__ uint32_t unit_at_cut(const mfb_group* groups, uint32_t n_groups, const uint32_t* pref,
+                                                const uint32_t* wpref, uint32_t tiles, uint32_t cut, uint32_t parts) {
+    if (cut >= parts) return pref[n_groups];
+    const uint32_t target = wpref[n_groups] * tiles * cut / parts;   // weight in front of the unit looked for
+    uint32_t lo = 0, hi = n_groups;   // last group whose prefix (times tiles) is <= target
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) / 2;
+        if (wpref[mid] * tiles <= target) lo = mid; else hi = mid;
+    }
+    uint32_t rem = target - wpref[lo] * tiles;
+    const uint32_t count = groups[lo].pair_count, full = count / 8, r = count % 8;
+    const uint32_t full_block = tiles * (UNIT_BASE + 8);
+    const uint32_t tt = min(full, rem / full_block);
+    rem -= tt * full_block;
+    const uint32_t w = tt < full ? UNIT_BASE + 8 : UNIT_BASE + r;
+    return pref[lo] + tt * tiles + min(rem / w, tiles - 1);
 }
 
 // Optional cycle accounting of CTA 0 (attached with the phase trace): counter k of warp w at dbg[w*8 + k].
 __device__ __forceinline__ void dbg_add(unsigned long long* dbg, uint32_t warp, uint32_t lane, int k, long long t0) {
-    if (dbg && blockIdx.x == 0 && lane == 0) dbg[warp * 8 + k] += (unsigned long long)(clock64() - t0);
+    if (dbg && blockIdx.x == 0 && lane == 0) atomicAdd(&dbg[warp * 8 + k], (unsigned long long)(clock64() - t0));   // no result: does not stall
 }
 
 // Advances `g` until unit u lies in group g (units are visited in increasing order).
@@ -312,7 +361,7 @@ constexpr int RPW = 2;   // 16-row MMA tiles per warp
 
 struct PhaseGeom {
     uint32_t k, n_rows, ksplit, row_groups, tile_rows, tiles, blk_rows, blk_stride, mat_bytes, gpr, scale_block,
-        stage_bytes, k_per_warp, n_stages;
+        stage_bytes, k_per_warp, n_stages, tile_shift, blk_shift;   // tile_rows and blk_rows are powers of two
 };
 
 __host__ __device__ inline PhaseGeom phase_geom(uint32_t nmat, uint32_t k, uint32_t n_rows, uint32_t ngw, uint32_t max_bits,
@@ -325,6 +374,9 @@ __host__ __device__ inline PhaseGeom phase_geom(uint32_t nmat, uint32_t k, uint3
     g.tile_rows = 16 * RPW * g.row_groups;
     g.tiles = n_rows / g.tile_rows;
     g.blk_rows = g.tile_rows / 4;
+    g.tile_shift = 0;
+    while ((1u << g.tile_shift) < g.tile_rows) ++g.tile_shift;
+    g.blk_shift = g.tile_shift - 2;
     g.blk_stride = g.blk_rows * (k * max_bits / 8) + ROW_PAD;
     g.mat_bytes = 4 * g.blk_stride;
     g.scale_block = g.tile_rows * g.gpr * 2;
@@ -352,8 +404,7 @@ __device__ __forceinline__ uint32_t tile_row(uint32_t blk_rows, uint32_t rtile, 
 // Copy-issuing side of one unit (all 32 lanes of the issuing warp call this).
 template <int NMAT>
 __device__ __forceinline__ bool phase_produce(const FastParams& P, const PhaseGeom& geo, const PhaseCtx& C, const GroupRef& G,
-                                              uint32_t tile, uint32_t seq, uint32_t lane) {
-    const uint32_t s = seq % geo.n_stages, ph = (seq / geo.n_stages) & 1u;
+                                              uint32_t tile, uint32_t s, uint32_t ph, uint32_t lane) {
     if (!mbar_wait(&C.empty[s], ph ^ 1u)) return false;
     if (!G.ok) {   // nothing to copy: complete the phase so the consumers move on
         if (lane == 0) mbar_arrive(&C.full[s]);
@@ -411,7 +462,7 @@ __device__ __forceinline__ void phase_load_x(const FastParams& P, const GroupRef
 
 // Compute side of one unit by one warp: RPW row tiles x NMAT matrices x NGW groups of this warp's k range, then the
 // exchange of the k-split partial sums and the epilogue.
-template <int NMAT, int NGW, int BITS>
+template <int NMAT, int NGW, int BITS, int SDT>
 __device__ __forceinline__ void phase_compute(const FastParams& P, const GroupRef& G, const PhaseGeom& geo, const uint8_t* stage,
                                               uint32_t tile, uint32_t tt, const uint32_t (&bf)[NGW][8], float2 (&sx)[NGW],
                                               bool fresh_x, uint32_t warp, uint32_t lane, float* red, uint32_t& red_buf) {
@@ -421,12 +472,11 @@ __device__ __forceinline__ void phase_compute(const FastParams& P, const GroupRe
     const uint16_t* sc = reinterpret_cast<const uint16_t*>(stage + NMAT * geo.mat_bytes);
     const uint32_t sblk = geo.tile_rows * gpr;
     constexpr uint32_t lane_bytes = BITS == 4 ? 8 : 4, group_bytes = 64 * BITS / 8;
-    const int sdt = (int)P.scale_dtype;
     const uint32_t cols = min(8u, G.pair_count - tt * 8);
 
     if (fresh_x) {
 #pragma unroll
-        for (int gi = 0; gi < NGW; ++gi) sx[gi] = group_sum(bf[gi]);   // valid for every row tile of this token tile
+        for (int gi = 0; gi < NGW; ++gi) sx[gi] = group_sum<BITS>(bf[gi]);   // valid for every row tile of this token tile
     }
     float acc[RPW][NMAT][4];
 #pragma unroll
@@ -450,7 +500,8 @@ __device__ __forceinline__ void phase_compute(const FastParams& P, const GroupRe
 #pragma unroll
             for (int m = 0; m < NMAT; ++m)
                 group_mma<BITS>(stage + m * geo.mat_bytes + a_lo, stage + m * geo.mat_bytes + a_hi, boff, bf[gi],
-                                sr[m][0].at(gi, sdt), sr[m][2].at(gi, sdt), sr[m][1].at(gi, sdt), sr[m][3].at(gi, sdt), sx[gi],
+                                sr[m][0].template at<SDT>(gi), sr[m][2].template at<SDT>(gi), sr[m][1].template at<SDT>(gi),
+                                sr[m][3].template at<SDT>(gi), sx[gi],
                                 acc[j][m]);
         }
     }
@@ -465,30 +516,48 @@ __device__ __forceinline__ void phase_compute(const FastParams& P, const GroupRe
             *reinterpret_cast<float4*>(rb + ((ksi * n_rtiles + rg * RPW + j) * PER_TILE) + m * 128 + lane * 4) =
                 make_float4(acc[j][m][0], acc[j][m][1], acc[j][m][2], acc[j][m][3]);
     named_barrier(1, CW * 32);
-    for (uint32_t o = warp * 32 + lane; o < n_rtiles * 128; o += CW * 32) {
-        const uint32_t rtile = o >> 7, row16 = (o & 127) >> 3, n = o & 7;
-        if (n >= cols) continue;
-        const uint32_t src = ((row16 & 7) * 4 + (n >> 1)) * 4 + (row16 >> 3) * 2 + (n & 1);
-        float v[NMAT];
+    // Fixed-order sum over the k splits and the phase's epilogue.  A thread keeps one row of the stage tile and steps
+    // through the token columns (tile_rows divides the CW * 32 threads or is a multiple of them), so everything that
+    // depends on the row is computed once, and consecutive threads store consecutive matrix rows of one column.
+    const uint32_t et = warp * 32 + lane;
+    for (uint32_t rl0 = 0; rl0 < geo.tile_rows; rl0 += CW * 32) {   // one pass unless the tile has more rows than threads
+        const uint32_t rl = rl0 + (et & (geo.tile_rows - 1)), n0 = et >> geo.tile_shift;
+        const uint32_t n_step = geo.tile_rows >= CW * 32 ? 1u : (CW * 32) >> geo.tile_shift;
+        // inverse of tile_row: block b = lane group % 4, then rtile * 4 + hi * 2 + (lane group / 4)
+        const uint32_t b = rl >> geo.blk_shift, q = rl & (geo.blk_rows - 1);
+        const uint32_t rtile = q >> 2, hi = (q >> 1) & 1u, gq = b + 4u * (q & 1u);
+        const float* rrow = rb + rtile * PER_TILE + gq * 16 + hi * 2;   // + k * n_rtiles * PER_TILE + m * 128 + (n / 2) * 4 + (n & 1)
+        const uint32_t r = tile * geo.tile_rows + rl;
+        const uint32_t pair0 = G.pair_start + tt * 8;
+        const uint32_t act_col = (r & ~15u) + perm_pos(r & 15u, G.bits);
+        const float act_scale = perm_scale(r & 15u, G.bits);
+        const bool clamp = !G.shared && P.limit > 0.0f;   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) v[m] = 0.0f;
-        for (uint32_t k = 0; k < geo.ksplit; ++k)
+        for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t n = n0 + j * n_step;
+            if (n >= cols) break;
+            float v[NMAT];
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) v[m] += rb[(k * n_rtiles + rtile) * PER_TILE + m * 128 + src];
-        const uint32_t r = tile * geo.tile_rows + tile_row(geo.blk_rows, rtile, row16 & 7, row16 >> 3);
-        const uint32_t pair = G.pair_start + tt * 8 + n;
-        if (NMAT == 2) {
-            float gate = v[0], up = v[NMAT - 1];
-            if (!G.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
-                gate = fminf(gate, P.limit);
-                up = fminf(fmaxf(up, -P.limit), P.limit);
+            for (int m = 0; m < NMAT; ++m) v[m] = 0.0f;
+            const float* src = rrow + (n >> 1) * 4 + (n & 1);
+            for (uint32_t k = 0; k < geo.ksplit; ++k)
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) v[m] += src[k * n_rtiles * PER_TILE + m * 128];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) v[m] *= CODE_UNSCALE;
+            if (NMAT == 2) {
+                float gate = v[0], up = v[NMAT - 1];
+                if (clamp) {
+                    gate = fminf(gate, P.limit);
+                    up = fminf(fmaxf(up, -P.limit), P.limit);
+                }
+                float a = hidden_act(gate, (int)P.activation) * up;
+                a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                P.actp[(size_t)(pair0 + n) * P.f + act_col] = __float2half_rn(a * act_scale);
+            } else {
+                const mfb_pair pr = P.sorted[pair0 + n];
+                P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + r] = v[0];
             }
-            float a = hidden_act(gate, (int)P.activation) * up;
-            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-            P.actp[(size_t)pair * P.f + (r & ~15u) + perm_pos(r & 15u, G.bits)] = __float2half_rn(a);
-        } else {
-            const mfb_pair pr = P.sorted[pair];
-            P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + r] = v[0];
         }
     }
     red_buf ^= 1u;
@@ -500,53 +569,74 @@ template <int NMAT, int NGW>
 __device__ __forceinline__ bool run_phase(const FastParams& P, const PhaseGeom& geo, const PhaseCtx& C, uint32_t n_groups,
                                           uint32_t first, uint32_t last, uint32_t& seq, uint32_t warp, uint32_t lane) {
     bool ok = true;
-    uint32_t g = 0, local_seq = seq;
+    if (first >= last) return true;
+    // cursors advanced by one unit per iteration: (group, token tile, row tile) and (ring stage, parity) - no
+    // divisions in the loop
+    uint32_t g = 0;
+    seek_group(C.pref, n_groups, first, g);
+    uint32_t tt = (first - C.pref[g]) / geo.tiles, tile = (first - C.pref[g]) % geo.tiles;
+    uint32_t st_i = seq % geo.n_stages, ph = (seq / geo.n_stages) & 1u;
+    GroupRef G = group_ref(P, g);   // the slot lookup is a dependent global load: once per group
+#define MFB_ADVANCE_UNIT()                                                                              \
+    do {                                                                                                \
+        if (++st_i == geo.n_stages) { st_i = 0; ph ^= 1u; }                                             \
+        if (++tile == geo.tiles) {                                                                      \
+            tile = 0; ++tt;                                                                             \
+            if (tt * 8 >= G.pair_count && g + 1 < n_groups) { ++g; tt = 0; G = group_ref(P, g); }       \
+        }                                                                                               \
+    } while (0)
     constexpr int DBG = NMAT == 2 ? 0 : 2;
     if (warp == CW) {
         fence_proxy_async();
-        for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
-            seek_group(C.pref, n_groups, u, g);
-            const GroupRef G = group_ref(P, g);
+        for (uint32_t u = first; u < last && ok; ++u) {
             const long long t0 = clock64();
-            ok = phase_produce<NMAT>(P, geo, C, G, (u - C.pref[g]) % geo.tiles, local_seq, lane);
+            ok = phase_produce<NMAT>(P, geo, C, G, tile, st_i, ph, lane);
             dbg_add(P.dbg, warp, lane, DBG, t0);
+            MFB_ADVANCE_UNIT();
         }
     } else {
         uint32_t bf[NGW][8];
         float2 sx[NGW];
         uint32_t cached = 0xFFFFFFFFu, red_buf = 0;
         const uint32_t k0 = (warp % geo.ksplit) * geo.k_per_warp;
-        for (uint32_t u = first; u < last && ok; ++u, ++local_seq) {
-            seek_group(C.pref, n_groups, u, g);
-            const GroupRef G = group_ref(P, g);
-            const uint32_t local = u - C.pref[g], tt = local / geo.tiles, tile = local % geo.tiles;
+        const long long t_phase = clock64();
+        for (uint32_t u = first; u < last && ok; ++u) {
+            const long long t_top = clock64();
             const uint32_t key = g * 16 + tt;
             const bool fresh_x = G.ok && key != cached;
             if (fresh_x) { phase_load_x<NMAT, NGW>(P, G, tt, k0, lane, bf); cached = key; }   // issued before the wait below
-            const uint32_t s = local_seq % geo.n_stages, ph = (local_seq / geo.n_stages) & 1u;
+            dbg_add(P.dbg, warp, lane, 4 + DBG, t_top);
             long long t0 = clock64();
-            if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+            if (!mbar_wait(&C.full[st_i], ph)) { ok = false; break; }
             dbg_add(P.dbg, warp, lane, DBG, t0);
             t0 = clock64();
             if (G.ok) {
-                const uint8_t* st = C.ring + s * geo.stage_bytes;
-                if (G.bits == 4) phase_compute<NMAT, NGW, 4>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
-                else phase_compute<NMAT, NGW, 2>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                const uint8_t* st = C.ring + st_i * geo.stage_bytes;
+                const bool bf16_scales = P.scale_dtype == MFB_DT_BF16;
+                if (G.bits == 4) {
+                    if (bf16_scales) phase_compute<NMAT, NGW, 4, MFB_DT_BF16>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                    else phase_compute<NMAT, NGW, 4, MFB_DT_F16>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                } else {
+                    if (bf16_scales) phase_compute<NMAT, NGW, 2, MFB_DT_BF16>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                    else phase_compute<NMAT, NGW, 2, MFB_DT_F16>(P, G, geo, st, tile, tt, bf, sx, fresh_x, warp, lane, C.red, red_buf);
+                }
             } else if (NMAT == 1) {
                 // an expert that is not resident contributes nothing: its rows of the partials are cleared
-                const mfb_group grp = P.groups[g];
-                const uint32_t cols = min(8u, grp.pair_count - tt * 8);
+                const uint32_t cols = min(8u, G.pair_count - tt * 8);
                 for (uint32_t o = warp * 32 + lane; o < geo.tile_rows * cols; o += CW * 32) {
-                    const mfb_pair pr = P.sorted[grp.pair_start + tt * 8 + o / geo.tile_rows];
+                    const mfb_pair pr = P.sorted[G.pair_start + tt * 8 + o / geo.tile_rows];
                     P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + tile * geo.tile_rows + o % geo.tile_rows] = 0.0f;
                 }
             }
             __syncwarp();
             dbg_add(P.dbg, warp, lane, DBG + 1, t0);
-            if (lane == 0) mbar_arrive(&C.empty[s]);
+            if (lane == 0) mbar_arrive(&C.empty[st_i]);
+            MFB_ADVANCE_UNIT();
         }
+        dbg_add(P.dbg, warp, lane, 5 + DBG, t_phase);
     }
-    seq += last > first ? last - first : 0;
+#undef MFB_ADVANCE_UNIT
+    seq += last - first;
     return ok;
 }
 
@@ -569,7 +659,8 @@ __device__ __forceinline__ void combine_slice(const FastParams& P, uint32_t begi
 // ------------------------------------------------------------------------------------------ separate kernels
 struct FastShared {
     uint64_t full1[MAX_STAGES], empty1[MAX_STAGES], full2[MAX_STAGES], empty2[MAX_STAGES];
-    uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1];
+    uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1], wpref[MAX_GROUPS + 1];
+    uint32_t range[4];   // this CTA's [first, last) units of phase 1 and of phase 2
     uint32_t flag, n_groups;
     float red[32];
 };
@@ -585,10 +676,13 @@ __device__ __forceinline__ void init_barriers(FastShared& S) {
     __syncthreads();
 }
 
-__device__ __forceinline__ void unit_range(uint32_t n_units, uint32_t& first, uint32_t& last) {
-    const uint32_t per_cta = (n_units + gridDim.x - 1) / gridDim.x;
-    first = min(blockIdx.x * per_cta, n_units);
-    last = min(first + per_cta, n_units);
+// This CTA's contiguous share of each phase's units: cuts at equal weight (see warp_unit_prefix2).  Called by warp 0
+// right after the prefix sums; lanes 0..3 each find one of the four cut points.
+__device__ __forceinline__ void warp_unit_ranges(FastShared& S, const mfb_group* groups, uint32_t n_groups, uint32_t tiles1,
+                                                 uint32_t tiles2, uint32_t lane) {
+    if (lane < 4)
+        S.range[lane] = unit_at_cut(groups, n_groups, lane < 2 ? S.pref1 : S.pref2, S.wpref, lane < 2 ? tiles1 : tiles2,
+                                    blockIdx.x + (lane & 1u), gridDim.x);
 }
 
 // Phase 1 (NMAT = 2) or phase 2 (NMAT = 1) over the groups of one layer call, as a kernel of its own.
@@ -602,11 +696,14 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) ffn_phase_kernel(const FastPa
                                     : phase_geom(1, P.f, P.d, NGW, max_bits, RING_BYTES);
     init_barriers(S);
     const uint32_t n_groups = *P.n_groups;
-    if (warp == 0) warp_unit_prefix(P.groups, n_groups, geo.tiles, S.pref1, S.pref2, lane);
+    if (warp == 0) {
+        warp_unit_prefix2(P.groups, n_groups, geo.tiles, geo.tiles, S.pref1, S.pref2, S.wpref, lane);
+        warp_unit_ranges(S, P.groups, n_groups, geo.tiles, geo.tiles, lane);
+    }
     __syncthreads();
     PhaseCtx C{smem, S.full1, S.empty1, reinterpret_cast<float*>(smem + RING_BYTES), S.pref1};
-    uint32_t first, last, seq = 0;
-    unit_range(S.pref1[n_groups], first, last);
+    uint32_t seq = 0;
+    const uint32_t first = S.range[0], last = S.range[1];
     if (!run_phase<NMAT, NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
 }
 
@@ -645,9 +742,8 @@ __global__ void prep_kernel(const void* __restrict__ h, int dtype, const __nv_bf
             v = widen16(narrow16(v, dtype), dtype);   // the FFN consumes the rounded row, as the layer-by-layer path does
         }
         v = fminf(fmaxf(v, -65504.0f), 65504.0f);
-        const __half hv = __float2half_rn(v);
-        xp[row * d + (i & ~15u) + perm_pos(i & 15u, bits)] = hv;
-        if (xp2) xp2[row * d + (i & ~15u) + perm_pos(i & 15u, bits2)] = hv;
+        xp[row * d + (i & ~15u) + perm_pos(i & 15u, bits)] = __float2half_rn(v * perm_scale(i & 15u, bits));
+        if (xp2) xp2[row * d + (i & ~15u) + perm_pos(i & 15u, bits2)] = __float2half_rn(v * perm_scale(i & 15u, bits2));
     }
 }
 
@@ -719,71 +815,94 @@ __device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLay
             const uint16_t bits = narrow16(v, M.x_dtype);
             xn_out[i] = bits;
             v = fminf(fmaxf(widen16(bits, M.x_dtype), -65504.0f), 65504.0f);
-            const __half hv = __float2half_rn(v);
-            xp_out[(i & ~15u) + perm_pos(i & 15u, M.bits)] = hv;
-            if (xp2_out) xp2_out[(i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = hv;
+            xp_out[(i & ~15u) + perm_pos(i & 15u, M.bits)] = __float2half_rn(v * perm_scale(i & 15u, M.bits));
+            if (xp2_out) xp2_out[(i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = __float2half_rn(v * perm_scale(i & 15u, M.shared_bits));
         }
     }
     __syncthreads();
 }
 
-// logits[t, e] for the experts this CTA owns (e = blockIdx.x, + gridDim.x, ...), every token, in the fixed
-// summation order of router_logits_kernel: lane l takes k = l, l+32, ... ascending, then a xor butterfly.
-// `stage` is free shared memory: up to two gate rows as fp32, then one activation row per warp as raw 16-bit.
-// With x_smem the single activation row is already in shared memory.
-constexpr uint32_t MEGA_ROWS_PER_PASS = 2;
+// logits[t, e] in the fixed summation order of router_logits_kernel: lane l takes k = l, l+32, ... ascending, then
+// a xor butterfly, the bias last.  The (expert, token) plane is cut into tasks of EB consecutive experts x
+// (warps x TT) tokens, dealt round-robin to the CTAs.  A CTA stages the EB gate rows as fp32 in `stage`; each
+// warp fetches its TT token rows into shared memory with asynchronous 16-byte copies (in flight while the gate
+// rows are converted) and then forms the EB x TT dot products together, so that every shared-memory load feeds
+// several multiply-adds.  With x_smem the single activation row is already in shared memory.
+constexpr uint32_t MEGA_MAX_EB = 4, MEGA_MAX_TT = 4;
 
-__device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage, const uint16_t* x_smem) {
+template <uint32_t EB, uint32_t TT>
+__device__ __forceinline__ void mega_logits_run(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage, const uint16_t* x_smem) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5, d = M.d;
-    float* w_rows = reinterpret_cast<float*>(stage);                                                   // [2][d]
-    uint16_t* x_stage = reinterpret_cast<uint16_t*>(stage + MEGA_ROWS_PER_PASS * d * 4) + warp * d;    // [warps][d]
-    for (uint32_t e0 = blockIdx.x; e0 < M.num_experts; e0 += MEGA_ROWS_PER_PASS * gridDim.x) {
+    float* w_rows = reinterpret_cast<float*>(stage);                                                       // [EB][d]
+    uint16_t* x_stage = reinterpret_cast<uint16_t*>(stage + MEGA_MAX_EB * d * 4) + warp * MEGA_MAX_TT * d; // [warps][TT][d]
+    const uint32_t tb = warps * TT;
+    const uint32_t n_eb = (M.num_experts + EB - 1) / EB, n_tb = (M.n_tokens + tb - 1) / tb;
+    for (uint32_t task = blockIdx.x; task < n_eb * n_tb; task += gridDim.x) {
+        const uint32_t e0 = (task % n_eb) * EB, t0 = (task / n_eb) * tb + warp * TT;
+        const uint32_t ne = min(EB, M.num_experts - e0);
+        const uint32_t nt = t0 < M.n_tokens ? min(TT, M.n_tokens - t0) : 0;
         __syncthreads();
-        uint32_t ne = 0;
-        for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) {
-            const uint32_t e = e0 + j * gridDim.x;
-            if (e >= M.num_experts) break;
-            ++ne;
-            const uint4* src = reinterpret_cast<const uint4*>(Ly.router_w + (size_t)e * d);
-            for (uint32_t i = threadIdx.x; i < d / 8; i += blockDim.x) {
-                const uint4 q = src[i];
-                float* dst = w_rows + j * d + i * 8;
-                dst[0] = __uint_as_float(q.x << 16); dst[1] = __uint_as_float(q.x & 0xFFFF0000u);
-                dst[2] = __uint_as_float(q.y << 16); dst[3] = __uint_as_float(q.y & 0xFFFF0000u);
-                dst[4] = __uint_as_float(q.z << 16); dst[5] = __uint_as_float(q.z & 0xFFFF0000u);
-                dst[6] = __uint_as_float(q.w << 16); dst[7] = __uint_as_float(q.w & 0xFFFF0000u);
+        if (!x_smem) {
+            for (uint32_t r = 0; r < nt; ++r) {
+                const uint16_t* x = (const uint16_t*)M.xn + (size_t)(t0 + r) * d;
+                for (uint32_t i = lane; i < d / 8; i += 32) cp_async16(x_stage + r * d + i * 8, x + i * 8);
             }
+            cp_async_commit();
         }
+        for (uint32_t j = 0; j < ne; ++j)
+        for (uint32_t c = threadIdx.x; c < d / 8; c += blockDim.x) {
+            const uint4 q = *reinterpret_cast<const uint4*>(Ly.router_w + (size_t)(e0 + j) * d + c * 8);
+            float* dst = w_rows + j * d + c * 8;
+            *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(q.x << 16), __uint_as_float(q.x & 0xFFFF0000u),
+                                                          __uint_as_float(q.y << 16), __uint_as_float(q.y & 0xFFFF0000u));
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(__uint_as_float(q.z << 16), __uint_as_float(q.z & 0xFFFF0000u),
+                                                              __uint_as_float(q.w << 16), __uint_as_float(q.w & 0xFFFF0000u));
+        }
+        cp_async_wait_all();
         __syncthreads();
-        for (uint32_t t = warp; t < M.n_tokens; t += warps) {
-            const uint16_t* x_row = x_smem;
-            if (!x_smem) {
-                const uint16_t* x = (const uint16_t*)M.xn + (size_t)t * d;
-                __syncwarp();
-                for (uint32_t i = lane; i < d / 8; i += 32) *reinterpret_cast<uint4*>(x_stage + i * 8) = ld_cg_u4(x + i * 8);
-                __syncwarp();
-                x_row = x_stage;
-            }
-            float acc[MEGA_ROWS_PER_PASS] = {0.0f, 0.0f};
-#pragma unroll 8
-            for (uint32_t i = lane; i < d; i += 32) {
-                const float xv = widen16(x_row[i], M.x_dtype);
+        if (nt == 0) continue;
+        const uint16_t* xr = x_smem ? x_smem : x_stage;
+        float acc[EB][TT];
 #pragma unroll
-                for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) acc[j] = fmaf(w_rows[j * d + i], xv, acc[j]);
-            }
+        for (uint32_t j = 0; j < EB; ++j)
 #pragma unroll
-            for (uint32_t j = 0; j < MEGA_ROWS_PER_PASS; ++j) {
-                float v = acc[j];
+            for (uint32_t r = 0; r < TT; ++r) acc[j][r] = 0.0f;
+#pragma unroll 2
+        for (uint32_t i = lane; i < d; i += 32) {
+            float xv[TT], wv[EB];
+#pragma unroll
+            for (uint32_t r = 0; r < TT; ++r) xv[r] = r < nt ? widen16(xr[r * d + i], M.x_dtype) : 0.0f;
+#pragma unroll
+            for (uint32_t j = 0; j < EB; ++j) wv[j] = w_rows[j * d + i];
+#pragma unroll
+            for (uint32_t j = 0; j < EB; ++j)
+#pragma unroll
+                for (uint32_t r = 0; r < TT; ++r) acc[j][r] = fmaf(wv[j], xv[r], acc[j][r]);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < EB; ++j)
+#pragma unroll
+            for (uint32_t r = 0; r < TT; ++r) {
+                float v = acc[j][r];
                 for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-                const uint32_t e = e0 + j * gridDim.x;
-                if (lane == 0 && j < ne) {
-                    if (Ly.logit_bias) v = v + Ly.logit_bias[e];
-                    M.logits[(size_t)t * M.num_experts + e] = v;
+                if (lane == 0 && j < ne && r < nt) {
+                    if (Ly.logit_bias) v = v + Ly.logit_bias[e0 + j];
+                    M.logits[(size_t)(t0 + r) * M.num_experts + e0 + j] = v;
                 }
             }
-        }
     }
     __syncthreads();
+}
+
+__device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer& Ly, uint8_t* stage, const uint16_t* x_smem) {
+    const uint32_t warps = blockDim.x >> 5;
+    if (M.n_tokens <= warps) {   // one token per warp; two experts per task give 128 tasks for 256 experts
+        mega_logits_run<2, 1>(M, Ly, stage, x_smem);
+    } else {
+        const uint32_t n_tb = (M.n_tokens + warps * 4 - 1) / (warps * 4);
+        if (((M.num_experts + 3) / 4) * n_tb * 4 >= gridDim.x * 3) mega_logits_run<4, 4>(M, Ly, stage, x_smem);
+        else mega_logits_run<2, 4>(M, Ly, stage, x_smem);
+    }
 }
 
 // Counting sort of the routing table into shared memory, identical order to group.cu / route_small_kernel; every
@@ -874,6 +993,17 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     init_barriers(S);
     uint32_t epoch = 0, seq1 = 0, seq2 = 0;
     bool alive = true;
+    // SM clock against the global timer over the whole launch (row 16 of the cycle counters): cycles per ns
+    auto clock_pair = [&](int slot) {
+        if (M.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+            uint64_t t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            uint64_t* row = M.trace + (size_t)M.n_layers * 8 + 16 * 8;
+            row[4 + slot] = (uint64_t)clock64();
+            row[6 + slot] = t;
+        }
+    };
+    clock_pair(0);
     for (uint32_t l = 0; l < M.n_layers && alive; ++l) {
         const MegaLayer Ly = M.layers[l];
         void* h = (uint8_t*)M.hidden + (size_t)l * M.layer_stride * 2;   // 16-bit activations
@@ -962,7 +1092,10 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
         const uint32_t n_groups = S.n_groups;
-        if (warp == 0) warp_unit_prefix2(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, lane);
+        if (warp == 0) {
+            warp_unit_prefix2(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, S.wpref, lane);
+            warp_unit_ranges(S, groups_s, n_groups, geo1.tiles, geo2.tiles, lane);
+        }
         __syncthreads();
 
         FastParams P;
@@ -981,8 +1114,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         // ---- phase 1: this CTA's contiguous share of the (group, token tile, row tile) units
         {
             PhaseCtx C{region_a, S.full1, S.empty1, red, S.pref1};
-            uint32_t first, last;
-            unit_range(S.pref1[n_groups], first, last);
+            const uint32_t first = S.range[0], last = S.range[1];
             if (!run_phase<2, NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
         }
         stamp(5);
@@ -991,8 +1123,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         // ---- phase 2: down projections of every (group, token tile, 128-row block) into the fp32 partial rows
         {
             PhaseCtx C{region_a, S.full2, S.empty2, red, S.pref2};
-            uint32_t first, last;
-            unit_range(S.pref2[n_groups], first, last);
+            const uint32_t first = S.range[2], last = S.range[3];
             if (!run_phase<1, 4>(P, geo2, C, n_groups, first, last, seq2, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
         }
         if (!(alive = grid_barrier(M, S, epoch))) break;
@@ -1005,6 +1136,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         }
         if (!(alive = grid_barrier(M, S, epoch))) break;
     }
+    clock_pair(1);
 }
 
 }  // namespace
@@ -1029,7 +1161,7 @@ size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
     const size_t pairs = (size_t)n_tokens * c.top_k;
     const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
                          ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 6 : 0);
-    if ((size_t)c.d * (MEGA_ROWS_PER_PASS * 4 + (CW + 1) * 2) > (size_t)RING_BYTES + RED_BYTES)
+    if ((size_t)c.d * (MEGA_MAX_EB * 4 + (CW + 1) * MEGA_MAX_TT * 2) > (size_t)RING_BYTES + RED_BYTES)
         return (size_t)1 << 30;   // the router staging does not fit: the caller falls back to the per-layer launches
     return (size_t)RING_BYTES + RED_BYTES + lists + 64;
 }

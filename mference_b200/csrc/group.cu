@@ -81,13 +81,11 @@ __global__ void group_finalize_kernel(const uint32_t* __restrict__ counts, uint3
                                       uint32_t* __restrict__ offsets, mfb_group* __restrict__ groups,
                                       uint32_t* __restrict__ n_groups, uint32_t* __restrict__ tile_prefix,
                                       mfb_pair* __restrict__ sorted) {
-    __shared__ uint32_t s_off[MFB_MAX_EXPERTS + 1];
     __shared__ uint32_t s_total;
     if (threadIdx.x == 0) {
         uint32_t run = 0, ng = 0, tiles = 0;
         for (uint32_t e = 0; e < num_experts; ++e) {
             const uint32_t c = counts[e];
-            s_off[e] = run;
             offsets[e] = c ? run : 0xFFFFFFFFu;
             if (c) {
                 groups[ng].expert = e;

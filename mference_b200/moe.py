@@ -230,9 +230,10 @@ class MoE:
     def encode_residual_add(self, a, b, out):
         L.check(self.lib.mfb_residual_add(self.handle, _stream(), _ptr(a), _ptr(b), a.numel(), _ptr(out)))
 
-    def set_generic(self, on: bool):
-        """Route every call through the generic kernels instead of the shape-specialised fast ones."""
-        L.check(self.lib.mfb_moe_set_generic(self.handle, 1 if on else 0))
+    def set_generic(self, on):
+        """True / 1: route every call through the generic kernels instead of the shape-specialised fast ones.
+        2: fast kernels, but a stack runs layer by layer and phase by phase instead of as one fused launch."""
+        L.check(self.lib.mfb_moe_set_generic(self.handle, int(on)))
 
     def set_trace(self, stamps):
         """Attach (or detach with None) a uint64 [n_layers, 8] CUDA tensor for per-phase global-timer stamps."""
