@@ -170,6 +170,26 @@ int32_t mfb_router_topk(mfb_moe* moe, void* stream, const void* x, uint32_t ldx,
 int32_t mfb_slot_lookup(mfb_moe* moe, void* stream, const uint32_t* idx, uint32_t n_tokens,
                         const int16_t* slot_of, uint64_t slot_stride, uint64_t* out_offsets, uint32_t* out_all_hit);
 
+/* Router top-k without a handle and without any allocation (no counterpart in the reference, whose wrappers are
+ * handed a pre-allocated logits buffer by their caller, MoE.swift:136-150): same kernels and the same results, bit
+ * for bit, as mfb_router_topk, but the fp32 logits scratch is a fixed array inside the library's device image, so
+ * that a host which may not allocate device memory - its whole budget lives in its own pool, it runs under a
+ * memory cap, or it is inside a region where allocation calls are not allowed - can still route a decode batch.
+ *  - Limit: n_tokens <= MFB_STATIC_ROUTER_MAX_TOKENS and num_experts <= MFB_MAX_EXPERTS; more rows return
+ *    MFB_ERR_CAPACITY (use mfb_router_topk with a handle for those).
+ *  - The first call on each device (with that device current) looks up the scratch array's device address; make
+ *    that first call before starting a stream capture.  Later calls only launch the two kernels.
+ *  - The scratch is one array per device shared by all callers: two calls that may overlap in time (different
+ *    streams, different threads) race on it.  Serialise them on one stream or with events.
+ *  - Nothing needs zeroing between calls: each call overwrites the part of the scratch it reads.
+ * x: [n_tokens, ldx] activations of x_dtype (MFB_DT_BF16 / MFB_DT_F16); router_w: bf16 [num_experts, d]; the other
+ * arguments have the meaning of the same-named fields of mfb_moe_config and mfb_layer_weights. */
+#define MFB_STATIC_ROUTER_MAX_TOKENS 64
+int32_t mfb_router_topk_static(void* stream, const void* x, uint32_t x_dtype, uint32_t ldx, uint32_t n_tokens, uint32_t d,
+                               const void* router_w, const float* logit_bias, uint32_t num_experts, uint32_t top_k,
+                               uint32_t router_mode, const void* per_expert_scale, const float* correction_bias,
+                               float route_scale, uint32_t* out_idx, uint16_t* out_w);
+
 /* ---- decode -------------------------------------------------------------------------------------------- */
 
 /* Routed + shared expert FFN with the weighted combine for n_tokens rows:

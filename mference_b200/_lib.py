@@ -84,6 +84,7 @@ SIGNATURES = {
     "mfb_router_select": (_I32, [_V, _V, _V, _U32, _V, _V, _V, _V]),
     "mfb_router_topk": (_I32, [_V, _V, _V, _U32, _U32, C.POINTER(LayerWeightsC), _V, _V]),
     "mfb_slot_lookup": (_I32, [_V, _V, _V, _U32, _V, _U64, _V, _V]),
+    "mfb_router_topk_static": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _U32, _U32, _U32, _V, _V, C.c_float, _V, _V]),
     "mfb_moe_decode": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, _V, _V]),
     "mfb_moe_experts": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, C.POINTER(_U32), _U32, _I32]),
     "mfb_moe_combine": (_I32, [_V, _V, _U32, _V, _I32, _V, _V]),

@@ -13,7 +13,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libmfb200.so")
 
-SOURCES = ["api.cu", "router.cu", "glue.cu", "group.cu", "decode.cu", "decode_mma.cu", "prefill_tc.cu", "synth.cu"]
+SOURCES = ["api.cu", "router.cu", "router_static.cu", "glue.cu", "group.cu", "decode.cu", "decode_mma.cu", "prefill_tc.cu",
+           "synth.cu"]
 EXTRA = ["pool.cpp"]
 
 NVCC_FLAGS = [

@@ -247,6 +247,17 @@ class MoE:
         return st.value
 
 
+def encode_router_static(x, router_w, out_indices, out_weights, *, top_k: int, x_dtype: int = L.DT_BF16,
+                         router_mode: int = L.ROUTER_SOFTMAX_TOPK, logit_bias=None, per_expert_scale=None,
+                         correction_bias=None, route_scale: float = 1.0):
+    """Router top-k for at most 64 rows without a handle and without allocating (mfb_router_topk_static): the
+    logits scratch is a fixed device array inside the library.  Calls that may overlap in time race on it."""
+    L.check(L.load().mfb_router_topk_static(_stream(), _ptr(x), x_dtype, x.stride(0), x.shape[0], x.shape[1], _ptr(router_w),
+                                            _ptr(logit_bias), router_w.shape[0], top_k, router_mode,
+                                            _ptr(per_expert_scale), _ptr(correction_bias), route_scale,
+                                            _ptr(out_indices), _ptr(out_weights)))
+
+
 # --------------------------------------------------------------------------------------------- synthetic layers
 
 def synth_normal(root: int, label: str, n: int, *, mean=0.0, std=1.0, absolute=False, dtype=L.DT_BF16,
