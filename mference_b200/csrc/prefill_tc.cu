@@ -1,13 +1,513 @@
+// Prefill / ragged-batch grouped expert FFN on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a only.
+//
+// Replaces PrefillGroupedRoutedMoE.encodeStreamedBatched and its kernels
+// (Sources/Mference/Kernels/Prefill/PrefillGroupedRoutedMoE.swift:391-466, Sources/Mference/Metal/Prefill/prefill.metal:748-820;
+// tensor-unit precedent mpp_prefill_affine_threadgroup_f16): tokens sorted by expert form a ragged grouped GEMM
+//     phase 1   H[pair, f] = act(X[pair,:] . Wgate[f,:]) * (X[pair,:] . Wup[f,:])      contraction over d
+//     phase 2   P[pair, d] = H[pair,:] . Wdown[d,:]                                    contraction over f
+// With many rows per expert this is a dense contraction, so it goes to the tensor cores.
+//
+// Shape of one MMA tile: M = 128 *weight rows*, N = up to 256 *token rows* of one expert, K in chunks of 64.  The
+// weights are the A operand: their row count is always a multiple of 128, while the ragged side (tokens of an
+// expert, from a handful to thousands) rides in N, which the hardware accepts in steps of 16.  Accumulators live in
+// TMEM: phase 1 keeps gate in columns [0, 256) and up in [256, 512) of the CTA's 512-column allocation.
+//
+// Roles inside a CTA (320 threads), connected by mbarriers, every wait bounded:
+//   warp 0      TMA: the activation chunk [N x 64] fp16 of the current token rows (gathered once per call into
+//               expert-major order, so a group's rows are contiguous) lands in shared memory in the 128-byte swizzle
+//   warp 1      one elected thread issues tcgen05.mma (A and B from shared memory, D in TMEM) and tcgen05.commit
+//   warps 2-9   dequantise: packed 4-bit codes + fp16/bf16 scale and bias -> fp16 weights, written straight into the
+//               swizzled K-major layout the MMA reads; the packed bytes come from global memory one chunk ahead
+//   warps 2-5   also the epilogue: tcgen05.ld the accumulators (warp w reads TMEM lanes 32 (w % 4) ...), apply the
+//               activation (phase 1) and store fp16 hidden rows / fp32 partial rows (phase 2)
+// The K order inside each 8-element piece is the one the mask-unpack of a packed word yields (0 4 1 5 2 6 3 7);
+// the gather kernel and the phase-1 epilogue store activations in the same order, so nothing is shuffled.
+#include <cuda.h>
+
 #include "prefill_tc.cuh"
 
 namespace mfb {
 
-bool tc_supported(const mfb_moe_config&) { return false; }
-void tc_release(mfb_moe*) {}
-int32_t tc_grouped_ffn(mfb_moe*, cudaStream_t, const mfb_layer_weights*, const void*, uint32_t, uint32_t,
-                       const mfb_pair*, const mfb_group*, const uint32_t*, uint32_t, bool, float*, uint32_t) {
-    set_error("tensor-core grouped FFN is not built");
-    return MFB_ERR_UNSUPPORTED_SHAPE;
+namespace {
+
+constexpr uint32_t TC_M = 128;          // weight rows per tile
+constexpr uint32_t TC_KC = 64;          // k elements per chunk = one 128-byte swizzle row of fp16
+constexpr uint32_t TC_BOX_ROWS = 64;    // token rows per TMA box
+constexpr uint32_t TC_DQ_WARPS = 8;
+constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS) * 32;
+constexpr uint32_t TC_A_BYTES = TC_M * 128;            // one matrix tile of one chunk
+constexpr uint32_t TC_B_BYTES = TC_TILE_N * 128;       // one activation tile of one chunk
+constexpr uint32_t TC_TMEM_COLS = 512;
+constexpr long long TC_WAIT_CYCLES = 400000000ll;      // ~0.2 s
+
+struct TcParams {
+    const uint8_t* pool;
+    uint64_t slot_stride;
+    const int16_t* slot_of;
+    const uint8_t* shared_blob;
+    mfb_expert_offsets routed_off, shared_off;
+    uint32_t d, f, num_experts, bits, shared_bits, scale_dtype, activation;
+    float limit;
+    const mfb_pair* sorted;
+    const mfb_group* groups;
+    const uint32_t* n_groups;
+    const uint32_t* tile_prefix;   // [n_groups + 1] exclusive prefix of ceil(pair_count / TC_TILE_N)
+    __half* acts16;                // [rows, f] hidden activations in sorted-pair order (phase 1 out, phase 2 in)
+    float* partial;                // [token * slots + rank, d]
+    uint32_t slots;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait; false when the limit runs out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, fp16 inputs, fp32 accumulate; issued by one thread.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier when every MMA this thread has issued so far has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows in the 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc(const void* tile) {
+    const uint64_t addr = (smem_u32(tile) & 0x3FFFFu) >> 4;
+    return addr | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: fp16 A and B, both K-major, fp32 D, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((TC_M >> 4) << 24);
+}
+
+// Position of element e (0..7) of an 8-element piece in the stored order 0 4 1 5 2 6 3 7.
+__host__ __device__ inline uint32_t tc_perm8(uint32_t e) { return ((e & 3u) << 1) | (e >> 2); }
+
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+// Eight 4-bit codes of one packed word -> eight fp16 weights q * scale + bias, as four half2 in the stored order.
+__device__ __forceinline__ uint4 dequant_word4(uint32_t w, uint32_t scale2, uint32_t bias2) {
+    constexpr uint32_t MAGIC = 0x64006400u, SIXTEENTH = 0x2C002C00u, M64 = 0xD400D400u;
+    const uint32_t hi = w >> 8;
+    uint4 o;
+    o.x = h2_fma(h2_sub((w & 0x000F000Fu) | MAGIC, MAGIC), scale2, bias2);            // codes 0, 4
+    o.y = h2_fma(h2_fma((w & 0x00F000F0u) | MAGIC, SIXTEENTH, M64), scale2, bias2);   // codes 1, 5
+    o.z = h2_fma(h2_sub((hi & 0x000F000Fu) | MAGIC, MAGIC), scale2, bias2);           // codes 2, 6
+    o.w = h2_fma(h2_fma((hi & 0x00F000F0u) | MAGIC, SIXTEENTH, M64), scale2, bias2);  // codes 3, 7
+    return o;
+}
+
+__device__ __forceinline__ uint32_t scale_pair(uint16_t bits, uint32_t dtype) {
+    __half h = dtype == MFB_DT_BF16 ? __float2half_rn(__uint_as_float((uint32_t)bits << 16)) : __ushort_as_half(bits);
+    const uint32_t u = __half_as_ushort(h);
+    return u | (u << 16);
+}
+
+struct Item {
+    const uint8_t* blob;
+    mfb_expert_offsets off;
+    uint32_t pair_start, count, row0, n, n_mma, ok, shared;
+};
+
+// Work item `it` -> (group, token tile, weight-row tile); the same arithmetic in every role.
+__device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* tp_s, uint32_t n_groups, uint32_t it,
+                                            uint32_t n_row_tiles) {
+    Item I;
+    const uint32_t tt = it / n_row_tiles;
+    uint32_t lo = 0, hi = n_groups;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) / 2;
+        if (tp_s[mid] <= tt) lo = mid; else hi = mid;
+    }
+    const mfb_group g = P.groups[lo];
+    const uint32_t n0 = (tt - tp_s[lo]) * TC_TILE_N;
+    I.pair_start = g.pair_start + n0;
+    I.count = g.pair_count;
+    I.n = min(TC_TILE_N, g.pair_count - n0);
+    I.n_mma = max(16u, (I.n + 15u) & ~15u);
+    I.row0 = (it % n_row_tiles) * TC_M;
+    I.shared = g.expert >= P.num_experts;
+    I.ok = 1;
+    if (I.shared) {
+        I.blob = P.shared_blob; I.off = P.shared_off; I.ok = P.shared_blob != nullptr;
+    } else {
+        int64_t slot = g.expert;
+        if (P.slot_of) slot = P.slot_of[g.expert];
+        I.ok = slot >= 0;
+        I.blob = P.pool + (uint64_t)(slot < 0 ? 0 : slot) * P.slot_stride;
+        I.off = P.routed_off;
+    }
+    return I;
+}
+
+struct TcShared {
+    uint64_t full_a[4], full_b[4], empty[4], acc_full, acc_empty;
+    uint32_t tmem_base, abort;
+    uint32_t tp[MFB_MAX_EXPERTS + 2];
+};
+
+template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P, const __grid_constant__ CUtensorMap map_b) {
+    constexpr uint32_t NMAT = PHASE == 1 ? 2 : 1;
+    constexpr uint32_t STAGE_BYTES = NMAT * TC_A_BYTES + TC_B_BYTES;
+    constexpr uint32_t STAGES = PHASE == 1 ? 3 : 4;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ TcShared S;
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t K = PHASE == 1 ? P.d : P.f, rows = PHASE == 1 ? P.f : P.d;
+    const uint32_t n_chunks = K / TC_KC, n_row_tiles = rows / TC_M;
+    const uint32_t n_groups = *P.n_groups;
+    for (uint32_t i = threadIdx.x; i <= n_groups; i += blockDim.x) S.tp[i] = P.tile_prefix[i];
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&S.full_a[s], TC_DQ_WARPS); mbar_init(&S.full_b[s], 1); mbar_init(&S.empty[s], 1); }
+        mbar_init(&S.acc_full, 1);
+        mbar_init(&S.acc_empty, 4);
+        S.abort = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp == 0) tmem_alloc(&S.tmem_base, TC_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = S.tmem_base;
+    const uint32_t total = S.tp[n_groups] * n_row_tiles;
+    volatile uint32_t* abort_flag = &S.abort;
+    auto fail = [&]() { *abort_flag = 1u; atomicOr(P.status, STATUS_MBAR_TIMEOUT); };
+    auto stage_a = [&](uint32_t s, uint32_t m) { return smem + s * STAGE_BYTES + m * TC_A_BYTES; };
+    auto stage_b = [&](uint32_t s) { return smem + s * STAGE_BYTES + NMAT * TC_A_BYTES; };
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- activation tiles by TMA
+        uint32_t seq = 0;
+        for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
+            if (!I.ok) continue;
+            const uint32_t copies = (I.n_mma + TC_BOX_ROWS - 1) / TC_BOX_ROWS;
+            for (uint32_t c = 0; c < n_chunks; ++c, ++seq) {
+                const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
+                if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); break; }
+                if (lane == 0) {
+                    mbar_expect_tx(&S.full_b[s], copies * TC_BOX_ROWS * 128);
+                    for (uint32_t j = 0; j < copies; ++j)
+                        tma_load_2d(stage_b(s) + j * TC_BOX_ROWS * 128, &map_b, c * TC_KC, I.pair_start + j * TC_BOX_ROWS, &S.full_b[s]);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issue
+        uint32_t seq = 0, item = 0;
+        for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
+            if (!I.ok) continue;
+            if (!mbar_wait(&S.acc_empty, (item & 1u) ^ 1u)) { fail(); break; }
+            tc_fence_after();
+            const uint32_t idesc = instr_desc(I.n_mma);
+            bool ok = true;
+            for (uint32_t c = 0; c < n_chunks && ok; ++c, ++seq) {
+                const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
+                if (!mbar_wait(&S.full_a[s], ph) || !mbar_wait(&S.full_b[s], ph)) { fail(); ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint64_t b_desc = smem_desc(stage_b(s));
+#pragma unroll
+                    for (uint32_t m = 0; m < NMAT; ++m) {
+                        const uint64_t a_desc = smem_desc(stage_a(s, m));
+#pragma unroll
+                        for (uint32_t kk = 0; kk < TC_KC / 16; ++kk)   // 16 k per MMA = 32 bytes along the swizzled row
+                            umma_f16(tmem + m * TC_TILE_N, a_desc + kk * 2, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
+                    }
+                    umma_commit(&S.empty[s]);   // frees the stage once these MMAs have read it
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(&S.acc_full);
+            __syncwarp();
+            ++item;
+        }
+    } else {
+        // ---------------------------------------------------------------- dequantise, then (warps 2-5) epilogue
+        const uint32_t td = threadIdx.x - 64;                 // 0..255
+        const uint32_t r = td & (TC_M - 1), part = td >> 7;   // phase 1: part = matrix; phase 2: part = half of the chunk
+        const uint32_t words = PHASE == 1 ? 8 : 4, word0 = PHASE == 1 ? 0 : part * 4;
+        const uint32_t mat = PHASE == 1 ? part : 0;
+        const bool epi = warp < 6;
+        const uint32_t q = warp & 3u;                         // TMEM lane quarter this warp may read
+        uint32_t seq = 0, item = 0;
+        for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
+            if (!I.ok) {
+                if (PHASE == 2 && epi) {   // a non-resident expert contributes nothing: clear its partial rows
+                    const uint32_t dcol = I.row0 + 32 * ((warp - 2) & 3u) + lane;
+                    for (uint32_t n = 0; n < I.n; ++n) {
+                        const mfb_pair pr = P.sorted[I.pair_start + n];
+                        P.partial[((size_t)pr.token * P.slots + pr.rank) * P.d + dcol] = 0.0f;
+                    }
+                }
+                continue;
+            }
+            const uint32_t w_off = PHASE == 1 ? (mat ? I.off.up_w : I.off.gate_w) : I.off.down_w;
+            const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
+            const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
+            const size_t row = I.row0 + r;
+            const uint4* wrow = reinterpret_cast<const uint4*>(I.blob + w_off + row * (K / 2)) + (word0 >> 2);
+            const uint4* srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
+            const uint4* brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
+            uint4 pre[2], cur[2];
+            pre[0] = wrow[0];
+            if (PHASE == 1) pre[1] = wrow[1];
+            uint4 sc8 = make_uint4(0, 0, 0, 0), bi8 = make_uint4(0, 0, 0, 0);
+            bool ok = true;
+            for (uint32_t c = 0; c < n_chunks; ++c, ++seq) {
+                const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
+                if ((c & 7u) == 0) { sc8 = srow[c >> 3]; bi8 = brow[c >> 3]; }
+                cur[0] = pre[0]; cur[1] = pre[1];
+                if (c + 1 < n_chunks) {
+                    pre[0] = wrow[(c + 1) * 2];
+                    if (PHASE == 1) pre[1] = wrow[(c + 1) * 2 + 1];
+                }
+                const uint32_t sw = (&sc8.x)[(c & 7u) >> 1], bw = (&bi8.x)[(c & 7u) >> 1];
+                const uint32_t s2 = scale_pair((uint16_t)((c & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
+                const uint32_t b2 = scale_pair((uint16_t)((c & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
+                if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
+                uint8_t* dst = stage_a(s, mat) + r * 128;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) {
+                    if (j >= words) break;
+                    const uint32_t wd = (&cur[j >> 2].x)[j & 3u];
+                    const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
+                    *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(wd, s2, b2);
+                }
+                fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&S.full_a[s]);
+            }
+            if (!ok) break;
+            if (epi) {
+                if (!mbar_wait(&S.acc_full, item & 1u)) { fail(); break; }
+                tc_fence_after();
+                const uint32_t lane_row = 32 * q + lane;
+                const uint32_t taddr = tmem + ((32 * q) << 16);
+                const uint32_t out_row = I.row0 + lane_row;
+                for (uint32_t col0 = 0; col0 < I.n; col0 += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + col0, v);
+                    if (PHASE == 1) {
+                        float u[32];
+                        tmem_ld32(taddr + TC_TILE_N + col0, u);
+                        const uint32_t fpos = (out_row & ~7u) + tc_perm8(out_row & 7u);
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            if (col0 + i >= I.n) break;
+                            float gate = v[i], up = u[i];
+                            if (!I.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+                                gate = fminf(gate, P.limit);
+                                up = fminf(fmaxf(up, -P.limit), P.limit);
+                            }
+                            float a = hidden_act(gate, (int)P.activation) * up;
+                            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                            P.acts16[(size_t)(I.pair_start + col0 + i) * P.f + fpos] = __float2half_rn(a);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            if (col0 + i >= I.n) break;
+                            const mfb_pair pr = P.sorted[I.pair_start + col0 + i];
+                            P.partial[((size_t)pr.token * P.slots + pr.rank) * P.d + out_row] = v[i];
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&S.acc_empty);
+            }
+            ++item;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TC_TMEM_COLS);
+}
+
+// xs16[pos, :] = fp16(x[sorted[pos].token, :]) in the stored k order, for every sorted pair.
+__global__ void tc_gather_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t d,
+                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, __half* __restrict__ xs16) {
+    const uint32_t pos = blockIdx.x;
+    if (pos >= n_rows) return;
+    const size_t src = (size_t)sorted[pos].token * ldx;
+    for (uint32_t k = threadIdx.x; k < d; k += blockDim.x) {
+        float v = load_act(x, src + k, x_dtype);
+        v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+        xs16[(size_t)pos * d + (k & ~7u) + tc_perm8(k & 7u)] = __float2half_rn(v);
+    }
+}
+
+// tile_prefix[g] = number of TC_TILE_N-row token tiles in groups [0, g); one warp.
+__global__ void tc_tile_prefix_kernel(const mfb_group* __restrict__ groups, const uint32_t* __restrict__ n_groups,
+                                      uint32_t* __restrict__ tile_prefix) {
+    const uint32_t ng = *n_groups, lane = threadIdx.x;
+    const uint32_t per = (ng + 31) / 32, g0 = lane * per;
+    uint32_t local = 0;
+    for (uint32_t j = 0; j < per; ++j)
+        if (g0 + j < ng) local += (groups[g0 + j].pair_count + TC_TILE_N - 1) / TC_TILE_N;
+    uint32_t incl = local;
+    for (uint32_t off = 1; off < 32; off <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (lane >= off) incl += n;
+    }
+    uint32_t run = incl - local;
+    for (uint32_t j = 0; j < per; ++j)
+        if (g0 + j < ng) { tile_prefix[g0 + j] = run; run += (groups[g0 + j].pair_count + TC_TILE_N - 1) / TC_TILE_N; }
+    if (lane == 31) tile_prefix[ng] = incl;
+}
+
+struct TcState {
+    CUtensorMap map_x, map_h;
+    uint64_t rows_cap = 0;
+    bool ready = false;
+};
+
+constexpr size_t TC_SMEM_BYTES = 3 * (2 * TC_A_BYTES + TC_B_BYTES) + 1024;   // = 4 * (TC_A_BYTES + TC_B_BYTES) + 1024
+
+int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {inner * sizeof(__half)};
+    const cuuint32_t box[2] = {TC_KC, TC_BOX_ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
+        return MFB_ERR_CUDA;
+    }
+    return MFB_OK;
+}
+
+}  // namespace
+
+bool tc_supported(const mfb_moe_config& c) {
+    // 4-bit codes; scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512
+    return c.bits == 4 && (c.shared_bits == 0 || c.shared_bits == 4) && c.d % 512 == 0 && c.f % 512 == 0;
+}
+
+void tc_release(mfb_moe* m) {
+    delete static_cast<TcState*>(m->tma);
+    m->tma = nullptr;
+}
+
+int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                       uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups, const uint32_t* n_groups,
+                       uint32_t max_groups, bool routed_only, float* partial, uint32_t slots) {
+    const mfb_moe_config& c = m->cfg;
+    Arena& a = m->a;
+    MFB_REQUIRE(a.xs16 && a.acts16, MFB_ERR_INVALID_ARGUMENT, "tensor-core path: the handle was created without MFB_FLAG_PREFILL_TENSOR_CORE");
+    TcState* st = static_cast<TcState*>(m->tma);
+    if (!st) {
+        st = new TcState();
+        m->tma = st;
+    }
+    if (!st->ready) {
+        st->rows_cap = m->max_rows + TC_ROW_PAD;
+        int32_t rc = make_map(&st->map_x, a.xs16, c.d, st->rows_cap);
+        if (rc) return rc;
+        rc = make_map(&st->map_h, a.acts16, c.f, st->rows_cap);
+        if (rc) return rc;
+        MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        st->ready = true;
+    }
+    const uint32_t n_rows = n_tokens * c.top_k + (routed_only ? 0u : n_tokens);
+    TcParams P;
+    P.pool = (const uint8_t*)w->pool; P.slot_stride = w->slot_stride; P.slot_of = w->slot_of;
+    P.shared_blob = routed_only ? nullptr : (const uint8_t*)w->shared_blob;
+    P.routed_off = w->routed_off; P.shared_off = w->shared_off;
+    P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.bits = c.bits; P.shared_bits = c.shared_bits;
+    P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
+    P.sorted = sorted; P.groups = groups; P.n_groups = n_groups; P.tile_prefix = a.tile_prefix;
+    P.acts16 = a.acts16; P.partial = partial; P.slots = slots; P.status = a.status;
+
+    tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, a.tile_prefix);
+    tc_gather_kernel<<<n_rows, 256, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, a.xs16);
+    const uint32_t token_tiles = (n_rows + TC_TILE_N - 1) / TC_TILE_N + max_groups;   // upper bound
+    const uint32_t items1 = token_tiles * (c.f / TC_M), items2 = token_tiles * (c.d / TC_M);
+    const uint32_t grid1 = items1 < (uint32_t)m->sm_count ? items1 : (uint32_t)m->sm_count;
+    const uint32_t grid2 = items2 < (uint32_t)m->sm_count ? items2 : (uint32_t)m->sm_count;
+    tc_ffn_kernel<1><<<grid1, TC_THREADS, TC_SMEM_BYTES, s>>>(P, st->map_x);
+    tc_ffn_kernel<2><<<grid2, TC_THREADS, TC_SMEM_BYTES, s>>>(P, st->map_h);
+    count_launches(4);
+    MFB_CUDA(cudaGetLastError());
+    return MFB_OK;
 }
 
 }  // namespace mfb

@@ -5,7 +5,7 @@
 
 namespace mfb {
 
-constexpr uint32_t TC_TILE_N = 128;   // token rows per tile of the grouped GEMM
+constexpr uint32_t TC_TILE_N = 256;   // token rows per tile of the grouped GEMM (the N of one tcgen05.mma)
 constexpr uint32_t TC_ROW_PAD = 256;  // spare rows behind the gathered activations so a tile may over-read
 
 bool tc_supported(const mfb_moe_config& c);

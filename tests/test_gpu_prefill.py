@@ -42,3 +42,61 @@ def test_grouped_ffn_and_reduce_match_oracle(d, f, E, K, bits, T):
     assert O.rel_l2(partial, ref) <= TOL_REL_L2
     h2 = O.reduce_token_major(ref.reshape(T, K, d), w, T, K, d)
     assert O.rel_l2(y, h2) <= TOL_REL_L2
+
+
+# ---- tensor-core (tcgen05 / TMEM) grouped GEMM ---------------------------------------------------------------
+# d and f multiples of 512; token counts chosen to give groups below 16 rows, around a TMA box, and above one
+# 256-row MMA tile (several passes per expert).
+TC_CASES = [(512, 512, 8, 2, 40), (1024, 512, 16, 4, 300), (512, 512, 4, 2, 700), (2048, 512, 16, 8, 128)]
+
+
+@pytest.mark.parametrize("d,f,E,K,T", TC_CASES)
+def test_tensor_core_grouped_ffn_matches_oracle(d, f, E, K, T):
+    W = O.LayerWeights(d, f, E, K, bits=4, shared=False)
+    x = make_x("x.tc", T, d)
+    lg = O.router_logits(x, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, K)
+    partial, y, sp, moe = _grouped(W, x, idx, w, tensor_core=True)
+    assert moe.device_status() == 0
+    pairs = np.array([tuple(r) for r in sp], dtype=O.PAIR_DTYPE)
+    ref_sorted = O.pair_partials(W, x, O.DT_BF16, pairs)
+    ref = np.zeros((T * K, d), dtype=np.float32)
+    ref[pairs["token"] * K + pairs["rank"]] = ref_sorted
+    assert np.isfinite(partial).all()
+    assert O.rel_l2(partial, ref) <= TOL_REL_L2
+    # per pair row as well: a wrong tile would hide in the aggregate
+    rows = pairs["token"] * K + pairs["rank"]
+    err = np.linalg.norm(partial[rows] - ref[rows], axis=1) / np.maximum(np.linalg.norm(ref[rows], axis=1), 1e-20)
+    assert err.max() <= 2 * TOL_REL_L2
+    h2 = O.reduce_token_major(ref.reshape(T, K, d), w, T, K, d)
+    assert O.rel_l2(y, h2) <= TOL_REL_L2
+
+
+def test_tensor_core_matches_generic_kernels():
+    d, f, E, K, T = 1024, 512, 16, 4, 200
+    W = O.LayerWeights(d, f, E, K, bits=4, shared=False)
+    x = make_x("x.tc2", T, d)
+    lg = O.router_logits(x, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, K)
+    p_tc, y_tc, _, _ = _grouped(W, x, idx, w, tensor_core=True)
+    p_gen, y_gen, _, _ = _grouped(W, x, idx, w, tensor_core=False)
+    assert O.rel_l2(p_tc, p_gen) <= TOL_REL_L2
+
+
+def test_tensor_core_prefill_layer_matches_decode_layer():
+    """The whole prefill layer (RMSNorm, router, sort, grouped GEMM incl. the shared expert, reduce + residual) on the
+    tensor-core path against the decode-path layer on the same rows."""
+    import torch
+    from mference_b200.moe import MoE
+    d, f, E, K, T = 1024, 512, 16, 4, 150
+    W = O.LayerWeights(d, f, E, K, bits=4, shared=True)
+    lw = upload_layer(W)
+    x = to_dev16(make_x("x.tc3", T, d), O.DT_BF16)
+    moe_tc = MoE(d, f, E, K, max_tokens=T, tensor_core_prefill=True)
+    moe_ref = MoE(d, f, E, K, max_tokens=T)
+    y_tc, y_ref = torch.empty_like(x), torch.empty_like(x)
+    moe_tc.encode_layer_prefill(lw, x, y_tc)
+    moe_ref.encode_layer(lw, x, y_ref)
+    torch.cuda.synchronize()
+    assert moe_tc.device_status() == 0
+    assert O.rel_l2(y_tc.float().cpu().numpy(), y_ref.float().cpu().numpy()) <= TOL_REL_L2
