@@ -261,6 +261,59 @@ int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const u
 int32_t mfb_moe_layer_prefill(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* h_in, void* h_out,
                               uint32_t n_tokens);
 
+/* ---- expert-slot cache over an HBM-resident pool ------------------------------------------------------ */
+
+/* Replaces PreadExpertStreamer (Sources/Mference/Infrastructure/Streaming/PreadExpertStreamer.swift:57-580): a slab of
+ * `slot_count` slots in HBM, an expert -> slot table (int16, -1 = not resident) on the device for the FFN kernels
+ * (mfb_layer_weights.pool / slot_stride / slot_of), and the same cache planning on the host.  One pool per layer.
+ * The reference reads missing experts from SSD with pread; here they are copied from pinned host memory. */
+typedef struct mfb_pool mfb_pool;
+#define MFB_POOL_LFU 0u        /* least frequently used expert first, recency as tie break (the reference's default) */
+#define MFB_POOL_LRU 1u
+#define MFB_POOL_HOST_ONLY 1u  /* flag: planning bookkeeping only, no device memory */
+int32_t mfb_pool_create(uint32_t num_experts, uint64_t slot_bytes, uint32_t slot_count, uint32_t policy, uint32_t flags,
+                        mfb_pool** out);
+int32_t mfb_pool_destroy(mfb_pool* pool);
+/* Device slab, bytes between slots, device slot table: the three fields of mfb_layer_weights. */
+int32_t mfb_pool_info(const mfb_pool* pool, void** slab, uint64_t* slot_stride, const int16_t** slot_of_device);
+/* planExpertsCachedIfPossible (PreadExpertStreamer.swift:197-269): out_slots[i] = slot of experts[i], out_miss[i] = 1
+ * if it has to be filled.  Hits keep their slots; `avoid_slots` (slots queued GPU work still reads) are never chosen
+ * as victims; MFB_ERR_NO_SLOT when the misses cannot be placed (nothing is changed then). */
+int32_t mfb_pool_plan(mfb_pool* pool, const int32_t* experts, uint32_t n, const int32_t* avoid_slots, uint32_t n_avoid,
+                      int32_t* out_slots, uint8_t* out_miss, uint32_t* out_hits);
+/* executeExpertCachePlan, first half (PreadExpertStreamer.swift:271-302): one asynchronous copy per miss from
+ * host_blobs[i] (pinned host memory, blob_bytes each) into its slot, on `stream`; the device table is refreshed
+ * first so that the victims read -1 before their bytes change.  MFB_ERR_IO for a missing or oversized source. */
+int32_t mfb_pool_fill_async(mfb_pool* pool, void* stream, const int32_t* experts, const int32_t* slots, const uint8_t* miss,
+                            uint32_t n, const void* const* host_blobs, uint64_t blob_bytes);
+/* executeExpertCachePlan, second half: the filled slots become hits on the host and, in stream order, on the device. */
+int32_t mfb_pool_publish(mfb_pool* pool, void* stream, const int32_t* experts, const int32_t* slots, const uint8_t* miss,
+                         uint32_t n);
+/* noteAllHitUse (PreadExpertStreamer.swift:427-440): usage accounting when the device-side lookup found every expert. */
+int32_t mfb_pool_note_all_hit(mfb_pool* pool, const int32_t* experts, uint32_t n);
+/* Host mirror of the slot table (num_experts entries). */
+int32_t mfb_pool_slot_of_host(mfb_pool* pool, int16_t* out);
+
+/* ---- expert parallelism (2, 4 or 8 GPUs of one box; batched / prefill workloads) ------------------------- */
+
+/* No counterpart in the reference (single device).  Experts are block-sharded, rank g owns experts
+ * [g * E/G, (g+1) * E/G); tokens stay on their home rank.  Per layer the host layer (mference_b200/ep.py) calls
+ * mfb_ep_plan + mfb_ep_pack, exchanges rows with an NCCL all-to-all, runs the grouped expert FFN on the received
+ * rows, exchanges the fp32 result rows back and calls mfb_ep_combine, which is bit-identical to the single-GPU
+ * weighted reduce (prefill_moe_reduce_token_major, prefill.metal:631-652: ranks ascending, fused multiply-add). */
+/* Send order of the n_tokens * top_k pairs: by (destination rank, token, rank slot).  perm[pos] = token * top_k + slot;
+ * inv = inverse of perm; counts[g] = pairs bound for rank g; local_expert[pos] = expert id relative to rank g's first. */
+int32_t mfb_ep_plan(void* stream, const uint32_t* idx, uint32_t n_tokens, uint32_t top_k, uint32_t num_experts, uint32_t world,
+                    uint32_t* perm, uint32_t* inv, int32_t* counts, int32_t* local_expert);
+/* rows[pos, :] = x[perm[pos] / top_k, :] for 16-bit activations (the dispatch send buffer). */
+int32_t mfb_ep_pack(void* stream, const void* x, uint32_t ldx, uint32_t d, const uint32_t* perm, uint32_t n_pairs,
+                    uint32_t top_k, void* rows);
+/* y[t,:] = dtype(residual[t,:] + shared_partial[t,:] + sum_k w[t,k] * recv[inv[t*top_k+k],:]); recv = the fp32 rows that
+ * came back, in send order; shared_partial and residual may be NULL. */
+int32_t mfb_ep_combine(void* stream, const float* recv, const uint32_t* inv, const uint16_t* route_w,
+                       const float* shared_partial, const void* residual, void* y, uint32_t n_tokens, uint32_t top_k,
+                       uint32_t d, uint32_t x_dtype);
+
 /* ---- glue ---------------------------------------------------------------------------------------------- */
 
 /* out = dtype(x * rsqrt(mean(x^2) + eps) * w).  Replaces rmsnorm_bf16w

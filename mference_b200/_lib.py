@@ -84,6 +84,17 @@ SIGNATURES = {
     "mfb_router_select": (_I32, [_V, _V, _V, _U32, _V, _V, _V, _V]),
     "mfb_router_topk": (_I32, [_V, _V, _V, _U32, _U32, C.POINTER(LayerWeightsC), _V, _V]),
     "mfb_slot_lookup": (_I32, [_V, _V, _V, _U32, _V, _U64, _V, _V]),
+    "mfb_pool_create": (_I32, [_U32, _U64, _U32, _U32, _U32, C.POINTER(_V)]),
+    "mfb_pool_destroy": (_I32, [_V]),
+    "mfb_pool_info": (_I32, [_V, C.POINTER(_V), C.POINTER(_U64), C.POINTER(_V)]),
+    "mfb_pool_plan": (_I32, [_V, _V, _U32, _V, _U32, _V, _V, C.POINTER(_U32)]),
+    "mfb_pool_fill_async": (_I32, [_V, _V, _V, _V, _V, _U32, _V, _U64]),
+    "mfb_pool_publish": (_I32, [_V, _V, _V, _V, _V, _U32]),
+    "mfb_pool_note_all_hit": (_I32, [_V, _V, _U32]),
+    "mfb_pool_slot_of_host": (_I32, [_V, _V]),
+    "mfb_ep_plan": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _V, _V]),
+    "mfb_ep_pack": (_I32, [_V, _V, _U32, _U32, _V, _U32, _U32, _V]),
+    "mfb_ep_combine": (_I32, [_V, _V, _V, _V, _V, _V, _V, _U32, _U32, _U32, _U32]),
     "mfb_router_topk_static": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _U32, _U32, _U32, _V, _V, C.c_float, _V, _V]),
     "mfb_moe_decode": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, _V, _V]),
     "mfb_moe_experts": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, C.POINTER(_U32), _U32, _I32]),

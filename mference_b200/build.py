@@ -14,8 +14,8 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libmfb200.so")
 
 SOURCES = ["api.cu", "router.cu", "router_static.cu", "glue.cu", "group.cu", "decode.cu", "decode_mma.cu", "prefill_tc.cu",
-           "synth.cu"]
-EXTRA = ["pool.cpp"]
+           "synth.cu", "pool.cu", "ep.cu"]
+EXTRA = []
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    link = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-ccbin", "/usr/bin/g++", "-o", LIB, *objs, "-lcudart", "-lcuda"]
+    link = [nvcc, "-shared", "-Wno-deprecated-gpu-targets", "-ccbin", "/usr/bin/g++", "-o", LIB, *objs, "-lcudart"]
     subprocess.run(link, check=True, env=env)
     return LIB
 

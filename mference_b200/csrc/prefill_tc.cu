@@ -74,11 +74,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const long long t0 = clock64();
     for (;;) {
         uint32_t done;
+        // the hint lets the hardware park the thread until the phase completes (or ~2 us pass): a waiting warp takes
+        // no issue slots from the dequantising ones and still wakes up at once
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+            : "=r"(done) : "r"(addr), "r"(parity), "r"(2000u) : "memory");
         if (done) return true;
         if (clock64() - t0 > TC_WAIT_CYCLES) return false;
     }
@@ -211,6 +213,7 @@ struct TcShared {
     uint64_t full_a[4], full_b[4], empty[4], acc_full, acc_empty;
     uint32_t tmem_base, abort;
     uint32_t tp[MFB_MAX_EXPERTS + 2];
+    uint32_t out_row[TC_TILE_N];   // phase 2: token * slots + rank of the current item's token columns
 };
 
 template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&S.full_a[s], TC_DQ_WARPS); mbar_init(&S.full_b[s], 1); mbar_init(&S.empty[s], 1); }
         mbar_init(&S.acc_full, 1);
-        mbar_init(&S.acc_empty, 4);
+        mbar_init(&S.acc_empty, TC_DQ_WARPS);
         S.abort = 0;
         fence_barrier_init();
     }
@@ -301,15 +304,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         const uint32_t r = td & (TC_M - 1), part = td >> 7;   // phase 1: part = matrix; phase 2: part = half of the chunk
         const uint32_t words = PHASE == 1 ? 8 : 4, word0 = PHASE == 1 ? 0 : part * 4;
         const uint32_t mat = PHASE == 1 ? part : 0;
-        const bool epi = warp < 6;
+        const uint32_t col_half = part;                       // epilogue: warps 2-5 take token columns [0, 128), warps 6-9 [128, 256)
         const uint32_t q = warp & 3u;                         // TMEM lane quarter this warp may read
         uint32_t seq = 0, item = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
             if (!I.ok) {
-                if (PHASE == 2 && epi) {   // a non-resident expert contributes nothing: clear its partial rows
+                if (PHASE == 2) {   // a non-resident expert contributes nothing: clear its partial rows
                     const uint32_t dcol = I.row0 + 32 * ((warp - 2) & 3u) + lane;
-                    for (uint32_t n = 0; n < I.n; ++n) {
+                    for (uint32_t n = col_half; n < I.n; n += 2) {
                         const mfb_pair pr = P.sorted[I.pair_start + n];
                         P.partial[((size_t)pr.token * P.slots + pr.rank) * P.d + dcol] = 0.0f;
                     }
@@ -320,46 +323,72 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
             const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
             const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
             const size_t row = I.row0 + r;
+            // phase 2: where each token column of this item goes; fetched now, parked in shared memory before the
+            // epilogue (a dependent global load per column inside the epilogue would serialise it)
+            uint32_t dest = 0;
+            if (PHASE == 2 && td < I.n) {
+                const mfb_pair pr = P.sorted[I.pair_start + td];
+                dest = pr.token * P.slots + pr.rank;
+            }
             const uint4* wrow = reinterpret_cast<const uint4*>(I.blob + w_off + row * (K / 2)) + (word0 >> 2);
             const uint4* srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
             const uint4* brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
-            uint4 pre[2], cur[2];
-            pre[0] = wrow[0];
-            if (PHASE == 1) pre[1] = wrow[1];
+            // packed codes travel in batches of four chunks, one batch ahead of the one in use: a load has four
+            // chunks of work to hide its latency behind
+            constexpr uint32_t BATCH = 4, PER = PHASE == 1 ? 2 : 1;   // uint4 per chunk for this thread
+            uint4 pre[BATCH * PER], cur[BATCH * PER];
+#pragma unroll
+            for (uint32_t i = 0; i < BATCH; ++i)
+#pragma unroll
+                for (uint32_t h = 0; h < PER; ++h) pre[i * PER + h] = wrow[i * 2 + h];
             uint4 sc8 = make_uint4(0, 0, 0, 0), bi8 = make_uint4(0, 0, 0, 0);
             bool ok = true;
-            for (uint32_t c = 0; c < n_chunks; ++c, ++seq) {
-                const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
-                if ((c & 7u) == 0) { sc8 = srow[c >> 3]; bi8 = brow[c >> 3]; }
-                cur[0] = pre[0]; cur[1] = pre[1];
-                if (c + 1 < n_chunks) {
-                    pre[0] = wrow[(c + 1) * 2];
-                    if (PHASE == 1) pre[1] = wrow[(c + 1) * 2 + 1];
-                }
-                const uint32_t sw = (&sc8.x)[(c & 7u) >> 1], bw = (&bi8.x)[(c & 7u) >> 1];
-                const uint32_t s2 = scale_pair((uint16_t)((c & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
-                const uint32_t b2 = scale_pair((uint16_t)((c & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
-                if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
-                uint8_t* dst = stage_a(s, mat) + r * 128;
+            for (uint32_t cb = 0; cb < n_chunks && ok; cb += BATCH) {   // n_chunks is a multiple of 8
+                if ((cb & 7u) == 0) { sc8 = srow[cb >> 3]; bi8 = brow[cb >> 3]; }
 #pragma unroll
-                for (uint32_t j = 0; j < 8; ++j) {
-                    if (j >= words) break;
-                    const uint32_t wd = (&cur[j >> 2].x)[j & 3u];
-                    const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
-                    *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(wd, s2, b2);
+                for (uint32_t i = 0; i < BATCH * PER; ++i) cur[i] = pre[i];
+                if (cb + BATCH < n_chunks) {
+#pragma unroll
+                    for (uint32_t i = 0; i < BATCH; ++i)
+#pragma unroll
+                        for (uint32_t h = 0; h < PER; ++h) pre[i * PER + h] = wrow[(cb + BATCH + i) * 2 + h];
                 }
-                fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&S.full_a[s]);
+                // this batch's four scale / bias pairs sit in two words of the eight-group vectors
+                const uint32_t sw0 = (cb & 4u) ? sc8.z : sc8.x, sw1 = (cb & 4u) ? sc8.w : sc8.y;
+                const uint32_t bw0 = (cb & 4u) ? bi8.z : bi8.x, bw1 = (cb & 4u) ? bi8.w : bi8.y;
+#pragma unroll
+                for (uint32_t i = 0; i < BATCH; ++i, ++seq) {
+                    const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
+                    const uint32_t sw = i < 2 ? sw0 : sw1, bw = i < 2 ? bw0 : bw1;
+                    const uint32_t s2 = scale_pair((uint16_t)((i & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
+                    const uint32_t b2 = scale_pair((uint16_t)((i & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
+                    if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
+                    uint8_t* dst = stage_a(s, mat) + r * 128;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        if (j >= words) break;
+                        const uint4 v = cur[i * PER + (j >> 2)];
+                        const uint32_t wd = (j & 3u) == 0 ? v.x : (j & 3u) == 1 ? v.y : (j & 3u) == 2 ? v.z : v.w;
+                        const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
+                        *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(wd, s2, b2);
+                    }
+                    fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&S.full_a[s]);
+                }
             }
             if (!ok) break;
-            if (epi) {
+            {
+                if (PHASE == 2) {
+                    S.out_row[td] = dest;
+                    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight dequantise / epilogue warps
+                }
                 if (!mbar_wait(&S.acc_full, item & 1u)) { fail(); break; }
                 tc_fence_after();
                 const uint32_t lane_row = 32 * q + lane;
                 const uint32_t taddr = tmem + ((32 * q) << 16);
                 const uint32_t out_row = I.row0 + lane_row;
-                for (uint32_t col0 = 0; col0 < I.n; col0 += 32) {
+                for (uint32_t col0 = col_half * (TC_TILE_N / 2); col0 < min(I.n, (col_half + 1) * (TC_TILE_N / 2)); col0 += 32) {
                     float v[32];
                     tmem_ld32(taddr + col0, v);
                     if (PHASE == 1) {
@@ -382,12 +411,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i) {
                             if (col0 + i >= I.n) break;
-                            const mfb_pair pr = P.sorted[I.pair_start + col0 + i];
-                            P.partial[((size_t)pr.token * P.slots + pr.rank) * P.d + out_row] = v[i];
+                            P.partial[(size_t)S.out_row[col0 + i] * P.d + out_row] = v[i];
                         }
                     }
                 }
                 tc_fence_before();
+                if (PHASE == 2) asm volatile("bar.sync 1, 256;" ::: "memory");   // out_row may be overwritten for the next item
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&S.acc_empty);
             }
@@ -444,9 +473,17 @@ int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
     const cuuint64_t strides[1] = {inner * sizeof(__half)};
     const cuuint32_t box[2] = {TC_KC, TC_BOX_ROWS};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
-                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // the driver entry point is looked up at run time: the library must load on machines without a GPU driver
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    MFB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &found));
+    MFB_REQUIRE(sym != nullptr && found == cudaDriverEntryPointSuccess, MFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+    const CUresult r = reinterpret_cast<encode_fn>(sym)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
+                                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
         return MFB_ERR_CUDA;

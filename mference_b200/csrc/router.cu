@@ -39,19 +39,60 @@ router_logits_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint
 #pragma unroll
         for (int j = 0; j < TE; ++j) acc[i][j] = 0.0f;
 
+    // 16-byte loads of eight consecutive k when rows are 16-bit and aligned; element by element otherwise
+    const bool vec = x_dtype != MFB_DT_F32 && (ldx & 7u) == 0 && (d & 7u) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0;
     for (uint32_t k0 = 0; k0 < d; k0 += RT_KC) {
         __syncthreads();
-        for (uint32_t i = tid; i < TM * RT_KC; i += RT_WARPS * 32) {
-            const uint32_t r = i / RT_KC, k = i % RT_KC;
-            float v = 0.0f;
-            if (t0 + r < n_tokens && k0 + k < d) v = load_act(x, (size_t)(t0 + r) * ldx + k0 + k, x_dtype);
-            xs[r][(k & 31) * 8 + (k >> 5)] = v;
-        }
-        for (uint32_t i = tid; i < BE * RT_KC; i += RT_WARPS * 32) {
-            const uint32_t r = i / RT_KC, k = i % RT_KC;
-            uint16_t v = 0;
-            if (e0 + r < num_experts && k0 + k < d) v = __bfloat16_as_ushort(w[(size_t)(e0 + r) * d + k0 + k]);
-            ws[r][(k & 31) * 8 + (k >> 5)] = v;
+        if (vec) {
+            // A thread takes columns c*8 .. c*8+7 of all eight 32-column blocks of one row: eight 16-byte loads form
+            // an 8 x 8 block whose transpose is, per column, the eight values one lane slot holds - contiguous in
+            // the lane-major tile, so they leave as whole 16-byte stores.
+            for (uint32_t i = tid; i < (TM + BE) * 4; i += RT_WARPS * 32) {
+                const bool is_x = i < TM * 4;
+                const uint32_t r = (is_x ? i : i - TM * 4) >> 2, c = i & 3u;
+                const bool live = is_x ? (t0 + r < n_tokens) : (e0 + r < num_experts);
+                const uint16_t* src = is_x ? reinterpret_cast<const uint16_t*>(x) + (size_t)(t0 + r) * ldx
+                                           : reinterpret_cast<const uint16_t*>(w) + (size_t)(e0 + r) * d;
+                uint32_t blk[8][4];
+#pragma unroll
+                for (int jb = 0; jb < 8; ++jb) {
+                    const uint32_t k = k0 + jb * 32 + c * 8;
+                    uint4 q = make_uint4(0, 0, 0, 0);
+                    if (live && k < d) q = *reinterpret_cast<const uint4*>(src + k);
+                    blk[jb][0] = q.x; blk[jb][1] = q.y; blk[jb][2] = q.z; blk[jb][3] = q.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {   // column c*8 + j = lane slot, values of the eight blocks in k order
+                    uint16_t h[8];
+#pragma unroll
+                    for (int jb = 0; jb < 8; ++jb)
+                        h[jb] = (uint16_t)((j & 1) ? (blk[jb][j >> 1] >> 16) : (blk[jb][j >> 1] & 0xFFFFu));
+                    const uint32_t slot = (c * 8 + j) * 8;
+                    if (is_x) {
+                        *reinterpret_cast<float4*>(&xs[r][slot]) = make_float4(widen16(h[0], x_dtype), widen16(h[1], x_dtype),
+                                                                                widen16(h[2], x_dtype), widen16(h[3], x_dtype));
+                        *reinterpret_cast<float4*>(&xs[r][slot + 4]) = make_float4(widen16(h[4], x_dtype), widen16(h[5], x_dtype),
+                                                                                    widen16(h[6], x_dtype), widen16(h[7], x_dtype));
+                    } else {
+                        *reinterpret_cast<uint4*>(&ws[r][slot]) = make_uint4(h[0] | ((uint32_t)h[1] << 16), h[2] | ((uint32_t)h[3] << 16),
+                                                                             h[4] | ((uint32_t)h[5] << 16), h[6] | ((uint32_t)h[7] << 16));
+                    }
+                }
+            }
+        } else {
+            for (uint32_t i = tid; i < TM * RT_KC; i += RT_WARPS * 32) {
+                const uint32_t r = i / RT_KC, k = i % RT_KC;
+                float v = 0.0f;
+                if (t0 + r < n_tokens && k0 + k < d) v = load_act(x, (size_t)(t0 + r) * ldx + k0 + k, x_dtype);
+                xs[r][(k & 31) * 8 + (k >> 5)] = v;
+            }
+            for (uint32_t i = tid; i < BE * RT_KC; i += RT_WARPS * 32) {
+                const uint32_t r = i / RT_KC, k = i % RT_KC;
+                uint16_t v = 0;
+                if (e0 + r < num_experts && k0 + k < d) v = __bfloat16_as_ushort(w[(size_t)(e0 + r) * d + k0 + k]);
+                ws[r][(k & 31) * 8 + (k >> 5)] = v;
+            }
         }
         __syncthreads();
         float xv[TM][8];
@@ -206,8 +247,8 @@ cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uin
         dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 7) / 8);
         router_logits_kernel<8, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
     } else {
-        dim3 grid((num_experts + RT_WARPS * 4 - 1) / (RT_WARPS * 4), (n_tokens + 7) / 8);
-        router_logits_kernel<8, 4><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+        dim3 grid((num_experts + RT_WARPS * 4 - 1) / (RT_WARPS * 4), (n_tokens + 15) / 16);
+        router_logits_kernel<16, 4><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
     }
     count_launches(1);
     return cudaGetLastError();

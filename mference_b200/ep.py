@@ -1,0 +1,145 @@
+"""Expert parallelism over 2, 4 or 8 GPUs of one box: one process per GPU, ``torch.distributed`` (NCCL) for the two
+all-to-all exchanges of a layer, the library's kernels for everything else.
+
+Experts are block-sharded - rank g owns experts [g*E/G, (g+1)*E/G) and only their slice of the pool - tokens stay
+data-parallel, the router weights and the shared expert are replicated.  Per layer:
+
+    norm + router (local) -> plan send order (by destination rank) -> pack rows -> all-to-all (counts, expert ids, rows)
+    -> grouped expert FFN on the received rows (sorted by expert; tensor-core path for 4-bit shapes)
+    -> all-to-all of the fp32 result rows back -> weighted rank-ordered reduce + shared expert + residual (one kernel)
+
+The result is bit-identical to the single-GPU prefill layer: the same per-row arithmetic, the same summation order.
+The reference (single device) has no counterpart; what is preserved is the order of prefill_moe_reduce_token_major
+(Sources/Mference/Metal/Prefill/prefill.metal:631-652).
+
+The exchange logic (`exchange_plan`, `ExpertParallelLayer.forward`) only needs an object with the five compute
+methods of `DeviceOps`; the product always uses `DeviceOps` (CUDA, fails loudly without the library).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+
+
+def exchange_plan(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    """recv_counts[g] = number of pairs rank g sends to this rank (an all-to-all of one int32 per peer)."""
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    return recv_counts
+
+
+def exchange_rows(rows: torch.Tensor, send_counts: List[int], recv_counts: List[int], group=None) -> torch.Tensor:
+    """All-to-all-v of rows: send_counts[g] consecutive rows go to rank g; returns the rows received, by source rank."""
+    out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+    return out
+
+
+class DeviceOps:
+    """The compute steps of an expert-parallel layer on the GPU, through the C ABI."""
+
+    def __init__(self, d, f, num_experts, top_k, world, max_tokens, max_recv_rows, *, bits=4, shared_bits=4, x_dtype=L.DT_BF16,
+                 tensor_core=True, **kw):
+        from .moe import MoE
+        self.lib = L.load()
+        self.d, self.f, self.E, self.K, self.world, self.x_dtype = d, f, num_experts, top_k, world, x_dtype
+        self.local_E = num_experts // world
+        # home side: norm + router over all experts; expert side: the local experts with one "rank slot" per received row
+        self.home = MoE(d, f, num_experts, top_k, bits=bits, shared_bits=shared_bits, x_dtype=x_dtype, max_tokens=max_tokens, **kw)
+        self.expert = MoE(d, f, self.local_E, 1, bits=bits, shared_bits=0, x_dtype=x_dtype, max_tokens=max_recv_rows,
+                          tensor_core_prefill=tensor_core, **kw)
+        self.shared = MoE(d, f, 1, 1, bits=shared_bits or bits, shared_bits=0, x_dtype=x_dtype, max_tokens=max_tokens,
+                          tensor_core_prefill=tensor_core and (shared_bits or bits) == 4, **kw)
+        self.tdt = torch.bfloat16 if x_dtype == L.DT_BF16 else torch.float16
+
+    @staticmethod
+    def _s():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def route(self, weights, h):
+        """RMSNorm + router top-k of the local rows: (xn, idx int32 [T,K], w fp16 [T,K])."""
+        T = h.shape[0]
+        xn = torch.empty_like(h)
+        idx = torch.empty((T, self.K), dtype=torch.int32, device=h.device)
+        w = torch.empty((T, self.K), dtype=torch.float16, device=h.device)
+        self.home.encode_rmsnorm(h, xn, weights.norm_w)
+        self.home.encode_router(xn, weights, idx, w)
+        return xn, idx, w
+
+    def plan(self, idx):
+        T, K = idx.shape
+        n = T * K
+        perm = torch.empty(n, dtype=torch.int32, device=idx.device)
+        inv = torch.empty(n, dtype=torch.int32, device=idx.device)
+        counts = torch.empty(self.world, dtype=torch.int32, device=idx.device)
+        local_expert = torch.empty(n, dtype=torch.int32, device=idx.device)
+        L.check(self.lib.mfb_ep_plan(self._s(), idx.data_ptr(), T, K, self.E, self.world, perm.data_ptr(), inv.data_ptr(),
+                                     counts.data_ptr(), local_expert.data_ptr()))
+        return perm, inv, counts, local_expert
+
+    def pack(self, xn, perm):
+        n = perm.numel()
+        rows = torch.empty((n, self.d), dtype=xn.dtype, device=xn.device)
+        L.check(self.lib.mfb_ep_pack(self._s(), xn.data_ptr(), xn.stride(0), self.d, perm.data_ptr(), n, self.K, rows.data_ptr()))
+        return rows
+
+    def expert_ffn(self, local_weights, rows, local_expert):
+        """fp32 [R, d] down-projection rows of the received rows through this rank's experts."""
+        R = rows.shape[0]
+        out = torch.empty((R, self.d), dtype=torch.float32, device=rows.device)
+        if R == 0:
+            return out
+        idx = local_expert.view(R, 1)
+        ones = torch.ones((R, 1), dtype=torch.float16, device=rows.device)
+        sp, _, _, groups, n_groups = self.expert.encode_group(idx, ones)
+        self.expert.encode_prefill_grouped(local_weights, rows, sp, groups, n_groups, out)
+        return out
+
+    def shared_ffn(self, shared_weights, xn):
+        T = xn.shape[0]
+        out = torch.empty((T, self.d), dtype=torch.float32, device=xn.device)
+        idx = torch.zeros((T, 1), dtype=torch.int32, device=xn.device)
+        ones = torch.ones((T, 1), dtype=torch.float16, device=xn.device)
+        sp, _, _, groups, n_groups = self.shared.encode_group(idx, ones)
+        self.shared.encode_prefill_grouped(shared_weights, xn, sp, groups, n_groups, out)
+        return out
+
+    def combine(self, recv, inv, w, shared_partial, residual, y):
+        T = w.shape[0]
+        L.check(self.lib.mfb_ep_combine(self._s(), recv.data_ptr(), inv.data_ptr(), w.data_ptr(),
+                                        None if shared_partial is None else shared_partial.data_ptr(),
+                                        None if residual is None else residual.data_ptr(), y.data_ptr(), T, self.K, self.d,
+                                        self.x_dtype))
+
+
+class ExpertParallelLayer:
+    """One MoE layer over `world` ranks.  `weights`: the replicated part (router, norm, shared expert); `local_weights`:
+    this rank's slice of the pool as a layer with E/world experts; `shared_weights`: the shared expert as a one-expert
+    layer (or None)."""
+
+    def __init__(self, ops, world: int, group=None):
+        self.ops, self.world, self.group = ops, world, group
+        self.last_send_counts: List[int] = []
+        self.last_recv_counts: List[int] = []
+
+    def forward(self, weights, local_weights, shared_weights, h_in, h_out):
+        ops = self.ops
+        xn, idx, w = ops.route(weights, h_in)
+        perm, inv, counts, local_expert = ops.plan(idx)
+        recv_counts_t = exchange_plan(counts, self.group)
+        send_counts = counts.cpu().tolist()          # the one host synchronisation of a layer: split sizes for NCCL
+        recv_counts = recv_counts_t.cpu().tolist()
+        self.last_send_counts, self.last_recv_counts = send_counts, recv_counts
+        rows = ops.pack(xn, perm)
+        got_rows = exchange_rows(rows, send_counts, recv_counts, self.group)
+        got_expert = exchange_rows(local_expert, send_counts, recv_counts, self.group)
+        partial = ops.expert_ffn(local_weights, got_rows, got_expert)
+        back = exchange_rows(partial, recv_counts, send_counts, self.group)     # reversed split sizes
+        shared_partial = ops.shared_ffn(shared_weights, xn) if shared_weights is not None else None
+        ops.combine(back, inv, w, shared_partial, h_in, h_out)
+        return h_out
