@@ -406,6 +406,101 @@ def run_prefill(args):
     }))
 
 
+def run_ep(args):
+    """The prefill layer of configs[2] with the experts block-sharded over the ranks: tokens split evenly (strong
+    scaling: the total stays --tokens), one all-to-all each way per layer."""
+    import copy
+    import torch
+    import torch.distributed as dist
+    from mference_b200 import _lib as L
+    from mference_b200.ep import DeviceOps, ExpertParallelLayer
+    from mference_b200.moe import synth_layer, synth_normal
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local)) if world > 1 else \
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    lib = L.load()
+    T = args.tokens // world
+    full = synth_layer(ROOT_SEED, 0, D, F, E)
+    full.logit_bias = torch.from_numpy(zipf_logit_bias(E)).cuda()
+    local_E = E // world
+    mine = copy.copy(full)
+    mine.pool = full.pool[rank * local_E * full.slot_stride:(rank + 1) * local_E * full.slot_stride]
+    shared = copy.copy(full)
+    shared.pool, shared.slot_stride, shared.routed_off = full.shared_blob, full.shared_blob.numel(), full.shared_off
+    shared.shared_blob = None
+    # a skewed router can send every pair of every rank to one rank: size the receive side for that
+    ops = DeviceOps(D, F, E, K, world, max_tokens=T, max_recv_rows=args.tokens * K)
+    layer = ExpertParallelLayer(ops, world)
+    xs = [synth_normal(ROOT_SEED + rank, f"x.ep.{i}", T * D, dtype=L.DT_BF16).view(T, D) for i in range(N_INPUTS)]
+    y = torch.empty_like(xs[0])
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        layer.forward(full, mine, shared, xs[i % N_INPUTS], y)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = lib.mfb_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        layer.forward(full, mine, shared, xs[i % N_INPUTS], y)
+    e1.record()
+    barrier()
+    launches = lib.mfb_launch_count() - launches0
+    ms_dev = e0.elapsed_time(e1)
+    # end to end with host rows
+    host_in = [t.cpu().pin_memory() for t in xs]
+    host_out = torch.empty_like(host_in[0]).pin_memory()
+    dev_in = torch.empty_like(xs[0])
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        dev_in.copy_(host_in[i % N_INPUTS], non_blocking=True)
+        layer.forward(full, mine, shared, dev_in, y)
+        host_out.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([ms_dev, e0.elapsed_time(e1), float(sum(layer.last_recv_counts))], dtype=torch.float64, device="cuda")
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    recv = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
+    dist.all_gather(recv, t[2:3].clone())
+    if rank == 0:
+        ms = float(tmax[0]) / args.steps
+        total_tokens = T * world
+        flops = 2 * 3 * D * F * (total_tokens * K + total_tokens) + 2 * total_tokens * D * E
+        _, tf_peak, peak_kind = measured_peaks()
+        achieved = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "moe_prefill_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+            "config": {"workload": f"configs[2] sharded: prefill gather-QMM, {total_tokens} tokens over {world} rank(s), experts "
+                                   f"block-sharded ({local_E} per rank), NCCL all-to-all dispatch and combine",
+                       "tokens_per_rank": T, "pairs_received_per_rank": [int(r.item()) for r in recv],
+                       "parallelism": f"ep{world}", "l2": f"{N_INPUTS} input sets cycled"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak * world, "unit": "TFLOP/s",
+                         "frac": achieved / (tf_peak * world), "peak_kind": peak_kind, "traffic": None,
+                         "kernel": "whole layer incl. the two exchanges"},
+            "cpu_baseline": None,
+            "e2e": {"value": total_tokens / (float(tmax[1]) / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * D * 2 * world, "d2h_bytes_per_step": T * D * 2 * world},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -416,8 +511,9 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers only for profiling a small case")
     ap.add_argument("--launch", default="fused", choices=["fused", "layers"],
                     help="layers: per-layer, per-phase launches of the same kernels (for profiling one phase alone)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: configs[1] (the headline); prefill: configs[2], 4096 tokens through one layer's gather-QMM")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep"],
+                    help="decode: configs[1] (the headline); prefill: configs[2], 4096 tokens through one layer's gather-QMM; "
+                         "ep: the same prefill layer with experts sharded over --gpus ranks (NCCL all-to-all)")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill token rows")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
@@ -428,6 +524,8 @@ def main():
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "ep":
+        run_ep(args)
     else:
         run_ours(args)
 

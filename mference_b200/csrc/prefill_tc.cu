@@ -33,11 +33,13 @@ namespace {
 constexpr uint32_t TC_M = 128;          // weight rows per tile
 constexpr uint32_t TC_KC = 64;          // k elements per chunk = one 128-byte swizzle row of fp16
 constexpr uint32_t TC_BOX_ROWS = 64;    // token rows per TMA box
-constexpr uint32_t TC_DQ_WARPS = 8;
-constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS) * 32;
+constexpr uint32_t TC_DQ_WARPS = 8, TC_EPI_WARPS = 4;
+constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS + TC_EPI_WARPS) * 32;
 constexpr uint32_t TC_A_BYTES = TC_M * 128;            // one matrix tile of one chunk
-constexpr uint32_t TC_B_BYTES = TC_TILE_N * 128;       // one activation tile of one chunk
-constexpr uint32_t TC_TMEM_COLS = 512;
+constexpr uint32_t TC_TMEM_COLS = 512;                 // two accumulator buffers of 256 columns
+constexpr uint32_t TC_STAGES = 4;
+// token rows per MMA tile: phase 1 keeps gate and up of a tile in one 256-column buffer, phase 2 has one matrix
+__host__ __device__ constexpr uint32_t tc_tile_n(int phase) { return phase == 1 ? TC_TILE_N / 2 : TC_TILE_N; }
 constexpr long long TC_WAIT_CYCLES = 400000000ll;      // ~0.2 s
 
 struct TcParams {
@@ -51,7 +53,8 @@ struct TcParams {
     const mfb_pair* sorted;
     const mfb_group* groups;
     const uint32_t* n_groups;
-    const uint32_t* tile_prefix;   // [n_groups + 1] exclusive prefix of ceil(pair_count / TC_TILE_N)
+    const uint32_t* tile_prefix1;  // [n_groups + 1] exclusive prefix of ceil(pair_count / 128): token tiles of phase 1
+    const uint32_t* tile_prefix2;  // the same for the 256-row token tiles of phase 2
     __half* acts16;                // [rows, f] hidden activations in sorted-pair order (phase 1 out, phase 2 in)
     float* partial;                // [token * slots + rank, d]
     uint32_t slots;
@@ -180,7 +183,7 @@ struct Item {
 
 // Work item `it` -> (group, token tile, weight-row tile); the same arithmetic in every role.
 __device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* tp_s, uint32_t n_groups, uint32_t it,
-                                            uint32_t n_row_tiles) {
+                                            uint32_t n_row_tiles, uint32_t tile_n) {
     Item I;
     const uint32_t tt = it / n_row_tiles;
     uint32_t lo = 0, hi = n_groups;
@@ -189,10 +192,10 @@ __device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* t
         if (tp_s[mid] <= tt) lo = mid; else hi = mid;
     }
     const mfb_group g = P.groups[lo];
-    const uint32_t n0 = (tt - tp_s[lo]) * TC_TILE_N;
+    const uint32_t n0 = (tt - tp_s[lo]) * tile_n;
     I.pair_start = g.pair_start + n0;
     I.count = g.pair_count;
-    I.n = min(TC_TILE_N, g.pair_count - n0);
+    I.n = min(tile_n, g.pair_count - n0);
     I.n_mma = max(16u, (I.n + 15u) & ~15u);
     I.row0 = (it % n_row_tiles) * TC_M;
     I.shared = g.expert >= P.num_experts;
@@ -210,7 +213,7 @@ __device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* t
 }
 
 struct TcShared {
-    uint64_t full_a[4], full_b[4], empty[4], acc_full, acc_empty;
+    uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base, abort;
     uint32_t tp[MFB_MAX_EXPERTS + 2];
     uint32_t out_row[TC_TILE_N];   // phase 2: token * slots + rank of the current item's token columns
@@ -219,8 +222,9 @@ struct TcShared {
 template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P, const __grid_constant__ CUtensorMap map_b) {
     constexpr uint32_t NMAT = PHASE == 1 ? 2 : 1;
-    constexpr uint32_t STAGE_BYTES = NMAT * TC_A_BYTES + TC_B_BYTES;
-    constexpr uint32_t STAGES = PHASE == 1 ? 3 : 4;
+    constexpr uint32_t TILE_N = tc_tile_n(PHASE);
+    constexpr uint32_t STAGE_BYTES = NMAT * TC_A_BYTES + TILE_N * 128;   // 48 KB in both phases
+    constexpr uint32_t STAGES = TC_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcShared S;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -228,11 +232,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
     const uint32_t K = PHASE == 1 ? P.d : P.f, rows = PHASE == 1 ? P.f : P.d;
     const uint32_t n_chunks = K / TC_KC, n_row_tiles = rows / TC_M;
     const uint32_t n_groups = *P.n_groups;
-    for (uint32_t i = threadIdx.x; i <= n_groups; i += blockDim.x) S.tp[i] = P.tile_prefix[i];
+    for (uint32_t i = threadIdx.x; i <= n_groups; i += blockDim.x) S.tp[i] = (PHASE == 1 ? P.tile_prefix1 : P.tile_prefix2)[i];
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&S.full_a[s], TC_DQ_WARPS); mbar_init(&S.full_b[s], 1); mbar_init(&S.empty[s], 1); }
-        mbar_init(&S.acc_full, 1);
-        mbar_init(&S.acc_empty, TC_DQ_WARPS);
+        for (uint32_t b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], TC_EPI_WARPS); }
         S.abort = 0;
         fence_barrier_init();
     }
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         // ---------------------------------------------------------------- activation tiles by TMA
         uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
             const uint32_t copies = (I.n_mma + TC_BOX_ROWS - 1) / TC_BOX_ROWS;
             for (uint32_t c = 0; c < n_chunks; ++c, ++seq) {
@@ -270,9 +273,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         // ---------------------------------------------------------------- MMA issue
         uint32_t seq = 0, item = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
-            if (!mbar_wait(&S.acc_empty, (item & 1u) ^ 1u)) { fail(); break; }
+            const uint32_t buf = item & 1u, use = (item >> 1) & 1u;   // accumulator buffer and how often it has been used
+            if (!mbar_wait(&S.acc_empty[buf], use ^ 1u)) { fail(); break; }
             tc_fence_after();
             const uint32_t idesc = instr_desc(I.n_mma);
             bool ok = true;
@@ -287,49 +291,31 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                         const uint64_t a_desc = smem_desc(stage_a(s, m));
 #pragma unroll
                         for (uint32_t kk = 0; kk < TC_KC / 16; ++kk)   // 16 k per MMA = 32 bytes along the swizzled row
-                            umma_f16(tmem + m * TC_TILE_N, a_desc + kk * 2, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
+                            umma_f16(tmem + buf * 256 + m * TILE_N, a_desc + kk * 2, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
                     }
                     umma_commit(&S.empty[s]);   // frees the stage once these MMAs have read it
                 }
                 __syncwarp();
             }
             if (!ok) break;
-            if (lane == 0) umma_commit(&S.acc_full);
+            if (lane == 0) umma_commit(&S.acc_full[buf]);
             __syncwarp();
             ++item;
         }
-    } else {
-        // ---------------------------------------------------------------- dequantise, then (warps 2-5) epilogue
+    } else if (warp < 2 + TC_DQ_WARPS) {
+        // ---------------------------------------------------------------- dequantise
         const uint32_t td = threadIdx.x - 64;                 // 0..255
         const uint32_t r = td & (TC_M - 1), part = td >> 7;   // phase 1: part = matrix; phase 2: part = half of the chunk
         const uint32_t words = PHASE == 1 ? 8 : 4, word0 = PHASE == 1 ? 0 : part * 4;
         const uint32_t mat = PHASE == 1 ? part : 0;
-        const uint32_t col_half = part;                       // epilogue: warps 2-5 take token columns [0, 128), warps 6-9 [128, 256)
-        const uint32_t q = warp & 3u;                         // TMEM lane quarter this warp may read
-        uint32_t seq = 0, item = 0;
+        uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles);
-            if (!I.ok) {
-                if (PHASE == 2) {   // a non-resident expert contributes nothing: clear its partial rows
-                    const uint32_t dcol = I.row0 + 32 * ((warp - 2) & 3u) + lane;
-                    for (uint32_t n = col_half; n < I.n; n += 2) {
-                        const mfb_pair pr = P.sorted[I.pair_start + n];
-                        P.partial[((size_t)pr.token * P.slots + pr.rank) * P.d + dcol] = 0.0f;
-                    }
-                }
-                continue;
-            }
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            if (!I.ok) continue;
             const uint32_t w_off = PHASE == 1 ? (mat ? I.off.up_w : I.off.gate_w) : I.off.down_w;
             const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
             const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
             const size_t row = I.row0 + r;
-            // phase 2: where each token column of this item goes; fetched now, parked in shared memory before the
-            // epilogue (a dependent global load per column inside the epilogue would serialise it)
-            uint32_t dest = 0;
-            if (PHASE == 2 && td < I.n) {
-                const mfb_pair pr = P.sorted[I.pair_start + td];
-                dest = pr.token * P.slots + pr.rank;
-            }
             const uint4* wrow = reinterpret_cast<const uint4*>(I.blob + w_off + row * (K / 2)) + (word0 >> 2);
             const uint4* srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
             const uint4* brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
@@ -378,48 +364,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                 }
             }
             if (!ok) break;
-            {
-                if (PHASE == 2) {
-                    S.out_row[td] = dest;
-                    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight dequantise / epilogue warps
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (its own four warps: the
+        // accumulators are double-buffered, so item i is read out while item i + 1 is being multiplied)
+        const uint32_t te = threadIdx.x - (2 + TC_DQ_WARPS) * 32;   // 0..127
+        const uint32_t q = warp & 3u;                               // TMEM lane quarter this warp may read
+        uint32_t item = 0;
+        for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
+            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            const uint32_t out_row = I.row0 + 32 * q + lane;
+            if (PHASE == 2) {
+                // where each token column of this item goes: fetched once into shared memory (a dependent global
+                // load per column inside the loop below would serialise it)
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // the previous item's table is no longer read
+                for (uint32_t n = te; n < I.n; n += TC_EPI_WARPS * 32) {
+                    const mfb_pair pr = P.sorted[I.pair_start + n];
+                    S.out_row[n] = pr.token * P.slots + pr.rank;
                 }
-                if (!mbar_wait(&S.acc_full, item & 1u)) { fail(); break; }
-                tc_fence_after();
-                const uint32_t lane_row = 32 * q + lane;
-                const uint32_t taddr = tmem + ((32 * q) << 16);
-                const uint32_t out_row = I.row0 + lane_row;
-                for (uint32_t col0 = col_half * (TC_TILE_N / 2); col0 < min(I.n, (col_half + 1) * (TC_TILE_N / 2)); col0 += 32) {
-                    float v[32];
-                    tmem_ld32(taddr + col0, v);
-                    if (PHASE == 1) {
-                        float u[32];
-                        tmem_ld32(taddr + TC_TILE_N + col0, u);
-                        const uint32_t fpos = (out_row & ~7u) + tc_perm8(out_row & 7u);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (!I.ok) {
+                if (PHASE == 2)   // a non-resident expert contributes nothing: clear its partial rows
+                    for (uint32_t n = 0; n < I.n; ++n) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
+                continue;
+            }
+            const uint32_t buf = item & 1u, use = (item >> 1) & 1u;
+            if (!mbar_wait(&S.acc_full[buf], use)) { fail(); break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((32 * q) << 16) + buf * 256;
+            for (uint32_t col0 = 0; col0 < I.n; col0 += 32) {
+                float v[32];
+                tmem_ld32(taddr + col0, v);
+                if (PHASE == 1) {
+                    float u[32];
+                    tmem_ld32(taddr + TILE_N + col0, u);
+                    const uint32_t fpos = (out_row & ~7u) + tc_perm8(out_row & 7u);
 #pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i) {
-                            if (col0 + i >= I.n) break;
-                            float gate = v[i], up = u[i];
-                            if (!I.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
-                                gate = fminf(gate, P.limit);
-                                up = fminf(fmaxf(up, -P.limit), P.limit);
-                            }
-                            float a = hidden_act(gate, (int)P.activation) * up;
-                            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                            P.acts16[(size_t)(I.pair_start + col0 + i) * P.f + fpos] = __float2half_rn(a);
+                    for (uint32_t i = 0; i < 32; ++i) {
+                        if (col0 + i >= I.n) break;
+                        float gate = v[i], up = u[i];
+                        if (!I.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+                            gate = fminf(gate, P.limit);
+                            up = fminf(fmaxf(up, -P.limit), P.limit);
                         }
-                    } else {
+                        float a = hidden_act(gate, (int)P.activation) * up;
+                        a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                        P.acts16[(size_t)(I.pair_start + col0 + i) * P.f + fpos] = __float2half_rn(a);
+                    }
+                } else {
 #pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i) {
-                            if (col0 + i >= I.n) break;
-                            P.partial[(size_t)S.out_row[col0 + i] * P.d + out_row] = v[i];
-                        }
+                    for (uint32_t i = 0; i < 32; ++i) {
+                        if (col0 + i >= I.n) break;
+                        P.partial[(size_t)S.out_row[col0 + i] * P.d + out_row] = v[i];
                     }
                 }
-                tc_fence_before();
-                if (PHASE == 2) asm volatile("bar.sync 1, 256;" ::: "memory");   // out_row may be overwritten for the next item
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&S.acc_empty);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
             ++item;
         }
     }
@@ -441,32 +444,39 @@ __global__ void tc_gather_kernel(const void* __restrict__ x, int x_dtype, uint32
     }
 }
 
-// tile_prefix[g] = number of TC_TILE_N-row token tiles in groups [0, g); one warp.
+// prefix1[g] / prefix2[g] = number of 128-row / 256-row token tiles in groups [0, g); one warp.
 __global__ void tc_tile_prefix_kernel(const mfb_group* __restrict__ groups, const uint32_t* __restrict__ n_groups,
-                                      uint32_t* __restrict__ tile_prefix) {
+                                      uint32_t* __restrict__ prefix1, uint32_t* __restrict__ prefix2) {
     const uint32_t ng = *n_groups, lane = threadIdx.x;
     const uint32_t per = (ng + 31) / 32, g0 = lane * per;
-    uint32_t local = 0;
+    const uint32_t t1 = tc_tile_n(1), t2 = tc_tile_n(2);
+    uint32_t l1 = 0, l2 = 0;
     for (uint32_t j = 0; j < per; ++j)
-        if (g0 + j < ng) local += (groups[g0 + j].pair_count + TC_TILE_N - 1) / TC_TILE_N;
-    uint32_t incl = local;
+        if (g0 + j < ng) { const uint32_t c = groups[g0 + j].pair_count; l1 += (c + t1 - 1) / t1; l2 += (c + t2 - 1) / t2; }
+    uint32_t i1 = l1, i2 = l2;
     for (uint32_t off = 1; off < 32; off <<= 1) {
-        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off);
-        if (lane >= off) incl += n;
+        const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, i1, off), b = __shfl_up_sync(0xFFFFFFFFu, i2, off);
+        if (lane >= off) { i1 += a; i2 += b; }
     }
-    uint32_t run = incl - local;
+    uint32_t r1 = i1 - l1, r2 = i2 - l2;
     for (uint32_t j = 0; j < per; ++j)
-        if (g0 + j < ng) { tile_prefix[g0 + j] = run; run += (groups[g0 + j].pair_count + TC_TILE_N - 1) / TC_TILE_N; }
-    if (lane == 31) tile_prefix[ng] = incl;
+        if (g0 + j < ng) {
+            const uint32_t c = groups[g0 + j].pair_count;
+            prefix1[g0 + j] = r1; prefix2[g0 + j] = r2;
+            r1 += (c + t1 - 1) / t1; r2 += (c + t2 - 1) / t2;
+        }
+    if (lane == 31) { prefix1[ng] = i1; prefix2[ng] = i2; }
 }
 
 struct TcState {
     CUtensorMap map_x, map_h;
     uint64_t rows_cap = 0;
+    uint32_t* prefix = nullptr;   // device: two arrays of MFB_MAX_EXPERTS + 2 token-tile prefixes
     bool ready = false;
 };
 
-constexpr size_t TC_SMEM_BYTES = 3 * (2 * TC_A_BYTES + TC_B_BYTES) + 1024;   // = 4 * (TC_A_BYTES + TC_B_BYTES) + 1024
+constexpr size_t TC_SMEM_BYTES = TC_STAGES * (2 * TC_A_BYTES + tc_tile_n(1) * 128) + 1024;   // the same in phase 2
+static_assert(2 * TC_A_BYTES + tc_tile_n(1) * 128 == TC_A_BYTES + tc_tile_n(2) * 128, "both phases use 48 KB stages");
 
 int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
     const cuuint64_t dims[2] = {inner, rows};
@@ -499,6 +509,7 @@ bool tc_supported(const mfb_moe_config& c) {
 }
 
 void tc_release(mfb_moe* m) {
+    if (m->tma) cudaFree(static_cast<TcState*>(m->tma)->prefix);
     delete static_cast<TcState*>(m->tma);
     m->tma = nullptr;
 }
@@ -520,6 +531,7 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
         if (rc) return rc;
         rc = make_map(&st->map_h, a.acts16, c.f, st->rows_cap);
         if (rc) return rc;
+        MFB_CUDA(cudaMalloc(&st->prefix, 2 * (MFB_MAX_EXPERTS + 2) * sizeof(uint32_t)));
         MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
         MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
         st->ready = true;
@@ -531,13 +543,15 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     P.routed_off = w->routed_off; P.shared_off = w->shared_off;
     P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.bits = c.bits; P.shared_bits = c.shared_bits;
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
-    P.sorted = sorted; P.groups = groups; P.n_groups = n_groups; P.tile_prefix = a.tile_prefix;
+    P.sorted = sorted; P.groups = groups; P.n_groups = n_groups;
+    P.tile_prefix1 = st->prefix; P.tile_prefix2 = st->prefix + MFB_MAX_EXPERTS + 2;
     P.acts16 = a.acts16; P.partial = partial; P.slots = slots; P.status = a.status;
 
-    tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, a.tile_prefix);
+    tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, st->prefix, st->prefix + MFB_MAX_EXPERTS + 2);
     tc_gather_kernel<<<n_rows, 256, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, a.xs16);
-    const uint32_t token_tiles = (n_rows + TC_TILE_N - 1) / TC_TILE_N + max_groups;   // upper bound
-    const uint32_t items1 = token_tiles * (c.f / TC_M), items2 = token_tiles * (c.d / TC_M);
+    // upper bounds of the work items (the kernels read the exact counts from the prefix arrays)
+    const uint32_t items1 = ((n_rows + tc_tile_n(1) - 1) / tc_tile_n(1) + max_groups) * (c.f / TC_M);
+    const uint32_t items2 = ((n_rows + tc_tile_n(2) - 1) / tc_tile_n(2) + max_groups) * (c.d / TC_M);
     const uint32_t grid1 = items1 < (uint32_t)m->sm_count ? items1 : (uint32_t)m->sm_count;
     const uint32_t grid2 = items2 < (uint32_t)m->sm_count ? items2 : (uint32_t)m->sm_count;
     tc_ffn_kernel<1><<<grid1, TC_THREADS, TC_SMEM_BYTES, s>>>(P, st->map_x);

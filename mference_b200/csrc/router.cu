@@ -128,6 +128,90 @@ router_logits_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint
         }
 }
 
+// Large batches (prefill): block tile 32 token rows x 16 experts, eight warps as 4 x 2, each warp 8 x 8 dot products
+// held as 64 accumulators per lane.  The staged tiles keep the natural k order (fp32 activations, raw bf16 gate
+// rows): lane l reads element s*32 + l of a row at sub-step s - exactly its k subset - so no transposition is needed
+// and every shared-memory read is conflict-free.  Summation order per dot product is the same as above: lane l adds
+// k = l, l+32, ... ascending with fma, then the xor butterfly, the bias last.
+constexpr int RL_TM = 32, RL_TE = 16;
+
+__global__ void __launch_bounds__(256, 2)
+router_logits_tile_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
+                          const __nv_bfloat16* __restrict__ w, uint32_t num_experts, uint32_t d,
+                          const float* __restrict__ logit_bias, float* __restrict__ logits) {
+    __shared__ __align__(16) float xs[RL_TM][RT_KC];
+    __shared__ __align__(16) uint16_t ws[RL_TE][RT_KC];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t t0 = blockIdx.y * RL_TM, e0 = blockIdx.x * RL_TE;
+    const uint32_t wt = (warp & 3u) * 8, we = (warp >> 2) * 8;   // this warp's rows of the two tiles
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    const bool vec = x_dtype != MFB_DT_F32 && (ldx & 7u) == 0 && (d & 7u) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0;
+    for (uint32_t k0 = 0; k0 < d; k0 += RT_KC) {
+        __syncthreads();
+        if (vec) {
+            for (uint32_t i = tid; i < RL_TM * (RT_KC / 8); i += 256) {
+                const uint32_t r = i / (RT_KC / 8), k = (i % (RT_KC / 8)) * 8;
+                uint4 q = make_uint4(0, 0, 0, 0);
+                if (t0 + r < n_tokens && k0 + k < d)
+                    q = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)(t0 + r) * ldx + k0 + k);
+                const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    f[j] = widen16((uint16_t)((j & 1) ? (u[j >> 1] >> 16) : (u[j >> 1] & 0xFFFFu)), x_dtype);
+                *reinterpret_cast<float4*>(&xs[r][k]) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(&xs[r][k + 4]) = make_float4(f[4], f[5], f[6], f[7]);
+            }
+            for (uint32_t i = tid; i < RL_TE * (RT_KC / 8); i += 256) {
+                const uint32_t r = i / (RT_KC / 8), k = (i % (RT_KC / 8)) * 8;
+                uint4 q = make_uint4(0, 0, 0, 0);
+                if (e0 + r < num_experts && k0 + k < d)
+                    q = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(w) + (size_t)(e0 + r) * d + k0 + k);
+                *reinterpret_cast<uint4*>(&ws[r][k]) = q;
+            }
+        } else {
+            for (uint32_t i = tid; i < RL_TM * RT_KC; i += 256) {
+                const uint32_t r = i / RT_KC, k = i % RT_KC;
+                xs[r][k] = (t0 + r < n_tokens && k0 + k < d) ? load_act(x, (size_t)(t0 + r) * ldx + k0 + k, x_dtype) : 0.0f;
+            }
+            for (uint32_t i = tid; i < RL_TE * RT_KC; i += 256) {
+                const uint32_t r = i / RT_KC, k = i % RT_KC;
+                ws[r][k] = (e0 + r < num_experts && k0 + k < d) ? __bfloat16_as_ushort(w[(size_t)(e0 + r) * d + k0 + k]) : (uint16_t)0;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < RT_KC / 32; ++s) {   // ascending k for this lane: k0 + s*32 + lane
+            float xv[8], wv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[i] = xs[wt + i][s * 32 + lane];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wv[j] = __uint_as_float((uint32_t)ws[we + j][s * 32 + lane] << 16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(wv[j], xv[i], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float v = acc[i][j];
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            const uint32_t e = e0 + we + j, t = t0 + wt + i;
+            if (lane == ((i * 8 + j) & 31) && e < num_experts && t < n_tokens) {   // every lane holds the sum: spread the stores
+                if (logit_bias) v = v + logit_bias[e];
+                logits[(size_t)t * num_experts + e] = v;
+            }
+        }
+}
+
 __global__ void router_select_kernel(const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts,
                                      uint32_t top_k, int mode, const __nv_bfloat16* __restrict__ per_expert_scale,
                                      const float* __restrict__ correction_bias, float route_scale,
@@ -247,8 +331,8 @@ cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uin
         dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 7) / 8);
         router_logits_kernel<8, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
     } else {
-        dim3 grid((num_experts + RT_WARPS * 4 - 1) / (RT_WARPS * 4), (n_tokens + 15) / 16);
-        router_logits_kernel<16, 4><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+        dim3 grid((num_experts + RL_TE - 1) / RL_TE, (n_tokens + RL_TM - 1) / RL_TM);
+        router_logits_tile_kernel<<<grid, 256, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
     }
     count_launches(1);
     return cudaGetLastError();
