@@ -1134,7 +1134,9 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             const uint32_t begin = min(blockIdx.x * per, total);
             combine_slice(P, begin, min(begin + per, total), shared);
         }
-        if (!(alive = grid_barrier(M, S, epoch))) break;
+        // rows of independent layers need no barrier here: the buffers the next layer writes first are not read by
+        // this combine, and the partial rows are not written again before three more barriers
+        if (M.layer_stride == 0 && !(alive = grid_barrier(M, S, epoch))) break;
     }
     clock_pair(1);
 }

@@ -10,16 +10,18 @@
 // Shape of one MMA tile: M = 128 *weight rows*, N = up to 256 *token rows* of one expert, K in chunks of 64.  The
 // weights are the A operand: their row count is always a multiple of 128, while the ragged side (tokens of an
 // expert, from a handful to thousands) rides in N, which the hardware accepts in steps of 16.  Accumulators live in
-// TMEM: phase 1 keeps gate in columns [0, 256) and up in [256, 512) of the CTA's 512-column allocation.
+// TMEM: two buffers of 256 columns; phase 1 (N <= 128) keeps gate and up side by side in a buffer, phase 2 (N <= 256)
+// fills a buffer with its one matrix.
 //
-// Roles inside a CTA (320 threads), connected by mbarriers, every wait bounded:
-//   warp 0      TMA: the activation chunk [N x 64] fp16 of the current token rows (gathered once per call into
-//               expert-major order, so a group's rows are contiguous) lands in shared memory in the 128-byte swizzle
-//   warp 1      one elected thread issues tcgen05.mma (A and B from shared memory, D in TMEM) and tcgen05.commit
-//   warps 2-9   dequantise: packed 4-bit codes + fp16/bf16 scale and bias -> fp16 weights, written straight into the
-//               swizzled K-major layout the MMA reads; the packed bytes come from global memory one chunk ahead
-//   warps 2-5   also the epilogue: tcgen05.ld the accumulators (warp w reads TMEM lanes 32 (w % 4) ...), apply the
-//               activation (phase 1) and store fp16 hidden rows / fp32 partial rows (phase 2)
+// Roles inside a CTA (704 threads), connected by mbarriers, every wait bounded:
+//   warp 0       TMA: the activation chunk [N x 64] fp16 of the current token rows (gathered once per call into
+//                expert-major order, so a group's rows are contiguous) lands in shared memory in the 128-byte swizzle
+//   warp 1       one elected thread issues tcgen05.mma (A and B from shared memory, D in TMEM) and tcgen05.commit
+//   warps 2-17   dequantise: packed 4-bit codes + fp16/bf16 scale and bias -> fp16 weights, written straight into the
+//                swizzled K-major layout the MMA reads; the packed bytes come from global memory a batch ahead
+//   warps 18-21  epilogue: tcgen05.ld the accumulators (warp w reads TMEM lanes 32 (w % 4) ...), apply the activation
+//                (phase 1) and store fp16 hidden rows / fp32 partial rows (phase 2).  The accumulators are double-
+//                buffered (2 x 256 TMEM columns), so tile i is read out while tile i + 1 is being multiplied.
 // The K order inside each 8-element piece is the one the mask-unpack of a packed word yields (0 4 1 5 2 6 3 7);
 // the gather kernel and the phase-1 epilogue store activations in the same order, so nothing is shuffled.
 #include <cuda.h>
@@ -33,7 +35,7 @@ namespace {
 constexpr uint32_t TC_M = 128;          // weight rows per tile
 constexpr uint32_t TC_KC = 64;          // k elements per chunk = one 128-byte swizzle row of fp16
 constexpr uint32_t TC_BOX_ROWS = 64;    // token rows per TMA box
-constexpr uint32_t TC_DQ_WARPS = 8, TC_EPI_WARPS = 4;
+constexpr uint32_t TC_DQ_WARPS = 8, TC_EPI_WARPS = 4;   // eight dequantising warps measured faster than sixteen
 constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS + TC_EPI_WARPS) * 32;
 constexpr uint32_t TC_A_BYTES = TC_M * 128;            // one matrix tile of one chunk
 constexpr uint32_t TC_TMEM_COLS = 512;                 // two accumulator buffers of 256 columns
@@ -169,6 +171,30 @@ __device__ __forceinline__ uint4 dequant_word4(uint32_t w, uint32_t scale2, uint
     return o;
 }
 
+// Sixteen 2-bit codes of one packed word -> sixteen fp16 weights as eight half2 (two 16-byte pieces), element i paired
+// with element i + 8: stored order 0 8 1 9 ... 7 15.  (1024 + 4^k q) * 4^-k - 1024 * 4^-k = q exactly.
+__device__ __forceinline__ void dequant_word2(uint32_t w, uint32_t scale2, uint32_t bias2, uint4& lo, uint4& hi) {
+    constexpr uint32_t MAGIC = 0x64006400u;
+    constexpr uint32_t S1 = 0x34003400u, C1 = 0xDC00DC00u;   // 1/4, -256
+    constexpr uint32_t S2 = 0x2C002C00u, C2 = 0xD400D400u;   // 1/16, -64
+    constexpr uint32_t S3 = 0x24002400u, C3 = 0xCC00CC00u;   // 1/64, -16
+    constexpr uint32_t S4 = 0x1C001C00u, C4 = 0xC400C400u;   // 1/256, -4
+    const uint32_t b = w >> 10;
+    lo.x = h2_fma(h2_sub((w & 0x00030003u) | MAGIC, MAGIC), scale2, bias2);
+    lo.y = h2_fma(h2_fma((w & 0x000C000Cu) | MAGIC, S1, C1), scale2, bias2);
+    lo.z = h2_fma(h2_fma((w & 0x00300030u) | MAGIC, S2, C2), scale2, bias2);
+    lo.w = h2_fma(h2_fma((w & 0x00C000C0u) | MAGIC, S3, C3), scale2, bias2);
+    hi.x = h2_fma(h2_fma((w & 0x03000300u) | MAGIC, S4, C4), scale2, bias2);
+    hi.y = h2_fma(h2_sub((b & 0x00030003u) | MAGIC, MAGIC), scale2, bias2);
+    hi.z = h2_fma(h2_fma((b & 0x000C000Cu) | MAGIC, S1, C1), scale2, bias2);
+    hi.w = h2_fma(h2_fma((b & 0x00300030u) | MAGIC, S2, C2), scale2, bias2);
+}
+
+// Position of element e of a 16-element run in the stored order of its code width (4-bit: per 8 elements).
+__host__ __device__ inline uint32_t tc_perm(uint32_t e, uint32_t bits) {
+    return bits == 4 ? (e & 8u) | tc_perm8(e & 7u) : ((e & 7u) << 1) | (e >> 3);
+}
+
 __device__ __forceinline__ uint32_t scale_pair(uint16_t bits, uint32_t dtype) {
     __half h = dtype == MFB_DT_BF16 ? __float2half_rn(__uint_as_float((uint32_t)bits << 16)) : __ushort_as_half(bits);
     const uint32_t u = __half_as_ushort(h);
@@ -178,7 +204,7 @@ __device__ __forceinline__ uint32_t scale_pair(uint16_t bits, uint32_t dtype) {
 struct Item {
     const uint8_t* blob;
     mfb_expert_offsets off;
-    uint32_t pair_start, count, row0, n, n_mma, ok, shared;
+    uint32_t pair_start, count, row0, n, n_mma, ok, shared, bits;
 };
 
 // Work item `it` -> (group, token tile, weight-row tile); the same arithmetic in every role.
@@ -201,13 +227,13 @@ __device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* t
     I.shared = g.expert >= P.num_experts;
     I.ok = 1;
     if (I.shared) {
-        I.blob = P.shared_blob; I.off = P.shared_off; I.ok = P.shared_blob != nullptr;
+        I.blob = P.shared_blob; I.off = P.shared_off; I.ok = P.shared_blob != nullptr; I.bits = P.shared_bits;
     } else {
         int64_t slot = g.expert;
         if (P.slot_of) slot = P.slot_of[g.expert];
         I.ok = slot >= 0;
         I.blob = P.pool + (uint64_t)(slot < 0 ? 0 : slot) * P.slot_stride;
-        I.off = P.routed_off;
+        I.off = P.routed_off; I.bits = P.bits;
     }
     return I;
 }
@@ -304,10 +330,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         }
     } else if (warp < 2 + TC_DQ_WARPS) {
         // ---------------------------------------------------------------- dequantise
-        const uint32_t td = threadIdx.x - 64;                 // 0..255
-        const uint32_t r = td & (TC_M - 1), part = td >> 7;   // phase 1: part = matrix; phase 2: part = half of the chunk
-        const uint32_t words = PHASE == 1 ? 8 : 4, word0 = PHASE == 1 ? 0 : part * 4;
-        const uint32_t mat = PHASE == 1 ? part : 0;
+        // The dequantising threads share the NMAT * 128 row chunks of a stage: a thread owns WORDS consecutive 16-byte
+        // pieces of fp16 (= WORDS packed words at 4 bits, WORDS / 2 at 2 bits) of one row.
+        constexpr uint32_t WORDS = NMAT * 1024 / (TC_DQ_WARPS * 32), PARTS_PER_ROW = 8 / WORDS;
+        const uint32_t td = threadIdx.x - 64;
+        const uint32_t r = td & (TC_M - 1), part = td >> 7;
+        const uint32_t mat = part / PARTS_PER_ROW;              // 0 in phase 2
+        const uint32_t word0 = (part % PARTS_PER_ROW) * WORDS;
         uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
@@ -316,28 +345,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
             const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
             const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
             const size_t row = I.row0 + r;
-            const uint4* wrow = reinterpret_cast<const uint4*>(I.blob + w_off + row * (K / 2)) + (word0 >> 2);
+            const bool four = I.bits == 4;
+            const uint32_t wpc = four ? 8u : 4u;   // packed words per 64-element chunk of a row
+            const uint32_t* wrow = reinterpret_cast<const uint32_t*>(I.blob + w_off + row * (K * I.bits / 8)) + (four ? word0 : word0 / 2);
             const uint4* srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
             const uint4* brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
             // packed codes travel in batches of four chunks, one batch ahead of the one in use: a load has four
             // chunks of work to hide its latency behind
-            constexpr uint32_t BATCH = 4, PER = PHASE == 1 ? 2 : 1;   // uint4 per chunk for this thread
-            uint4 pre[BATCH * PER], cur[BATCH * PER];
+            constexpr uint32_t BATCH = 4;
+            uint32_t pre[BATCH][WORDS], cur[BATCH][WORDS];
+            auto load_n = [&](const uint32_t* src, uint32_t (&dst)[WORDS], uint32_t n) {   // n = 1, 2, 4 or 8 words
+                if (n >= 4) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(src);
+                    dst[0] = v.x; dst[1 % WORDS] = v.y; dst[2 % WORDS] = v.z; dst[3 % WORDS] = v.w;
+                    if (n == 8) {
+                        const uint4 u = *reinterpret_cast<const uint4*>(src + 4);
+                        dst[4 % WORDS] = u.x; dst[5 % WORDS] = u.y; dst[6 % WORDS] = u.z; dst[7 % WORDS] = u.w;
+                    }
+                } else if (n == 2) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(src);
+                    dst[0] = v.x; dst[1 % WORDS] = v.y;
+                } else {
+                    dst[0] = *src;
+                }
+            };
+            auto load_words = [&](uint32_t chunk, uint32_t (&dst)[WORDS]) { load_n(wrow + chunk * wpc, dst, four ? WORDS : WORDS / 2); };
 #pragma unroll
-            for (uint32_t i = 0; i < BATCH; ++i)
-#pragma unroll
-                for (uint32_t h = 0; h < PER; ++h) pre[i * PER + h] = wrow[i * 2 + h];
+            for (uint32_t i = 0; i < BATCH; ++i) load_words(i, pre[i]);
             uint4 sc8 = make_uint4(0, 0, 0, 0), bi8 = make_uint4(0, 0, 0, 0);
             bool ok = true;
             for (uint32_t cb = 0; cb < n_chunks && ok; cb += BATCH) {   // n_chunks is a multiple of 8
                 if ((cb & 7u) == 0) { sc8 = srow[cb >> 3]; bi8 = brow[cb >> 3]; }
 #pragma unroll
-                for (uint32_t i = 0; i < BATCH * PER; ++i) cur[i] = pre[i];
+                for (uint32_t i = 0; i < BATCH; ++i)
+#pragma unroll
+                    for (uint32_t j = 0; j < WORDS; ++j) cur[i][j] = pre[i][j];
                 if (cb + BATCH < n_chunks) {
 #pragma unroll
-                    for (uint32_t i = 0; i < BATCH; ++i)
-#pragma unroll
-                        for (uint32_t h = 0; h < PER; ++h) pre[i * PER + h] = wrow[(cb + BATCH + i) * 2 + h];
+                    for (uint32_t i = 0; i < BATCH; ++i) load_words(cb + BATCH + i, pre[i]);
                 }
                 // this batch's four scale / bias pairs sit in two words of the eight-group vectors
                 const uint32_t sw0 = (cb & 4u) ? sc8.z : sc8.x, sw1 = (cb & 4u) ? sc8.w : sc8.y;
@@ -350,13 +395,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     const uint32_t b2 = scale_pair((uint16_t)((i & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
                     if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
                     uint8_t* dst = stage_a(s, mat) + r * 128;
+                    if (four) {
 #pragma unroll
-                    for (uint32_t j = 0; j < 8; ++j) {
-                        if (j >= words) break;
-                        const uint4 v = cur[i * PER + (j >> 2)];
-                        const uint32_t wd = (j & 3u) == 0 ? v.x : (j & 3u) == 1 ? v.y : (j & 3u) == 2 ? v.z : v.w;
-                        const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
-                        *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(wd, s2, b2);
+                        for (uint32_t j = 0; j < WORDS; ++j) {
+                            const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
+                            *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(cur[i][j], s2, b2);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t j = 0; j < WORDS / 2; ++j) {
+                            uint4 lo, hi;
+                            dequant_word2(cur[i][j], s2, b2, lo, hi);
+                            const uint32_t piece = word0 + 2 * j;
+                            *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = lo;
+                            *reinterpret_cast<uint4*>(dst + (((piece + 1) ^ (r & 7u)) << 4)) = hi;
+                        }
                     }
                     fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
                     __syncwarp();
@@ -399,7 +452,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                 if (PHASE == 1) {
                     float u[32];
                     tmem_ld32(taddr + TILE_N + col0, u);
-                    const uint32_t fpos = (out_row & ~7u) + tc_perm8(out_row & 7u);
+                    const uint32_t fpos = (out_row & ~15u) + tc_perm(out_row & 15u, I.bits);
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
                         if (col0 + i >= I.n) break;
@@ -432,15 +485,43 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
 }
 
 // xs16[pos, :] = fp16(x[sorted[pos].token, :]) in the stored k order, for every sorted pair.
+// Rows from n_routed on belong to the shared expert's group and follow its code width.  A thread converts sixteen
+// consecutive elements: two 16-byte loads, the permutation in registers, two 16-byte stores.
 __global__ void tc_gather_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t d,
-                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, __half* __restrict__ xs16) {
+                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, uint32_t n_routed, uint32_t bits,
+                                 uint32_t shared_bits, __half* __restrict__ xs16) {
     const uint32_t pos = blockIdx.x;
     if (pos >= n_rows) return;
+    const uint32_t width = pos < n_routed ? bits : shared_bits;
     const size_t src = (size_t)sorted[pos].token * ldx;
-    for (uint32_t k = threadIdx.x; k < d; k += blockDim.x) {
-        float v = load_act(x, src + k, x_dtype);
-        v = fminf(fmaxf(v, -65504.0f), 65504.0f);
-        xs16[(size_t)pos * d + (k & ~7u) + tc_perm8(k & 7u)] = __float2half_rn(v);
+    const bool vec = x_dtype != MFB_DT_F32 && (ldx & 7u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    for (uint32_t k = threadIdx.x * 16; k < d; k += blockDim.x * 16) {
+        uint16_t in[16];
+        if (vec) {
+            const uint4 a = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + src + k);
+            const uint4 b = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + src + k + 8);
+            const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) in[j] = (uint16_t)((j & 1) ? (u[j >> 1] >> 16) : (u[j >> 1] & 0xFFFFu));
+        }
+        uint16_t out[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float v = vec ? widen16(in[j], x_dtype) : load_act(x, src + k + j, x_dtype);
+            v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+            const uint16_t h = __half_as_ushort(__float2half_rn(v));
+            // both permutations, selected by the row's width (register indices stay compile-time constants)
+            const int p4 = (j & 8) | (((j & 7) & 3) << 1) | ((j & 7) >> 2), p2 = ((j & 7) << 1) | (j >> 3);
+            if (width == 4) out[p4] = h; else out[p2] = h;
+        }
+        uint4 o0, o1;
+        o0.x = out[0] | ((uint32_t)out[1] << 16); o0.y = out[2] | ((uint32_t)out[3] << 16);
+        o0.z = out[4] | ((uint32_t)out[5] << 16); o0.w = out[6] | ((uint32_t)out[7] << 16);
+        o1.x = out[8] | ((uint32_t)out[9] << 16); o1.y = out[10] | ((uint32_t)out[11] << 16);
+        o1.z = out[12] | ((uint32_t)out[13] << 16); o1.w = out[14] | ((uint32_t)out[15] << 16);
+        uint4* dst = reinterpret_cast<uint4*>(xs16 + (size_t)pos * d + k);
+        dst[0] = o0;
+        dst[1] = o1;
     }
 }
 
@@ -504,8 +585,8 @@ int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
 }  // namespace
 
 bool tc_supported(const mfb_moe_config& c) {
-    // 4-bit codes; scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512
-    return c.bits == 4 && (c.shared_bits == 0 || c.shared_bits == 4) && c.d % 512 == 0 && c.f % 512 == 0;
+    // scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512
+    return c.d % 512 == 0 && c.f % 512 == 0;
 }
 
 void tc_release(mfb_moe* m) {
@@ -548,7 +629,8 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     P.acts16 = a.acts16; P.partial = partial; P.slots = slots; P.status = a.status;
 
     tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, st->prefix, st->prefix + MFB_MAX_EXPERTS + 2);
-    tc_gather_kernel<<<n_rows, 256, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, a.xs16);
+    tc_gather_kernel<<<n_rows, 128, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, n_tokens * c.top_k, c.bits,
+                                            c.shared_bits ? c.shared_bits : c.bits, a.xs16);
     // upper bounds of the work items (the kernels read the exact counts from the prefix arrays)
     const uint32_t items1 = ((n_rows + tc_tile_n(1) - 1) / tc_tile_n(1) + max_groups) * (c.f / TC_M);
     const uint32_t items2 = ((n_rows + tc_tile_n(2) - 1) / tc_tile_n(2) + max_groups) * (c.d / TC_M);

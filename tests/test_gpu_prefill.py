@@ -47,12 +47,13 @@ def test_grouped_ffn_and_reduce_match_oracle(d, f, E, K, bits, T):
 # ---- tensor-core (tcgen05 / TMEM) grouped GEMM ---------------------------------------------------------------
 # d and f multiples of 512; token counts chosen to give groups below 16 rows, around a TMA box, and above one
 # 256-row MMA tile (several passes per expert).
-TC_CASES = [(512, 512, 8, 2, 40), (1024, 512, 16, 4, 300), (512, 512, 4, 2, 700), (2048, 512, 16, 8, 128)]
+TC_CASES = [(512, 512, 8, 2, 40, 4), (1024, 512, 16, 4, 300, 4), (512, 512, 4, 2, 700, 4), (2048, 512, 16, 8, 128, 4),
+            (512, 512, 8, 2, 150, 2), (1024, 1024, 8, 3, 90, 2)]
 
 
-@pytest.mark.parametrize("d,f,E,K,T", TC_CASES)
-def test_tensor_core_grouped_ffn_matches_oracle(d, f, E, K, T):
-    W = O.LayerWeights(d, f, E, K, bits=4, shared=False)
+@pytest.mark.parametrize("d,f,E,K,T,bits", TC_CASES)
+def test_tensor_core_grouped_ffn_matches_oracle(d, f, E, K, T, bits):
+    W = O.LayerWeights(d, f, E, K, bits=bits, shared=False)
     x = make_x("x.tc", T, d)
     lg = O.router_logits(x, O.DT_BF16, W.router)
     idx, w = O.topk_softmax(lg, K)
@@ -81,6 +82,25 @@ def test_tensor_core_matches_generic_kernels():
     p_tc, y_tc, _, _ = _grouped(W, x, idx, w, tensor_core=True)
     p_gen, y_gen, _, _ = _grouped(W, x, idx, w, tensor_core=False)
     assert O.rel_l2(p_tc, p_gen) <= TOL_REL_L2
+
+
+def test_tensor_core_prefill_layer_with_2bit_experts_and_4bit_shared_expert():
+    """The V-shape combination (2-bit routed experts, 4-bit shared expert) through the whole prefill layer."""
+    import torch
+    from mference_b200.moe import MoE
+    d, f, E, K, T = 512, 512, 8, 3, 140
+    W = O.LayerWeights(d, f, E, K, bits=2, shared=True, shared_bits=4)
+    lw = upload_layer(W)
+    x = to_dev16(make_x("x.tc4", T, d), O.DT_BF16)
+    moe_tc = MoE(d, f, E, K, bits=2, shared_bits=4, max_tokens=T, tensor_core_prefill=True)
+    moe_ref = MoE(d, f, E, K, bits=2, shared_bits=4, max_tokens=T)
+    moe_ref.set_generic(True)
+    y_tc, y_ref = torch.empty_like(x), torch.empty_like(x)
+    moe_tc.encode_layer_prefill(lw, x, y_tc)
+    moe_ref.encode_layer(lw, x, y_ref)
+    torch.cuda.synchronize()
+    assert moe_tc.device_status() == 0
+    assert O.rel_l2(y_tc.float().cpu().numpy(), y_ref.float().cpu().numpy()) <= TOL_REL_L2
 
 
 def test_tensor_core_prefill_layer_matches_decode_layer():
