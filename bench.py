@@ -429,6 +429,7 @@ def run_ep(args):
     local_E = E // world
     mine = copy.copy(full)
     mine.pool = full.pool[rank * local_E * full.slot_stride:(rank + 1) * local_E * full.slot_stride]
+    mine.shared_blob = None
     shared = copy.copy(full)
     shared.pool, shared.slot_stride, shared.routed_off = full.shared_blob, full.shared_blob.numel(), full.shared_off
     shared.shared_blob = None

@@ -21,13 +21,16 @@ def _worker(rank, world, port, tokens, q):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     try:
         T = tokens[rank]
         full = synth_layer(ROOT, 0, D, F, E)
         local_E = E // world
         local = copy.copy(full)
         local.pool = full.pool[rank * local_E * full.slot_stride:(rank + 1) * local_E * full.slot_stride]
+        local.shared_blob = None
         shared = copy.copy(full)
         shared.pool, shared.slot_stride, shared.routed_off = full.shared_blob, full.shared_blob.numel(), full.shared_off
         shared.shared_blob = None
@@ -43,6 +46,9 @@ def _worker(rank, world, port, tokens, q):
         exact = bool(torch.equal(y, y_ref))
         err = float((y.float() - y_ref.float()).norm() / y_ref.float().norm())
         q.put((rank, exact, err, layer.last_send_counts))
+    except Exception as exc:   # report instead of leaving the peer waiting in a collective
+        q.put((rank, False, float("inf"), [repr(exc)]))
+        os._exit(1)
     finally:
         dist.destroy_process_group()
 
@@ -60,10 +66,21 @@ def test_two_gpu_expert_parallel_layer_equals_single_gpu_layer(tokens):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, tokens, q)) for r in range(2)]
     for p in procs:
         p.start()
-    results = sorted(q.get(timeout=300) for _ in range(2))
+    results = []
+    try:
+        for _ in range(2):
+            results.append(q.get(timeout=240))
+            if results[-1][2] == float("inf"):
+                break
+    finally:
+        if len(results) < 2 or any(r[2] == float("inf") for r in results):
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
     for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+        p.join(timeout=60)
+    assert len(results) == 2 and all(r[2] != float("inf") for r in results), results
+    results.sort()
     for rank, exact, err, send in results:
         assert err <= 1e-6, (rank, err)
         assert exact, rank
