@@ -44,7 +44,7 @@ ROOT_SEED = 0xB2000001
 N_INPUTS = 4          # distinct input sets cycled through the steps
 # DRAM bytes (read + write) of one stack_mega_kernel launch from an ncu capture, keyed by (batch, rows, layers); the
 # capture of a 2-layer case is scaled by the layer count since every layer reads its own weights once
-TRAFFIC_PER_LAUNCH: dict = {}
+TRAFFIC_PER_LAUNCH: dict = {(64, "fresh", 2): 820.7e6, (64, "fresh", 40): 820.7e6 / 2 * 40}
 
 
 def measured_peaks():
