@@ -120,3 +120,44 @@ def test_tensor_core_prefill_layer_matches_decode_layer():
     torch.cuda.synchronize()
     assert moe_tc.device_status() == 0
     assert O.rel_l2(y_tc.float().cpu().numpy(), y_ref.float().cpu().numpy()) <= TOL_REL_L2
+
+
+# ---- full-size configurations, through properties that need no CPU evaluation --------------------------------
+
+def _prefill_layer(d, f, E, K, T, bits, shared_bits, tensor_core, x, layer, generic=False):
+    import torch
+    from mference_b200.moe import MoE
+    moe = MoE(d, f, E, K, bits=bits, shared_bits=shared_bits, max_tokens=T, tensor_core_prefill=tensor_core)
+    if generic:
+        moe.set_generic(True)
+    y = torch.empty_like(x)
+    (moe.encode_layer_prefill if tensor_core else moe.encode_layer)(layer, x, y)
+    torch.cuda.synchronize()
+    assert moe.device_status() == 0
+    return y
+
+
+@pytest.mark.parametrize("name,d,f,E,K,T,bits,shared_bits", [
+    ("qwen-a3b prefill, 4096 tokens", 2048, 512, 256, 8, 4096, 4, 4),
+    ("dsv4-flash shape, 2-bit experts + 4-bit shared, 2048 tokens", 4096, 2048, 256, 6, 2048, 2, 4),
+])
+def test_full_size_prefill_tensor_core_agrees_with_generic_kernels_and_is_row_independent(name, d, f, E, K, T, bits, shared_bits):
+    """At the full sizes of the benchmark configurations: (1) the tensor-core layer agrees with the generic SIMT
+    kernels on a sample of rows (those kernels are the ones checked against the oracle at small sizes); (2) a
+    token's output does not depend on which other tokens share its batch: permuting the rows permutes the outputs
+    bit for bit."""
+    import torch
+    from mference_b200 import _lib as L
+    from mference_b200.moe import synth_layer, synth_normal
+    layer = synth_layer(0xB2000001, 0, d, f, E, bits=bits, shared_bits=shared_bits)
+    x = synth_normal(0xB2000001, "x.full", T * d, dtype=L.DT_BF16).view(T, d)
+    y = _prefill_layer(d, f, E, K, T, bits, shared_bits, True, x, layer)
+    assert bool(torch.isfinite(y.float()).all())
+    sample = torch.arange(0, T, max(T // 64, 1), device="cuda")[:64]
+    xs = x[sample].contiguous()
+    y_gen = _prefill_layer(d, f, E, K, xs.shape[0], bits, shared_bits, False, xs, layer, generic=True)
+    err = float((y[sample].float() - y_gen.float()).norm() / y_gen.float().norm())
+    assert err <= TOL_REL_L2, (name, err)
+    perm = torch.randperm(T, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    y_perm = _prefill_layer(d, f, E, K, T, bits, shared_bits, True, x[perm].contiguous(), layer)
+    assert torch.equal(y_perm, y[perm]), name
