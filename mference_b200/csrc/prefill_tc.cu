@@ -337,6 +337,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         const uint32_t r = td & (TC_M - 1), part = td >> 7;
         const uint32_t mat = part / PARTS_PER_ROW;              // 0 in phase 2
         const uint32_t word0 = (part % PARTS_PER_ROW) * WORDS;
+        uint32_t piece_off[WORDS];   // byte offset of this thread's 16-byte pieces inside its swizzled 128-byte row
+#pragma unroll
+        for (uint32_t j = 0; j < WORDS; ++j) piece_off[j] = r * 128 + (((word0 + j) ^ (r & 7u)) << 4);
         uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
@@ -394,21 +397,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     const uint32_t s2 = scale_pair((uint16_t)((i & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
                     const uint32_t b2 = scale_pair((uint16_t)((i & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
                     if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
-                    uint8_t* dst = stage_a(s, mat) + r * 128;
+                    uint8_t* dst = stage_a(s, mat);
                     if (four) {
 #pragma unroll
-                        for (uint32_t j = 0; j < WORDS; ++j) {
-                            const uint32_t piece = word0 + j;   // 16-byte piece of the 128-byte row
-                            *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = dequant_word4(cur[i][j], s2, b2);
-                        }
+                        for (uint32_t j = 0; j < WORDS; ++j)
+                            *reinterpret_cast<uint4*>(dst + piece_off[j]) = dequant_word4(cur[i][j], s2, b2);
                     } else {
 #pragma unroll
                         for (uint32_t j = 0; j < WORDS / 2; ++j) {
                             uint4 lo, hi;
                             dequant_word2(cur[i][j], s2, b2, lo, hi);
-                            const uint32_t piece = word0 + 2 * j;
-                            *reinterpret_cast<uint4*>(dst + ((piece ^ (r & 7u)) << 4)) = lo;
-                            *reinterpret_cast<uint4*>(dst + (((piece + 1) ^ (r & 7u)) << 4)) = hi;
+                            *reinterpret_cast<uint4*>(dst + piece_off[2 * j]) = lo;
+                            *reinterpret_cast<uint4*>(dst + piece_off[2 * j + 1]) = hi;
                         }
                     }
                     fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
@@ -453,23 +453,30 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     float u[32];
                     tmem_ld32(taddr + TILE_N + col0, u);
                     const uint32_t fpos = (out_row & ~15u) + tc_perm(out_row & 15u, I.bits);
+                    const bool clamp = !I.shared && P.limit > 0.0f;   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+                    const bool silu = P.activation == MFB_ACT_SILU;
+                    __half* out = P.acts16 + (size_t)(I.pair_start + col0) * P.f + fpos;
+                    const uint32_t live = min(32u, I.n - col0);
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
-                        if (col0 + i >= I.n) break;
+                        if (i >= live) break;
                         float gate = v[i], up = u[i];
-                        if (!I.shared && P.limit > 0.0f) {   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+                        if (clamp) {
                             gate = fminf(gate, P.limit);
                             up = fminf(fmaxf(up, -P.limit), P.limit);
                         }
-                        float a = hidden_act(gate, (int)P.activation) * up;
+                        // SiLU with the fast divide (2 ulp): the result is rounded to fp16 right after
+                        float a = (silu ? __fdividef(gate, 1.0f + __expf(-gate)) : hidden_act(gate, (int)P.activation)) * up;
                         a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                        P.acts16[(size_t)(I.pair_start + col0 + i) * P.f + fpos] = __float2half_rn(a);
+                        out[(size_t)i * P.f] = __float2half_rn(a);
                     }
                 } else {
+                    const uint32_t live = min(32u, I.n - col0);
+                    float* out = P.partial + out_row;
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
-                        if (col0 + i >= I.n) break;
-                        P.partial[(size_t)S.out_row[col0 + i] * P.d + out_row] = v[i];
+                        if (i >= live) break;
+                        out[(size_t)S.out_row[col0 + i] * P.d] = v[i];
                     }
                 }
             }
