@@ -37,7 +37,6 @@ constexpr uint32_t TC_KC = 64;          // k elements per chunk = one 128-byte s
 constexpr uint32_t TC_BOX_ROWS = 64;    // token rows per TMA box
 constexpr uint32_t TC_DQ_WARPS = 8, TC_EPI_WARPS = 4;   // eight dequantising warps measured faster than sixteen
 constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS + TC_EPI_WARPS) * 32;
-constexpr uint32_t TC_A_BYTES = TC_M * 128;            // one matrix tile of one chunk
 constexpr uint32_t TC_TMEM_COLS = 512;                 // two accumulator buffers of 256 columns
 constexpr uint32_t TC_STAGES = 4;
 // token rows per MMA tile: phase 1 keeps gate and up of a tile in one 256-column buffer, phase 2 has one matrix
@@ -91,7 +90,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -106,14 +104,34 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]^T, fp16 inputs, fp32 accumulate; issued by one thread.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]^T, fp16 inputs, fp32 accumulate; issued by one thread.  A sits in tensor memory:
+// 128 lanes = rows, two fp16 per 32-bit column along K.
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// N consecutive 32-bit columns of this thread's TMEM lane, from registers.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Arrives on the mbarrier when every MMA this thread has issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -249,7 +267,10 @@ template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activati
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P, const __grid_constant__ CUtensorMap map_b) {
     constexpr uint32_t NMAT = PHASE == 1 ? 2 : 1;
     constexpr uint32_t TILE_N = tc_tile_n(PHASE);
-    constexpr uint32_t STAGE_BYTES = NMAT * TC_A_BYTES + TILE_N * 128;   // 48 KB in both phases
+    constexpr uint32_t STAGE_BYTES = TILE_N * 128;        // shared memory holds only the activation tiles
+    // tensor memory: accumulators in columns [0, 256) (phase 1: gate then up, N <= 128 each), the dequantised weight
+    // chunks of the ring behind them - a 64-element chunk of a matrix is 32 columns (two fp16 per column)
+    constexpr uint32_t A_COL0 = 256, A_STAGE_COLS = NMAT * 32;
     constexpr uint32_t STAGES = TC_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcShared S;
@@ -274,8 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
     const uint32_t total = S.tp[n_groups] * n_row_tiles;
     volatile uint32_t* abort_flag = &S.abort;
     auto fail = [&]() { *abort_flag = 1u; atomicOr(P.status, STATUS_MBAR_TIMEOUT); };
-    auto stage_a = [&](uint32_t s, uint32_t m) { return smem + s * STAGE_BYTES + m * TC_A_BYTES; };
-    auto stage_b = [&](uint32_t s) { return smem + s * STAGE_BYTES + NMAT * TC_A_BYTES; };
+    auto stage_b = [&](uint32_t s) { return smem + s * STAGE_BYTES; };
 
     if (warp == 0) {
         // ---------------------------------------------------------------- activation tiles by TMA
@@ -301,7 +321,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
-            const uint32_t buf = item & 1u, use = (item >> 1) & 1u;   // accumulator buffer and how often it has been used
+            const uint32_t buf = 0, use = item & 1u;   // one accumulator buffer; `use` = parity of its uses
             if (!mbar_wait(&S.acc_empty[buf], use ^ 1u)) { fail(); break; }
             tc_fence_after();
             const uint32_t idesc = instr_desc(I.n_mma);
@@ -314,10 +334,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     const uint64_t b_desc = smem_desc(stage_b(s));
 #pragma unroll
                     for (uint32_t m = 0; m < NMAT; ++m) {
-                        const uint64_t a_desc = smem_desc(stage_a(s, m));
+                        const uint32_t a_tmem = tmem + A_COL0 + s * A_STAGE_COLS + m * 32;
 #pragma unroll
-                        for (uint32_t kk = 0; kk < TC_KC / 16; ++kk)   // 16 k per MMA = 32 bytes along the swizzled row
-                            umma_f16(tmem + buf * 256 + m * TILE_N, a_desc + kk * 2, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
+                        for (uint32_t kk = 0; kk < TC_KC / 16; ++kk)   // 16 k per MMA: 8 TMEM columns of A, 32 bytes of B's swizzled row
+                            umma_f16_ta(tmem + m * TILE_N, a_tmem + kk * 8, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
                     }
                     umma_commit(&S.empty[s]);   // frees the stage once these MMAs have read it
                 }
@@ -333,13 +353,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         // The dequantising threads share the NMAT * 128 row chunks of a stage: a thread owns WORDS consecutive 16-byte
         // pieces of fp16 (= WORDS packed words at 4 bits, WORDS / 2 at 2 bits) of one row.
         constexpr uint32_t WORDS = NMAT * 1024 / (TC_DQ_WARPS * 32), PARTS_PER_ROW = 8 / WORDS;
-        const uint32_t td = threadIdx.x - 64;
-        const uint32_t r = td & (TC_M - 1), part = td >> 7;
+        // a warp may only touch the 32 TMEM lanes of its quarter (warp index % 4), so it takes those 32 weight rows;
+        // the two warps of a quarter split the matrices (phase 1) or the chunk's halves (phase 2)
+        const uint32_t q = warp & 3u, part = (warp - 2) >> 2;
+        const uint32_t r = 32 * q + lane;
         const uint32_t mat = part / PARTS_PER_ROW;              // 0 in phase 2
         const uint32_t word0 = (part % PARTS_PER_ROW) * WORDS;
-        uint32_t piece_off[WORDS];   // byte offset of this thread's 16-byte pieces inside its swizzled 128-byte row
-#pragma unroll
-        for (uint32_t j = 0; j < WORDS; ++j) piece_off[j] = r * 128 + (((word0 + j) ^ (r & 7u)) << 4);
+        const uint32_t a_lane_col = ((32 * q) << 16) + A_COL0 + mat * 32 + word0 * 4;   // + stage * A_STAGE_COLS
         uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
@@ -397,21 +417,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     const uint32_t s2 = scale_pair((uint16_t)((i & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
                     const uint32_t b2 = scale_pair((uint16_t)((i & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
                     if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
-                    uint8_t* dst = stage_a(s, mat);
+                    uint32_t outw[WORDS * 4];   // WORDS * 8 fp16 weights = WORDS * 4 TMEM columns of this row
                     if (four) {
 #pragma unroll
-                        for (uint32_t j = 0; j < WORDS; ++j)
-                            *reinterpret_cast<uint4*>(dst + piece_off[j]) = dequant_word4(cur[i][j], s2, b2);
+                        for (uint32_t j = 0; j < WORDS; ++j) {
+                            const uint4 o = dequant_word4(cur[i][j], s2, b2);
+                            outw[4 * j] = o.x; outw[4 * j + 1] = o.y; outw[4 * j + 2] = o.z; outw[4 * j + 3] = o.w;
+                        }
                     } else {
 #pragma unroll
                         for (uint32_t j = 0; j < WORDS / 2; ++j) {
                             uint4 lo, hi;
                             dequant_word2(cur[i][j], s2, b2, lo, hi);
-                            *reinterpret_cast<uint4*>(dst + piece_off[2 * j]) = lo;
-                            *reinterpret_cast<uint4*>(dst + piece_off[2 * j + 1]) = hi;
+                            outw[8 * j] = lo.x; outw[8 * j + 1] = lo.y; outw[8 * j + 2] = lo.z; outw[8 * j + 3] = lo.w;
+                            outw[8 * j + 4] = hi.x; outw[8 * j + 5] = hi.y; outw[8 * j + 6] = hi.z; outw[8 * j + 7] = hi.w;
                         }
                     }
-                    fence_async_shared();   // generic-proxy writes -> visible to the tensor core's async proxy
+                    if (WORDS == 8) tmem_st32(tmem + a_lane_col + s * A_STAGE_COLS, reinterpret_cast<const uint32_t (&)[32]>(outw));
+                    else tmem_st16(tmem + a_lane_col + s * A_STAGE_COLS, reinterpret_cast<const uint32_t (&)[16]>(outw));
+                    tmem_st_wait();
+                    tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&S.full_a[s]);
                 }
@@ -442,10 +467,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     for (uint32_t n = 0; n < I.n; ++n) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
                 continue;
             }
-            const uint32_t buf = item & 1u, use = (item >> 1) & 1u;
+            const uint32_t buf = 0, use = item & 1u;
             if (!mbar_wait(&S.acc_full[buf], use)) { fail(); break; }
             tc_fence_after();
-            const uint32_t taddr = tmem + ((32 * q) << 16) + buf * 256;
+            const uint32_t taddr = tmem + ((32 * q) << 16);
             for (uint32_t col0 = 0; col0 < I.n; col0 += 32) {
                 float v[32];
                 tmem_ld32(taddr + col0, v);
@@ -563,8 +588,7 @@ struct TcState {
     bool ready = false;
 };
 
-constexpr size_t TC_SMEM_BYTES = TC_STAGES * (2 * TC_A_BYTES + tc_tile_n(1) * 128) + 1024;   // the same in phase 2
-static_assert(2 * TC_A_BYTES + tc_tile_n(1) * 128 == TC_A_BYTES + tc_tile_n(2) * 128, "both phases use 48 KB stages");
+constexpr size_t TC_SMEM_BYTES = TC_STAGES * tc_tile_n(2) * 128 + 1024;   // activation tiles only (phase 2 is the larger)
 
 int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
     const cuuint64_t dims[2] = {inner, rows};
