@@ -7,23 +7,25 @@
 //     phase 2   P[pair, d] = H[pair,:] . Wdown[d,:]                                    contraction over f
 // With many rows per expert this is a dense contraction, so it goes to the tensor cores.
 //
-// Shape of one MMA tile: M = 128 *weight rows*, N = up to 256 *token rows* of one expert, K in chunks of 64.  The
-// weights are the A operand: their row count is always a multiple of 128, while the ragged side (tokens of an
-// expert, from a handful to thousands) rides in N, which the hardware accepts in steps of 16.  Accumulators live in
-// TMEM: two buffers of 256 columns; phase 1 (N <= 128) keeps gate and up side by side in a buffer, phase 2 (N <= 256)
-// fills a buffer with its one matrix.
+// Shape of one MMA tile: M = 128 *weight rows*, N = *token rows* of one expert (up to 128 in phase 1, 256 in phase 2),
+// K in chunks of 64.  The weights are the A operand: their row count is always a multiple of 128, while the ragged
+// side (tokens of an expert, from a handful to thousands) rides in N, which the hardware accepts in steps of 16.
+// Tensor memory (512 columns per CTA) holds the accumulators in columns [0, 256) - phase 1: gate then up - and,
+// behind them, a four-stage ring of dequantised weight chunks: the A operand is read from tensor memory, so the
+// weights never touch shared memory, which only stages the activations (B operand).
 //
-// Roles inside a CTA (704 threads), connected by mbarriers, every wait bounded:
-//   warp 0       TMA: the activation chunk [N x 64] fp16 of the current token rows (gathered once per call into
-//                expert-major order, so a group's rows are contiguous) lands in shared memory in the 128-byte swizzle
-//   warp 1       one elected thread issues tcgen05.mma (A and B from shared memory, D in TMEM) and tcgen05.commit
-//   warps 2-17   dequantise: packed 4-bit codes + fp16/bf16 scale and bias -> fp16 weights, written straight into the
-//                swizzled K-major layout the MMA reads; the packed bytes come from global memory a batch ahead
-//   warps 18-21  epilogue: tcgen05.ld the accumulators (warp w reads TMEM lanes 32 (w % 4) ...), apply the activation
-//                (phase 1) and store fp16 hidden rows / fp32 partial rows (phase 2).  The accumulators are double-
-//                buffered (2 x 256 TMEM columns), so tile i is read out while tile i + 1 is being multiplied.
-// The K order inside each 8-element piece is the one the mask-unpack of a packed word yields (0 4 1 5 2 6 3 7);
-// the gather kernel and the phase-1 epilogue store activations in the same order, so nothing is shuffled.
+// Roles inside a CTA (448 threads in phase 1, 576 in phase 2), connected by mbarriers, every wait bounded:
+//   warp 0        TMA: the activation chunk [N x 64] fp16 of the current token rows (gathered once per call into
+//                 expert-major order, so a group's rows are contiguous) lands in shared memory in the 128-byte swizzle
+//   warp 1        one elected thread issues tcgen05.mma (A from TMEM, B from shared memory, D in TMEM) and tcgen05.commit
+//   warps 2-9     dequantise: packed 4-bit or 2-bit codes + fp16/bf16 scale and bias -> fp16 weights, stored with
+//                 tcgen05.st into the ring (a warp owns the 32 rows of its TMEM lane quarter); the packed bytes and
+//                 scales come from global memory eight chunks ahead, across work-item boundaries
+//   warps 10-...  epilogue (4 warps in phase 1, 8 in phase 2): tcgen05.ld the accumulators (warp w reads TMEM lanes
+//                 32 (w % 4) ...), apply the activation and store fp16 hidden rows (phase 1) / fp32 partial rows (phase 2)
+// The K order inside each 8- or 16-element run is the one the mask-unpack of a packed word yields (4-bit: 0 4 1 5 2
+// 6 3 7; 2-bit: 0 8 1 9 ...); the gather kernel and the phase-1 epilogue store activations in the same order, so
+// nothing is shuffled.
 #include <cuda.h>
 
 #include "prefill_tc.cuh"
@@ -35,8 +37,11 @@ namespace {
 constexpr uint32_t TC_M = 128;          // weight rows per tile
 constexpr uint32_t TC_KC = 64;          // k elements per chunk = one 128-byte swizzle row of fp16
 constexpr uint32_t TC_BOX_ROWS = 64;    // token rows per TMA box
-constexpr uint32_t TC_DQ_WARPS = 8, TC_EPI_WARPS = 4;   // eight dequantising warps measured faster than sixteen
-constexpr uint32_t TC_THREADS = (2 + TC_DQ_WARPS + TC_EPI_WARPS) * 32;
+constexpr uint32_t TC_DQ_WARPS = 8;   // eight dequantising warps measured faster than sixteen
+// epilogue warps: four in phase 1 (the dequantising threads need 128 registers, which 14 warps still allow), eight in
+// phase 2, whose accumulator tiles are twice as wide
+__host__ __device__ constexpr uint32_t tc_epi_warps(int phase) { return phase == 1 ? 4 : 8; }
+__host__ __device__ constexpr uint32_t tc_threads(int phase) { return (2 + TC_DQ_WARPS + tc_epi_warps(phase)) * 32; }
 constexpr uint32_t TC_TMEM_COLS = 512;                 // two accumulator buffers of 256 columns
 constexpr uint32_t TC_STAGES = 4;
 // token rows per MMA tile: phase 1 keeps gate and up of a tile in one 256-column buffer, phase 2 has one matrix
@@ -264,9 +269,10 @@ struct TcShared {
 };
 
 template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P, const __grid_constant__ CUtensorMap map_b) {
+__global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcParams P, const __grid_constant__ CUtensorMap map_b) {
     constexpr uint32_t NMAT = PHASE == 1 ? 2 : 1;
     constexpr uint32_t TILE_N = tc_tile_n(PHASE);
+    constexpr uint32_t TC_EPI_WARPS = tc_epi_warps(PHASE);
     constexpr uint32_t STAGE_BYTES = TILE_N * 128;        // shared memory holds only the activation tiles
     // tensor memory: accumulators in columns [0, 256) (phase 1: gate then up, N <= 128 each), the dequantised weight
     // chunks of the ring behind them - a 64-element chunk of a matrix is 32 columns (two fp16 per column)
@@ -328,7 +334,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
             bool ok = true;
             for (uint32_t c = 0; c < n_chunks && ok; ++c, ++seq) {
                 const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
-                if (!mbar_wait(&S.full_a[s], ph) || !mbar_wait(&S.full_b[s], ph)) { fail(); ok = false; break; }
+                if (!mbar_wait(&S.full_a[s], ph)) { fail(); ok = false; break; }
+                if (!mbar_wait(&S.full_b[s], ph)) { fail(); ok = false; break; }
                 tc_fence_after();
                 if (lane == 0) {
                     const uint64_t b_desc = smem_desc(stage_b(s));
@@ -360,79 +367,100 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
         const uint32_t mat = part / PARTS_PER_ROW;              // 0 in phase 2
         const uint32_t word0 = (part % PARTS_PER_ROW) * WORDS;
         const uint32_t a_lane_col = ((32 * q) << 16) + A_COL0 + mat * 32 + word0 * 4;   // + stage * A_STAGE_COLS
+        // Packed codes and scales are fetched eight chunks (one scale vector) ahead of their use, through a ring of
+        // registers that a load cursor refills as soon as a slot has been consumed; the cursor runs on into the
+        // next work item, so the memory latency is hidden across item boundaries too.
+        struct RowSrc {
+            const uint32_t* wrow; const uint4* srow; const uint4* brow;
+            uint32_t wpc, it, blk; bool four, valid;
+        };
+        auto open_item = [&](uint32_t it) {   // first resident item at or after `it` in this CTA's sequence
+            RowSrc R{};
+            for (; it < total; it += gridDim.x) {
+                const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+                if (!I.ok) continue;
+                const uint32_t w_off = PHASE == 1 ? (mat ? I.off.up_w : I.off.gate_w) : I.off.down_w;
+                const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
+                const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
+                const size_t row = I.row0 + r;
+                R.four = I.bits == 4;
+                R.wpc = R.four ? 8u : 4u;   // packed words per 64-element chunk of a row
+                R.wrow = reinterpret_cast<const uint32_t*>(I.blob + w_off + row * (K * I.bits / 8)) + (R.four ? word0 : word0 / 2);
+                R.srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
+                R.brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
+                R.valid = true;
+                break;
+            }
+            R.it = it; R.blk = 0;
+            return R;
+        };
+        auto load_n = [&](const uint32_t* src, uint32_t (&dst)[WORDS], uint32_t n) {   // n = 1, 2, 4 or 8 words
+            if (n >= 4) {
+                const uint4 v = *reinterpret_cast<const uint4*>(src);
+                dst[0] = v.x; dst[1 % WORDS] = v.y; dst[2 % WORDS] = v.z; dst[3 % WORDS] = v.w;
+                if (n == 8) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(src + 4);
+                    dst[4 % WORDS] = u.x; dst[5 % WORDS] = u.y; dst[6 % WORDS] = u.z; dst[7 % WORDS] = u.w;
+                }
+            } else if (n == 2) {
+                const uint2 v = *reinterpret_cast<const uint2*>(src);
+                dst[0] = v.x; dst[1 % WORDS] = v.y;
+            } else {
+                dst[0] = *src;
+            }
+        };
+        constexpr uint32_t RING = 8;
+        uint32_t ring[RING][WORDS];
+        uint4 sc_nxt = make_uint4(0, 0, 0, 0), bi_nxt = make_uint4(0, 0, 0, 0);
+        RowSrc Lc = open_item(blockIdx.x);   // load cursor
+        auto load_block_head = [&]() {       // scales and biases of the cursor's block
+            if (Lc.valid) { sc_nxt = Lc.srow[Lc.blk]; bi_nxt = Lc.brow[Lc.blk]; }
+        };
+        auto load_chunk = [&](uint32_t i, uint32_t (&dst)[WORDS]) {   // chunk i of the cursor's block
+            if (Lc.valid) load_n(Lc.wrow + (Lc.blk * RING + i) * Lc.wpc, dst, Lc.four ? WORDS : WORDS / 2);
+        };
+        auto advance_block = [&]() {
+            if (!Lc.valid) return;
+            if (++Lc.blk * RING >= n_chunks) Lc = open_item(Lc.it + gridDim.x);
+        };
+        // prime the ring with the first block
+        load_block_head();
+#pragma unroll
+        for (uint32_t i = 0; i < RING; ++i) load_chunk(i, ring[i]);
+        advance_block();
         uint32_t seq = 0;
-        for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
+        bool ok = true;
+        for (uint32_t it = blockIdx.x; it < total && !*abort_flag && ok; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
-            const uint32_t w_off = PHASE == 1 ? (mat ? I.off.up_w : I.off.gate_w) : I.off.down_w;
-            const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
-            const uint32_t b_off = PHASE == 1 ? (mat ? I.off.up_b : I.off.gate_b) : I.off.down_b;
-            const size_t row = I.row0 + r;
             const bool four = I.bits == 4;
-            const uint32_t wpc = four ? 8u : 4u;   // packed words per 64-element chunk of a row
-            const uint32_t* wrow = reinterpret_cast<const uint32_t*>(I.blob + w_off + row * (K * I.bits / 8)) + (four ? word0 : word0 / 2);
-            const uint4* srow = reinterpret_cast<const uint4*>(I.blob + s_off + row * (K / 64) * 2);
-            const uint4* brow = reinterpret_cast<const uint4*>(I.blob + b_off + row * (K / 64) * 2);
-            // packed codes travel in batches of four chunks, one batch ahead of the one in use: a load has four
-            // chunks of work to hide its latency behind
-            constexpr uint32_t BATCH = 4;
-            uint32_t pre[BATCH][WORDS], cur[BATCH][WORDS];
-            auto load_n = [&](const uint32_t* src, uint32_t (&dst)[WORDS], uint32_t n) {   // n = 1, 2, 4 or 8 words
-                if (n >= 4) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(src);
-                    dst[0] = v.x; dst[1 % WORDS] = v.y; dst[2 % WORDS] = v.z; dst[3 % WORDS] = v.w;
-                    if (n == 8) {
-                        const uint4 u = *reinterpret_cast<const uint4*>(src + 4);
-                        dst[4 % WORDS] = u.x; dst[5 % WORDS] = u.y; dst[6 % WORDS] = u.z; dst[7 % WORDS] = u.w;
-                    }
-                } else if (n == 2) {
-                    const uint2 v = *reinterpret_cast<const uint2*>(src);
-                    dst[0] = v.x; dst[1 % WORDS] = v.y;
-                } else {
-                    dst[0] = *src;
-                }
-            };
-            auto load_words = [&](uint32_t chunk, uint32_t (&dst)[WORDS]) { load_n(wrow + chunk * wpc, dst, four ? WORDS : WORDS / 2); };
+            for (uint32_t cb = 0; cb < n_chunks && ok; cb += RING) {   // n_chunks is a multiple of 8
+                const uint4 sc8 = sc_nxt, bi8 = bi_nxt;   // fetched one block ago
+                load_block_head();                        // the cursor's block: the one after this
 #pragma unroll
-            for (uint32_t i = 0; i < BATCH; ++i) load_words(i, pre[i]);
-            uint4 sc8 = make_uint4(0, 0, 0, 0), bi8 = make_uint4(0, 0, 0, 0);
-            bool ok = true;
-            for (uint32_t cb = 0; cb < n_chunks && ok; cb += BATCH) {   // n_chunks is a multiple of 8
-                if ((cb & 7u) == 0) { sc8 = srow[cb >> 3]; bi8 = brow[cb >> 3]; }
-#pragma unroll
-                for (uint32_t i = 0; i < BATCH; ++i)
-#pragma unroll
-                    for (uint32_t j = 0; j < WORDS; ++j) cur[i][j] = pre[i][j];
-                if (cb + BATCH < n_chunks) {
-#pragma unroll
-                    for (uint32_t i = 0; i < BATCH; ++i) load_words(cb + BATCH + i, pre[i]);
-                }
-                // this batch's four scale / bias pairs sit in two words of the eight-group vectors
-                const uint32_t sw0 = (cb & 4u) ? sc8.z : sc8.x, sw1 = (cb & 4u) ? sc8.w : sc8.y;
-                const uint32_t bw0 = (cb & 4u) ? bi8.z : bi8.x, bw1 = (cb & 4u) ? bi8.w : bi8.y;
-#pragma unroll
-                for (uint32_t i = 0; i < BATCH; ++i, ++seq) {
+                for (uint32_t i = 0; i < RING; ++i, ++seq) {
                     const uint32_t s = seq % STAGES, ph = (seq / STAGES) & 1u;
-                    const uint32_t sw = i < 2 ? sw0 : sw1, bw = i < 2 ? bw0 : bw1;
+                    const uint32_t sw = (&sc8.x)[i >> 1], bw = (&bi8.x)[i >> 1];
                     const uint32_t s2 = scale_pair((uint16_t)((i & 1u) ? (sw >> 16) : (sw & 0xFFFFu)), P.scale_dtype);
                     const uint32_t b2 = scale_pair((uint16_t)((i & 1u) ? (bw >> 16) : (bw & 0xFFFFu)), P.scale_dtype);
-                    if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
                     uint32_t outw[WORDS * 4];   // WORDS * 8 fp16 weights = WORDS * 4 TMEM columns of this row
                     if (four) {
 #pragma unroll
                         for (uint32_t j = 0; j < WORDS; ++j) {
-                            const uint4 o = dequant_word4(cur[i][j], s2, b2);
+                            const uint4 o = dequant_word4(ring[i][j], s2, b2);
                             outw[4 * j] = o.x; outw[4 * j + 1] = o.y; outw[4 * j + 2] = o.z; outw[4 * j + 3] = o.w;
                         }
                     } else {
 #pragma unroll
                         for (uint32_t j = 0; j < WORDS / 2; ++j) {
                             uint4 lo, hi;
-                            dequant_word2(cur[i][j], s2, b2, lo, hi);
+                            dequant_word2(ring[i][j], s2, b2, lo, hi);
                             outw[8 * j] = lo.x; outw[8 * j + 1] = lo.y; outw[8 * j + 2] = lo.z; outw[8 * j + 3] = lo.w;
                             outw[8 * j + 4] = hi.x; outw[8 * j + 5] = hi.y; outw[8 * j + 6] = hi.z; outw[8 * j + 7] = hi.w;
                         }
                     }
+                    load_chunk(i, ring[i]);   // refill the slot just consumed: needed eight chunks from now
+                    if (!mbar_wait(&S.empty[s], ph ^ 1u)) { fail(); ok = false; break; }
                     if (WORDS == 8) tmem_st32(tmem + a_lane_col + s * A_STAGE_COLS, reinterpret_cast<const uint32_t (&)[32]>(outw));
                     else tmem_st16(tmem + a_lane_col + s * A_STAGE_COLS, reinterpret_cast<const uint32_t (&)[16]>(outw));
                     tmem_st_wait();
@@ -440,14 +468,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&S.full_a[s]);
                 }
+                advance_block();
             }
-            if (!ok) break;
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (its own four warps: the
-        // accumulators are double-buffered, so item i is read out while item i + 1 is being multiplied)
-        const uint32_t te = threadIdx.x - (2 + TC_DQ_WARPS) * 32;   // 0..127
+        // ---------------------------------------------------------------- epilogue: eight warps, two per TMEM lane
+        // quarter, each taking every other block of 32 token columns
+        const uint32_t te = threadIdx.x - (2 + TC_DQ_WARPS) * 32;   // 0..255
         const uint32_t q = warp & 3u;                               // TMEM lane quarter this warp may read
+        const uint32_t col_par = (warp - (2 + TC_DQ_WARPS)) >> 2;   // which 32-column blocks this warp takes
+        constexpr uint32_t COL_WAYS = TC_EPI_WARPS / 4;
         uint32_t item = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
@@ -455,23 +485,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_ffn_kernel(const TcParams P,
             if (PHASE == 2) {
                 // where each token column of this item goes: fetched once into shared memory (a dependent global
                 // load per column inside the loop below would serialise it)
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // the previous item's table is no longer read
+                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");   // the previous item's table is no longer read
                 for (uint32_t n = te; n < I.n; n += TC_EPI_WARPS * 32) {
                     const mfb_pair pr = P.sorted[I.pair_start + n];
                     S.out_row[n] = pr.token * P.slots + pr.rank;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
             }
             if (!I.ok) {
                 if (PHASE == 2)   // a non-resident expert contributes nothing: clear its partial rows
-                    for (uint32_t n = 0; n < I.n; ++n) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
+                    for (uint32_t n = col_par; n < I.n; n += COL_WAYS) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
                 continue;
             }
             const uint32_t buf = 0, use = item & 1u;
             if (!mbar_wait(&S.acc_full[buf], use)) { fail(); break; }
             tc_fence_after();
             const uint32_t taddr = tmem + ((32 * q) << 16);
-            for (uint32_t col0 = 0; col0 < I.n; col0 += 32) {
+            for (uint32_t col0 = col_par * 32; col0 < I.n; col0 += 32 * COL_WAYS) {
                 float v[32];
                 tmem_ld32(taddr + col0, v);
                 if (PHASE == 1) {
@@ -667,8 +697,8 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     const uint32_t items2 = ((n_rows + tc_tile_n(2) - 1) / tc_tile_n(2) + max_groups) * (c.d / TC_M);
     const uint32_t grid1 = items1 < (uint32_t)m->sm_count ? items1 : (uint32_t)m->sm_count;
     const uint32_t grid2 = items2 < (uint32_t)m->sm_count ? items2 : (uint32_t)m->sm_count;
-    tc_ffn_kernel<1><<<grid1, TC_THREADS, TC_SMEM_BYTES, s>>>(P, st->map_x);
-    tc_ffn_kernel<2><<<grid2, TC_THREADS, TC_SMEM_BYTES, s>>>(P, st->map_h);
+    tc_ffn_kernel<1><<<grid1, tc_threads(1), TC_SMEM_BYTES, s>>>(P, st->map_x);
+    tc_ffn_kernel<2><<<grid2, tc_threads(2), TC_SMEM_BYTES, s>>>(P, st->map_h);
     count_launches(4);
     MFB_CUDA(cudaGetLastError());
     return MFB_OK;
