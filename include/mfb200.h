@@ -142,8 +142,11 @@ int32_t mfb_moe_destroy(mfb_moe* moe);
 int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on);
 /* Phase tracing of the fused stack kernel (the reference's MFERENCE_PHASES counters,
  * Sources/Mference/Runtime/Inference/RealForwardRunner.swift:395-398, 5478-5529): while a device buffer of
- * n_layers x 8 uint64 is attached, mfb_moe_stack / mfb_moe_stack_rows record the GPU global timer (ns) at the
- * eight phase boundaries of every layer: norm, logits, select, sort, phase 1, barrier, phase 2, end.  NULL detaches. */
+ * (n_layers + 17) x 8 uint64 is attached, mfb_moe_stack / mfb_moe_stack_rows record in its first n_layers rows the
+ * GPU global timer (ns) at the eight phase boundaries of every layer - norm, logits, select, sort, phase 1, barrier,
+ * phase 2, end - and in the 17 rows behind them SM-cycle counters of CTA 0: one row per warp (wait and compute cycles
+ * of the two FFN phases), and in the last row the SM clock and the global timer at the start and end of the launch
+ * (cycles per ns).  The caller zeroes the buffer; NULL detaches. */
 int32_t mfb_moe_set_trace(mfb_moe* moe, uint64_t* device_stamps);
 /* Reads and clears the device status word that kernels set when a bounded wait runs out. Synchronises `stream`. */
 int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status);

@@ -236,7 +236,8 @@ class MoE:
         L.check(self.lib.mfb_moe_set_generic(self.handle, int(on)))
 
     def set_trace(self, stamps):
-        """Attach (or detach with None) a uint64 [n_layers, 8] CUDA tensor for per-phase global-timer stamps."""
+        """Attach (or detach with None) a zeroed uint64 [n_layers + 17, 8] CUDA tensor: per-phase global-timer stamps
+        of every layer, then 17 rows of cycle counters of CTA 0 (see mfb_moe_set_trace in the header)."""
         L.check(self.lib.mfb_moe_set_trace(self.handle, _ptr(stamps)))
 
     def device_status(self) -> int:

@@ -270,3 +270,31 @@ def test_fused_stack_kernel_equals_layer_by_layer(T):
         moe.encode_layer(lw, rows[l], ref)
         assert torch.equal(c[l].view(torch.int16), ref.view(torch.int16)), l
     assert moe.device_status() == 0
+
+
+def test_phase_trace_of_the_fused_stack_kernel():
+    """mfb_moe_set_trace: per-layer phase stamps are increasing global-timer values and the output is unchanged."""
+    import torch
+    from mference_b200 import _lib as L
+    from mference_b200.moe import MoE, synth_layer, synth_normal
+    d, f, E, K, T, NL = 2048, 512, 16, 8, 8, 3
+    layers = [synth_layer(0xB2000001, l, d, f, E) for l in range(NL)]
+    moe = MoE(d, f, E, K, max_tokens=T)
+    stack = moe.make_stack(layers)
+    h0 = synth_normal(0xB2000001, "x.trace", T * d, dtype=L.DT_BF16).view(T, d)
+    ref = h0.clone()
+    moe.encode_stack(stack, ref)
+    trace = torch.zeros((NL + 17, 8), dtype=torch.int64, device="cuda")
+    moe.set_trace(trace)
+    h = h0.clone()
+    moe.encode_stack(stack, h)
+    moe.set_trace(None)
+    torch.cuda.synchronize()
+    assert moe.device_status() == 0
+    assert torch.equal(h, ref)
+    stamps = trace[:NL].cpu().numpy()
+    assert (stamps > 0).all()
+    flat = stamps.reshape(-1)
+    assert (flat[1:] >= flat[:-1]).all()          # phases within a layer and layers in order
+    clocks = trace[NL + 16].cpu().numpy()
+    assert clocks[5] > clocks[4] and clocks[7] > clocks[6]   # SM clock and global timer advanced over the launch
