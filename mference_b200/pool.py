@@ -71,9 +71,11 @@ class ExpertPool:
         ms = (C.c_uint8 * max(n, 1))(*[1 if i in set(plan.misses) else 0 for i in range(n)])
         return n, ex, sl, ms
 
-    def execute_expert_cache_plan(self, plan: ExpertCachePlan, host_blobs, stream: int = 0):
-        """Fill the misses from pinned host tensors (host_blobs[expert] -> uint8 tensor) and publish them, all on
-        ``stream``.  Returns the byte offset of every expert's slot in the slab."""
+    def fill_async(self, plan: ExpertCachePlan, host_blobs, stream: int = 0):
+        """beginAsyncFill: copy the plan's misses from pinned host tensors (host_blobs[expert] -> uint8 tensor) into
+        their slots on ``stream``.  The device slot table is untouched until ``publish``."""
+        if not plan.misses:
+            return
         n, ex, sl, ms = self._arrays(plan)
         ptrs = (C.c_void_p * max(n, 1))()
         blob_bytes = 0
@@ -81,9 +83,18 @@ class ExpertPool:
             t = host_blobs[plan.experts[i]]
             ptrs[i] = t.data_ptr()
             blob_bytes = t.numel() * t.element_size()
-        if plan.misses:
-            L.check(self.lib.mfb_pool_fill_async(self.handle, C.c_void_p(stream), ex, sl, ms, n, ptrs, blob_bytes))
+        L.check(self.lib.mfb_pool_fill_async(self.handle, C.c_void_p(stream), ex, sl, ms, n, ptrs, blob_bytes))
+
+    def publish(self, plan: ExpertCachePlan, stream: int = 0):
+        """Makes the plan's slot assignment visible to kernels launched on ``stream`` after this call."""
+        n, ex, sl, ms = self._arrays(plan)
         L.check(self.lib.mfb_pool_publish(self.handle, C.c_void_p(stream), ex, sl, ms, n))
+
+    def execute_expert_cache_plan(self, plan: ExpertCachePlan, host_blobs, stream: int = 0):
+        """Fill the misses from pinned host tensors and publish them, all on ``stream``.  Returns the byte offset of
+        every expert's slot in the slab."""
+        self.fill_async(plan, host_blobs, stream)
+        self.publish(plan, stream)
         return [s * self.slot_stride for s in plan.assigned_slots]
 
     def note_all_hit_use(self, experts: Sequence[int]):
