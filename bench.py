@@ -322,6 +322,16 @@ def zipf_logit_bias(num_experts: int, exponent: float = 1.1):
     return np.log(p / p.sum()).astype(np.float32)
 
 
+RAGGED_SEQUENCES, RAGGED_PARTS = 48, (1, 256, 512, 1024)
+
+
+def ragged_mix_offsets():
+    """configs[4]: row offsets of the segments of the packed batch (sequence-major: decode row, then the three chunks)."""
+    import numpy as np
+    sizes = np.tile(np.asarray(RAGGED_PARTS, dtype=np.int64), RAGGED_SEQUENCES)
+    return np.concatenate([[0], np.cumsum(sizes)])
+
+
 def run_prefill(args):
     """configs[2]: T token rows through one Q layer - RMSNorm, router with a Zipf(1.1) logit bias, sort by expert, the
     ragged grouped GEMM on the tensor cores (routed experts + the shared expert), weighted reduce + residual."""
@@ -331,9 +341,12 @@ def run_prefill(args):
 
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     lib = L.load()
-    T = args.tokens
+    ragged = args.workload == "ragged"
+    offsets = ragged_mix_offsets() if ragged else None
+    T = int(offsets[-1]) if ragged else args.tokens
     layer = synth_layer(ROOT_SEED, 0, D, F, E)
-    layer.logit_bias = torch.from_numpy(zipf_logit_bias(E)).cuda()
+    if not ragged:
+        layer.logit_bias = torch.from_numpy(zipf_logit_bias(E)).cuda()
     moe = MoE(D, F, E, K, max_tokens=T, tensor_core_prefill=True)
     n_sets = N_INPUTS
     inputs = [synth_normal(ROOT_SEED, f"x.prefill.{i}", T * D, dtype=L.DT_BF16).view(T, D) for i in range(n_sets)]
@@ -391,7 +404,10 @@ def run_prefill(args):
         "metric": "moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16xf16->f32", "data": "synthetic",
-        "config": {"workload": f"configs[2]: prefill gather-QMM, {T} tokens, one Qwen3.6-A3B MoE layer, Zipf(1.1) router bias",
+        "config": {"workload": (f"configs[4]: ragged continuous-batch mix, 48 sequences x (1 decode row + prefill chunks of 256/512/1024) "
+                                f"= {T} rows in {len(offsets) - 1} segments packed into one batch, one Qwen3.6-A3B MoE layer, unbiased router"
+                                if ragged else
+                                f"configs[2]: prefill gather-QMM, {T} tokens, one Qwen3.6-A3B MoE layer, Zipf(1.1) router bias"),
                    "hidden": D, "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4, "group_size": 64,
                    "pairs": T * K, "largest_group": int(counts.max()), "smallest_group": int(counts.min()),
                    "experts_used": int((counts > 0).sum()),
@@ -512,8 +528,9 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers only for profiling a small case")
     ap.add_argument("--launch", default="fused", choices=["fused", "layers"],
                     help="layers: per-layer, per-phase launches of the same kernels (for profiling one phase alone)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ragged", "ep"],
                     help="decode: configs[1] (the headline); prefill: configs[2], 4096 tokens through one layer's gather-QMM; "
+                         "ragged: configs[4], the 86,064-row continuous-batch mix through the same layer; "
                          "ep: the same prefill layer with experts sharded over --gpus ranks (NCCL all-to-all)")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill token rows")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -523,7 +540,7 @@ def main():
         args.rows = "chained" if args.batch == 1 else "fresh"
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "prefill":
+    elif args.workload in ("prefill", "ragged"):
         run_prefill(args)
     elif args.workload == "ep":
         run_ep(args)

@@ -161,3 +161,32 @@ def test_full_size_prefill_tensor_core_agrees_with_generic_kernels_and_is_row_in
     perm = torch.randperm(T, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
     y_perm = _prefill_layer(d, f, E, K, T, bits, shared_bits, True, x[perm].contiguous(), layer)
     assert torch.equal(y_perm, y[perm]), name
+
+
+def test_ragged_continuous_batch_mix_full_size():
+    """The ragged mix of the benchmark configurations at full size: 48 sequences, each one decode row and prefill
+    chunks of 256, 512 and 1024 rows, packed into one batch of 86,064 rows (688,512 token-expert pairs).  The layer
+    works row by row, so packing must not matter: segments of every kind run on their own give the same rows bit
+    for bit, and a sample of rows agrees with the generic kernels."""
+    import numpy as np
+    import torch
+    from mference_b200 import _lib as L
+    from mference_b200.moe import synth_layer, synth_normal
+    d, f, E, K = 2048, 512, 256, 8
+    sizes = np.tile(np.asarray([1, 256, 512, 1024], dtype=np.int64), 48)
+    offsets = np.concatenate([[0], np.cumsum(sizes)])
+    T = int(offsets[-1])
+    assert T == 86064
+    layer = synth_layer(0xB2000001, 0, d, f, E)
+    x = synth_normal(0xB2000001, "x.ragged", T * d, dtype=L.DT_BF16).view(T, d)
+    y = _prefill_layer(d, f, E, K, T, 4, 4, True, x, layer)
+    assert bool(torch.isfinite(y.float()).all())
+    for seg in (0, 1, 2, 3, 4, len(sizes) - 1):          # a decode row, one chunk of each length, the next decode row, the last chunk
+        a, b = int(offsets[seg]), int(offsets[seg + 1])
+        y_seg = _prefill_layer(d, f, E, K, b - a, 4, 4, True, x[a:b].contiguous(), layer)
+        assert torch.equal(y_seg, y[a:b]), (seg, a, b)
+    sample = torch.arange(0, T, T // 48, device="cuda")[:48]
+    xs = x[sample].contiguous()
+    y_gen = _prefill_layer(d, f, E, K, xs.shape[0], 4, 4, False, xs, layer, generic=True)
+    err = float((y[sample].float() - y_gen.float()).norm() / y_gen.float().norm())
+    assert err <= TOL_REL_L2, err
