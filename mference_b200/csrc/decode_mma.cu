@@ -906,8 +906,11 @@ __device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer
 }
 
 // Counting sort of the routing table into shared memory, identical order to group.cu / route_small_kernel; every
-// CTA builds the same lists.  run_s is scratch of num_experts entries.  Warp 0 does the scans with shuffles.
-__device__ __forceinline__ void mega_group(const MegaParams& M, FastShared& S, const uint32_t* idx_s, const uint16_t* w_s,
+// CTA builds the same lists.  run_s (u32) and mask_s (u64) are scratch of num_experts entries; warp 0 does the scans.
+// Two forms with the same result.  The scan form places 32 pairs per round with one warp (cheap for a few dozen
+// pairs); the mask form places all pairs at once (several hundred pairs).  The kernel is instantiated once per form
+// (MASK_SORT) so that neither changes the other's code.
+__device__ __forceinline__ void mega_group_scan(const MegaParams& M, FastShared& S, const uint32_t* idx_s, const uint16_t* w_s,
                                            uint32_t* run_s, mfb_pair* sorted_s, mfb_group* groups_s, bool shared) {
     const uint32_t n_pairs = M.n_tokens * M.top_k, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) run_s[e] = 0;
@@ -965,7 +968,58 @@ __device__ __forceinline__ void mega_group(const MegaParams& M, FastShared& S, c
     __syncthreads();
 }
 
-template <int NGW>
+__device__ __forceinline__ void mega_group_mask(const MegaParams& M, FastShared& S, const uint32_t* idx_s, const uint16_t* w_s,
+                                           uint32_t* run_s, unsigned long long* mask_s, mfb_pair* sorted_s, mfb_group* groups_s,
+                                           bool shared) {
+    // A token selects an expert at most once and there are at most 64 tokens, so the rows of a group are a 64-bit
+    // token mask per expert: the count is its population count, a pair's place inside its group the number of set
+    // bits below its token.  That is the (token, rank) order of the stable sort, found without any serial scan.
+    const uint32_t n_pairs = M.n_tokens * M.top_k, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t e = threadIdx.x; e < M.num_experts; e += blockDim.x) mask_s[e] = 0ull;
+    __syncthreads();
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicOr(&mask_s[idx_s[p]], 1ull << (p / M.top_k));
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t per = (M.num_experts + 31) / 32, e0 = lane * per;
+        uint32_t cnt = 0, nz = 0;
+        for (uint32_t j = 0; j < per; ++j)
+            if (e0 + j < M.num_experts) { const uint32_t c = __popcll(mask_s[e0 + j]); cnt += c; nz += c ? 1u : 0u; }
+        uint32_t cnt_incl = cnt, nz_incl = nz;
+        for (uint32_t off = 1; off < 32; off <<= 1) {
+            const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, cnt_incl, off), b = __shfl_up_sync(0xFFFFFFFFu, nz_incl, off);
+            if (lane >= off) { cnt_incl += a; nz_incl += b; }
+        }
+        uint32_t run = cnt_incl - cnt, gi = nz_incl - nz;
+        for (uint32_t j = 0; j < per; ++j)
+            if (e0 + j < M.num_experts) {
+                const uint32_t c = __popcll(mask_s[e0 + j]);
+                run_s[e0 + j] = run;
+                if (c) { groups_s[gi].expert = e0 + j; groups_s[gi].pair_start = run; groups_s[gi].pair_count = c; ++gi; }
+                run += c;
+            }
+        uint32_t ng = __shfl_sync(0xFFFFFFFFu, nz_incl, 31);
+        if (lane == 0) {
+            if (shared) { groups_s[ng].expert = M.num_experts; groups_s[ng].pair_start = n_pairs; groups_s[ng].pair_count = M.n_tokens; ++ng; }
+            S.n_groups = ng;
+        }
+    } else if (shared) {
+        for (uint32_t t = threadIdx.x - 32; t < M.n_tokens; t += blockDim.x - 32) {
+            mfb_pair out;
+            out.token = t; out.expert = M.num_experts; out.rank = M.top_k; out.weight_bits = 0x3C00u;
+            sorted_s[n_pairs + t] = out;
+        }
+    }
+    __syncthreads();
+    for (uint32_t p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const uint32_t e = idx_s[p], t = p / M.top_k;
+        mfb_pair out;
+        out.token = t; out.expert = e; out.rank = p - t * M.top_k; out.weight_bits = w_s[p];
+        sorted_s[run_s[e] + __popcll(mask_s[e] & ((1ull << t) - 1ull))] = out;
+    }
+    __syncthreads();
+}
+
+template <int NGW, bool MASK_SORT>
 __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaParams M) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ FastShared S;
@@ -1089,7 +1143,8 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
                 w_s[p] = ld_cg_u16(M.route_w + p);
             }
             __syncthreads();
-            mega_group(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
+            if (MASK_SORT) mega_group_mask(M, S, idx_s, w_s, run_s, reinterpret_cast<unsigned long long*>(region_a), sorted_s, groups_s, shared);
+            else mega_group_scan(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
         const uint32_t n_groups = S.n_groups;
         if (warp == 0) {
@@ -1171,7 +1226,8 @@ size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
 template <int NGW>
 static cudaError_t fast_init_ngw() {
     cudaError_t e = cudaFuncSetAttribute(ffn_phase_kernel<2, NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     return e;
 }
 
@@ -1220,10 +1276,11 @@ cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe
     MegaParams copy = M;
     void* args[] = {&copy};
     const void* fn = nullptr;
+    const bool mask_sort = (uint64_t)M.n_tokens * c.top_k > 128;   // several rounds of the one-warp scan cost more than the all-threads form
     switch (c.d / 512) {
-        case 1: fn = (const void*)stack_mega_kernel<1>; break;
-        case 2: fn = (const void*)stack_mega_kernel<2>; break;
-        case 4: fn = (const void*)stack_mega_kernel<4>; break;
+        case 1: fn = mask_sort ? (const void*)stack_mega_kernel<1, true> : (const void*)stack_mega_kernel<1, false>; break;
+        case 2: fn = mask_sort ? (const void*)stack_mega_kernel<2, true> : (const void*)stack_mega_kernel<2, false>; break;
+        case 4: fn = mask_sort ? (const void*)stack_mega_kernel<4, true> : (const void*)stack_mega_kernel<4, false>; break;
         default: return cudaErrorInvalidValue;
     }
     e = cudaLaunchCooperativeKernel(fn, dim3((unsigned)sm_count), dim3(FAST_THREADS), args, fast_smem_stack(c, M.n_tokens), s);
