@@ -277,49 +277,68 @@ struct ScaleRow {
 // the units of each group, by one warp: pref1[g] counts phase-1 units, pref2[g] phase-2 units.
 //
 // Units do not cost the same: the MMA work of a unit is fixed, its epilogue grows with the token columns in use.
-// wpref[g] is the exclusive prefix of the groups' weights, a token tile with c columns weighing UNIT_BASE + c (per
-// row tile); the CTAs cut the unit list at equal weight rather than at equal count (unit_range).
-constexpr uint32_t UNIT_BASE = 6;
+// wpref1[g] / wpref2[g] are the exclusive prefixes of the groups' weights in phase 1 / phase 2, a token tile with c
+// columns weighing base + c (per row tile); the CTAs cut the unit list at equal weight rather than at equal count.
+// The bases are the measured ratios of a unit's fixed cost to its cost per token column (SM cycles in the running
+// pipeline: phase 1 about 4330 + 154 c, phase 2 about 2360 + 195 c).
+// With only a handful of units per CTA (small batches) the cut points matter less than their granularity, and
+// the flatter weights measured slower there: those launches keep a base of 6 for both phases.
+struct UnitBases { uint32_t b1, b2; };
+__device__ __forceinline__ UnitBases unit_bases(bool large_batch) { return large_batch ? UnitBases{28u, 12u} : UnitBases{6u, 6u}; }
 
-__device__ __forceinline__ uint32_t group_weight(uint32_t pair_count) {
+__device__ __forceinline__ uint32_t group_weight(uint32_t pair_count, uint32_t base) {
     const uint32_t full = pair_count / 8, rem = pair_count % 8;
-    return full * (UNIT_BASE + 8) + (rem ? UNIT_BASE + rem : 0);
+    return full * (base + 8) + (rem ? base + rem : 0);
 }
 
+template <bool TWO>   // TWO = false: one weight model for both phases (b1), wpref2 is not written
 __device__ __forceinline__ void warp_unit_prefix2(const mfb_group* groups, uint32_t n_groups, uint32_t tiles1, uint32_t tiles2,
-                                                  uint32_t* pref1, uint32_t* pref2, uint32_t* wpref, uint32_t lane) {
+                                                  uint32_t* pref1, uint32_t* pref2, uint32_t* wpref1, uint32_t* wpref2,
+                                                  UnitBases ub, uint32_t lane) {
     const uint32_t per = (n_groups + 31) / 32, g0 = lane * per;
-    uint32_t local = 0, wlocal = 0;
+    uint32_t local = 0, w1local = 0, w2local = 0;
     for (uint32_t j = 0; j < per; ++j)
         if (g0 + j < n_groups) {
             const uint32_t c = groups[g0 + j].pair_count;
             local += (c + 7) / 8;
-            wlocal += group_weight(c);
+            w1local += group_weight(c, ub.b1);
+            if (TWO) w2local += group_weight(c, ub.b2);
         }
-    uint32_t incl = local, wincl = wlocal;
+    uint32_t incl = local, w1incl = w1local, w2incl = w2local;
     for (uint32_t off = 1; off < 32; off <<= 1) {
-        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off), wn = __shfl_up_sync(0xFFFFFFFFu, wincl, off);
-        if (lane >= off) { incl += n; wincl += wn; }
+        const uint32_t n = __shfl_up_sync(0xFFFFFFFFu, incl, off), a = __shfl_up_sync(0xFFFFFFFFu, w1incl, off);
+        if (lane >= off) { incl += n; w1incl += a; }
+        if (TWO) {
+            const uint32_t b = __shfl_up_sync(0xFFFFFFFFu, w2incl, off);
+            if (lane >= off) w2incl += b;
+        }
     }
-    uint32_t run = incl - local, wrun = wincl - wlocal;
+    uint32_t run = incl - local, w1run = w1incl - w1local, w2run = w2incl - w2local;
     for (uint32_t j = 0; j < per; ++j)
         if (g0 + j < n_groups) {
             const uint32_t c = groups[g0 + j].pair_count;
             pref1[g0 + j] = run * tiles1;
             pref2[g0 + j] = run * tiles2;
-            wpref[g0 + j] = wrun;
+            wpref1[g0 + j] = w1run;
+            if (TWO) wpref2[g0 + j] = w2run;
             run += (c + 7) / 8;
-            wrun += group_weight(c);
+            w1run += group_weight(c, ub.b1);
+            if (TWO) w2run += group_weight(c, ub.b2);
         }
-    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), wtotal = __shfl_sync(0xFFFFFFFFu, wincl, 31);
-    if (lane == 0) { pref1[n_groups] = total * tiles1; pref2[n_groups] = total * tiles2; wpref[n_groups] = wtotal; }
+    const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31), w1total = __shfl_sync(0xFFFFFFFFu, w1incl, 31);
+    if (lane == 0) { pref1[n_groups] = total * tiles1; pref2[n_groups] = total * tiles2; wpref1[n_groups] = w1total; }
+    if (TWO) {
+        const uint32_t w2total = __shfl_sync(0xFFFFFFFFu, w2incl, 31);
+        if (lane == 0) wpref2[n_groups] = w2total;
+    }
     __syncwarp();
 }
 
 // First unit at or after weight position `cut` of `parts` equal cuts of the phase's total weight.  32-bit arithmetic
-// suffices: at most 64 tokens x (top_k + 1) pairs of weight <= UNIT_BASE + 1 each, times tiles, times parts.
+// suffices: at most 64 tokens x (top_k + 1) pairs of weight <= base + 1 each, times tiles, times parts.
 __device__ __forceinline__ uint32_t unit_at_cut(const mfb_group* groups, uint32_t n_groups, const uint32_t* pref,
-                                                const uint32_t* wpref, uint32_t tiles, uint32_t cut, uint32_t parts) {
+                                                const uint32_t* wpref, uint32_t tiles, uint32_t base, uint32_t cut,
+                                                uint32_t parts) {
     if (cut >= parts) return pref[n_groups];
     const uint32_t target = wpref[n_groups] * tiles * cut / parts;   // weight in front of the unit looked for
     uint32_t lo = 0, hi = n_groups;   // last group whose prefix (times tiles) is <= target
@@ -329,10 +348,10 @@ __device__ __forceinline__ uint32_t unit_at_cut(const mfb_group* groups, uint32_
     }
     uint32_t rem = target - wpref[lo] * tiles;
     const uint32_t count = groups[lo].pair_count, full = count / 8, r = count % 8;
-    const uint32_t full_block = tiles * (UNIT_BASE + 8);
+    const uint32_t full_block = tiles * (base + 8);
     const uint32_t tt = min(full, rem / full_block);
     rem -= tt * full_block;
-    const uint32_t w = tt < full ? UNIT_BASE + 8 : UNIT_BASE + r;
+    const uint32_t w = tt < full ? base + 8 : base + r;
     return pref[lo] + tt * tiles + min(rem / w, tiles - 1);
 }
 
@@ -659,7 +678,7 @@ __device__ __forceinline__ void combine_slice(const FastParams& P, uint32_t begi
 // ------------------------------------------------------------------------------------------ separate kernels
 struct FastShared {
     uint64_t full1[MAX_STAGES], empty1[MAX_STAGES], full2[MAX_STAGES], empty2[MAX_STAGES];
-    uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1], wpref[MAX_GROUPS + 1];
+    uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1], wpref1[MAX_GROUPS + 1];
     uint32_t range[4];   // this CTA's [first, last) units of phase 1 and of phase 2
     uint32_t flag, n_groups;
     float red[32];
@@ -678,11 +697,13 @@ __device__ __forceinline__ void init_barriers(FastShared& S) {
 
 // This CTA's contiguous share of each phase's units: cuts at equal weight (see warp_unit_prefix2).  Called by warp 0
 // right after the prefix sums; lanes 0..3 each find one of the four cut points.
+template <bool TWO>   // wpref2: scratch of MAX_GROUPS + 1 entries, dead once the ranges are found (used when TWO)
 __device__ __forceinline__ void warp_unit_ranges(FastShared& S, const mfb_group* groups, uint32_t n_groups, uint32_t tiles1,
-                                                 uint32_t tiles2, uint32_t lane) {
+                                                 uint32_t tiles2, UnitBases ub, const uint32_t* wpref2, uint32_t lane) {
     if (lane < 4)
-        S.range[lane] = unit_at_cut(groups, n_groups, lane < 2 ? S.pref1 : S.pref2, S.wpref, lane < 2 ? tiles1 : tiles2,
-                                    blockIdx.x + (lane & 1u), gridDim.x);
+        S.range[lane] = unit_at_cut(groups, n_groups, lane < 2 ? S.pref1 : S.pref2, (lane < 2 || !TWO) ? S.wpref1 : wpref2,
+                                    lane < 2 ? tiles1 : tiles2, (lane < 2 || !TWO) ? ub.b1 : ub.b2, blockIdx.x + (lane & 1u),
+                                    gridDim.x);
 }
 
 // Phase 1 (NMAT = 2) or phase 2 (NMAT = 1) over the groups of one layer call, as a kernel of its own.
@@ -697,13 +718,15 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) ffn_phase_kernel(const FastPa
     init_barriers(S);
     const uint32_t n_groups = *P.n_groups;
     if (warp == 0) {
-        warp_unit_prefix2(P.groups, n_groups, geo.tiles, geo.tiles, S.pref1, S.pref2, S.wpref, lane);
-        warp_unit_ranges(S, P.groups, n_groups, geo.tiles, geo.tiles, lane);
+        const UnitBases ub = unit_bases(P.n_tokens > 16);
+        uint32_t* wpref2 = reinterpret_cast<uint32_t*>(smem);   // the stage ring is not in use yet
+        warp_unit_prefix2<true>(P.groups, n_groups, geo.tiles, geo.tiles, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
+        warp_unit_ranges<true>(S, P.groups, n_groups, geo.tiles, geo.tiles, ub, wpref2, lane);
     }
     __syncthreads();
     PhaseCtx C{smem, S.full1, S.empty1, reinterpret_cast<float*>(smem + RING_BYTES), S.pref1};
     uint32_t seq = 0;
-    const uint32_t first = S.range[0], last = S.range[1];
+    const uint32_t first = S.range[NMAT == 2 ? 0 : 2], last = S.range[NMAT == 2 ? 1 : 3];   // cut with this phase's weights
     if (!run_phase<NMAT, NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
 }
 
@@ -909,7 +932,7 @@ __device__ __forceinline__ void mega_logits(const MegaParams& M, const MegaLayer
 // CTA builds the same lists.  run_s (u32) and mask_s (u64) are scratch of num_experts entries; warp 0 does the scans.
 // Two forms with the same result.  The scan form places 32 pairs per round with one warp (cheap for a few dozen
 // pairs); the mask form places all pairs at once (several hundred pairs).  The kernel is instantiated once per form
-// (MASK_SORT) so that neither changes the other's code.
+// (LARGE_BATCH) so that neither changes the other's code.
 __device__ __forceinline__ void mega_group_scan(const MegaParams& M, FastShared& S, const uint32_t* idx_s, const uint16_t* w_s,
                                            uint32_t* run_s, mfb_pair* sorted_s, mfb_group* groups_s, bool shared) {
     const uint32_t n_pairs = M.n_tokens * M.top_k, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1019,7 +1042,7 @@ __device__ __forceinline__ void mega_group_mask(const MegaParams& M, FastShared&
     __syncthreads();
 }
 
-template <int NGW, bool MASK_SORT>
+template <int NGW, bool LARGE_BATCH>
 __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaParams M) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ FastShared S;
@@ -1143,13 +1166,15 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
                 w_s[p] = ld_cg_u16(M.route_w + p);
             }
             __syncthreads();
-            if (MASK_SORT) mega_group_mask(M, S, idx_s, w_s, run_s, reinterpret_cast<unsigned long long*>(region_a), sorted_s, groups_s, shared);
+            if (LARGE_BATCH) mega_group_mask(M, S, idx_s, w_s, run_s, reinterpret_cast<unsigned long long*>(region_a), sorted_s, groups_s, shared);
             else mega_group_scan(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
         const uint32_t n_groups = S.n_groups;
         if (warp == 0) {
-            warp_unit_prefix2(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, S.wpref, lane);
-            warp_unit_ranges(S, groups_s, n_groups, geo1.tiles, geo2.tiles, lane);
+            const UnitBases ub = unit_bases(LARGE_BATCH);
+            uint32_t* wpref2 = reinterpret_cast<uint32_t*>(region_a);   // the stage ring is not in use yet
+            warp_unit_prefix2<LARGE_BATCH>(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
+            warp_unit_ranges<LARGE_BATCH>(S, groups_s, n_groups, geo1.tiles, geo2.tiles, ub, wpref2, lane);
         }
         __syncthreads();
 
@@ -1276,7 +1301,7 @@ cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe
     MegaParams copy = M;
     void* args[] = {&copy};
     const void* fn = nullptr;
-    const bool mask_sort = (uint64_t)M.n_tokens * c.top_k > 128;   // several rounds of the one-warp scan cost more than the all-threads form
+    const bool mask_sort = M.n_tokens > 16;   // several rounds of the one-warp scan cost more than the all-threads form; also selects the unit weights
     switch (c.d / 512) {
         case 1: fn = mask_sort ? (const void*)stack_mega_kernel<1, true> : (const void*)stack_mega_kernel<1, false>; break;
         case 2: fn = mask_sort ? (const void*)stack_mega_kernel<2, true> : (const void*)stack_mega_kernel<2, false>; break;
