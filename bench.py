@@ -44,7 +44,7 @@ ROOT_SEED = 0xB2000001
 N_INPUTS = 4          # distinct input sets cycled through the steps
 # DRAM bytes (read + write) of one stack_mega_kernel launch from an ncu capture, keyed by (batch, rows, layers); the
 # capture of a 2-layer case is scaled by the layer count since every layer reads its own weights once
-TRAFFIC_PER_LAUNCH: dict = {(64, "fresh", 2): 820.7e6, (64, "fresh", 40): 820.7e6 / 2 * 40}
+TRAFFIC_PER_LAYER: dict = {}
 
 
 def measured_peaks():
@@ -110,9 +110,9 @@ def layer_bytes(unique_experts: int, n_tokens: int, blob: int) -> int:
 
 def cpu_port_tokens_per_s(batch: int, budget_s: float, layers: int = LAYERS):
     """Times the CPU port of the reference's scalar decode path (oracle/mfb_oracle.c: mfbo_ref_moe_layer_f32 plus the
-    router) on this box's host cores, on ONE layer of the stack, and scales by the layer count."""
+    router) on this box's host cores, on ONE layer of the stack over the whole batch, and scales by the layer count."""
     from oracle import oracle as O
-    rows = min(batch, 8)
+    rows = batch
     W0 = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=[])
     x = O.fill_normal(O.seed_for_label(ROOT_SEED, "x"), rows * D, dtype=O.DT_BF16).reshape(rows, D)
     lg = O.router_logits(x, O.DT_BF16, W0.router)
@@ -134,10 +134,50 @@ def cpu_port_tokens_per_s(batch: int, budget_s: float, layers: int = LAYERS):
     return tok_s, O.num_threads(), f"1 of {layers} layers x {rows} token rows x {reps} repeats, scaled x{layers}"
 
 
+def cpu_port_prefill_tokens_per_s(sample_rows: int, budget_s: float, zipf: bool):
+    """CPU port of the reference's scalar prefill path on a sample of the batch's rows: router, grouping by expert,
+    the per-pair scalar int4 loop (oracle mfbo_pair_partials, the restatement of the reference's test-local loop) and
+    the token-major weighted reduce.  Tokens/s of the sample; the cost per token row does not depend on the batch."""
+    import numpy as np
+    from oracle import oracle as O
+    T = sample_rows
+    W0 = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=[])
+    x = O.fill_normal(O.seed_for_label(ROOT_SEED, "x.prefill.cpu"), T * D, dtype=O.DT_BF16).reshape(T, D)
+    bias = zipf_logit_bias(E) if zipf else None
+    lg = O.router_logits(x, O.DT_BF16, W0.router, logit_bias=bias)
+    idx, w = O.topk_softmax(lg, K)
+    W = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=sorted(set(idx.reshape(-1).tolist())))
+    pairs = np.zeros(T * K, dtype=O.PAIR_DTYPE)
+    pairs["token"] = np.repeat(np.arange(T), K)
+    pairs["expert"] = idx.reshape(-1)
+    pairs["rank"] = np.tile(np.arange(K), T)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        lg = O.router_logits(x, O.DT_BF16, W.router, logit_bias=bias)
+        idx2, w2 = O.topk_softmax(lg, K)
+        g = O.group_pairs(pairs, T, K, E)
+        part = O.pair_partials(W, x, O.DT_BF16, g["sorted_pairs"])
+        full = np.empty((T * K, D), dtype=np.float32)
+        sp = g["sorted_pairs"]
+        full[sp["token"] * K + sp["rank"]] = part
+        O.reduce_token_major(full.reshape(T, K, D), w2, T, K, D)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or reps >= 200:
+            break
+    return T * reps / dt, O.num_threads(), f"{T} token rows ({T * K} pairs) of one layer x {reps} repeats; tokens/s of the sample"
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # under torchrun every rank is given OMP_NUM_THREADS=1; this arm is rank 0 alone and uses every host core
+    try:
+        from oracle import oracle as O
+        O.set_num_threads(os.cpu_count() or 1)
+    except Exception:
+        pass
     steps, warm = max(args.steps, 1), args.warmup
     budget = max(1.0, min(15.0, 90.0 / (steps + warm)))
     vals = []
@@ -147,14 +187,17 @@ def run_reference(args):
         if i >= warm:
             vals.append(tok_s)
     v = statistics.mean(vals)
-    rows = min(args.batch, 8)
+    rows = args.batch
     print(json.dumps({
         "impl": "reference", "metric": "moe_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": 1e3 * rows / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"configs[1]: {args.layers}-layer Qwen3.6-A3B MoE FFN stack, decode batch {rows} (CPU port)",
+        "config": {"workload": f"configs[1]: {args.layers}-layer Qwen3.6-A3B MoE FFN stack, decode batch {rows}, {args.rows} rows",
+                   "hidden": D, "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4,
+                   "group_size": 64, "layers": args.layers, "batch_per_gpu": rows,
                    "note": "the reference is Swift + Metal and cannot be built here; this arm is the C port of its scalar "
-                           "path (oracle/mfb_oracle.c) on the host cores"},
+                           "path (oracle/mfb_oracle.c) on the host cores, one layer timed per step and scaled by the "
+                           "layer count; its tokens/s does not depend on how rows are chained between layers"},
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -162,11 +205,192 @@ def run_reference(args):
 
 # ----------------------------------------------------------------------------------------------- GPU arm
 
+class DecodeBench:
+    """The resident 40-layer pool and the decode measurements over it (configs[1])."""
+
+    def __init__(self, args, world, rank, local):
+        from mference_b200 import _lib as L
+        from mference_b200.moe import expert_layout, synth_layer
+        self.args, self.world, self.rank, self.local = args, world, rank, local
+        self.L, self.lib = L, L.load()
+        self.NL = args.layers
+        _, self.blob = expert_layout(4, D, F)
+        self.layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(self.NL)]
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(self, B, rows, steps, warmup, *, launch="fused", trace=False, cpu_budget=10.0, sampler=None):
+        """One decode configuration: batch B, rows 'fresh' | 'chained'.  Returns the record of the measurement."""
+        import torch
+        import torch.distributed as dist
+        from mference_b200.moe import MoE, synth_normal
+        L, lib, NL, layers, world, rank = self.L, self.lib, self.NL, self.layers, self.world, self.rank
+        fresh = rows == "fresh"
+        moe = MoE(D, F, E, K, max_tokens=B, max_layers=max(NL, 1))
+        if launch == "layers":
+            moe.set_generic(2)
+        stack = moe.make_stack(layers)
+        n_sets = N_INPUTS
+        shape = (NL, B, D) if fresh else (B, D)
+        inputs = [synth_normal(ROOT_SEED + rank, f"x.{B}.{i}", (NL if fresh else 1) * B * D, dtype=L.DT_BF16).view(*shape)
+                  for i in range(n_sets)]
+        torch.cuda.synchronize()
+
+        # distinct experts per layer for each input set (untimed; same kernels, layer by layer)
+        step_bytes = []
+        idx = torch.empty((B, K), dtype=torch.int32, device="cuda")
+        w = torch.empty((B, K), dtype=torch.float16, device="cuda")
+        for h0 in inputs:
+            total = 0
+            h = None if fresh else h0.clone()
+            for l, lw in enumerate(layers):
+                src = h0[l] if fresh else h
+                xn = torch.empty_like(src)
+                moe.encode_rmsnorm(src, xn, lw.norm_w)
+                moe.encode_router(xn, lw, idx, w)
+                total += layer_bytes(int(torch.unique(idx).numel()), B, self.blob)
+                if not fresh:
+                    nxt = torch.empty_like(h)
+                    moe.encode_decode(lw, xn, idx, w, nxt, residual=h)
+                    h = nxt
+            step_bytes.append(total)
+        torch.cuda.synchronize()
+        work = [torch.empty_like(t) for t in inputs]
+        kev = []   # (start, end) events around the stack call alone
+
+        def step(i, src=None, timed=False):
+            buf = work[i % n_sets]
+            if src is None:
+                buf.copy_(inputs[i % n_sets])
+            if timed:
+                kev.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+                kev[-1][0].record()
+            if fresh:
+                moe.encode_stack_rows(stack, buf)    # layer l on rows buf[l]; strictly one layer after the other
+            else:
+                moe.encode_stack(stack, buf)
+            if timed:
+                kev[-1][1].record()
+            return buf
+
+        for i in range(warmup):
+            step(i)
+        self.barrier()
+        if sampler is not None:
+            sampler.start()
+        launches0 = lib.mfb_launch_count()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        self.barrier()
+        ev[0].record()
+        for i in range(steps):
+            step(i, timed=True)
+            ev[i + 1].record()
+        self.barrier()
+        launches = lib.mfb_launch_count() - launches0
+        total_ms = ev[0].elapsed_time(ev[-1])
+        stack_ms = [a.elapsed_time(b) for a, b in kev]   # the pass alone, without the refresh of its input rows
+
+        # end to end through the C ABI with host buffers
+        host_in = [t.cpu().pin_memory() for t in inputs]
+        host_out = torch.empty_like(host_in[0]).pin_memory()
+        for i in range(3):
+            work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
+            host_out.copy_(step(i, src="host"), non_blocking=True)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
+            host_out.copy_(step(i, src="host"), non_blocking=True)
+            torch.cuda.current_stream().synchronize()   # the caller reads the result before the next step
+        e1.record()
+        self.barrier()
+        clocks = sampler.stop() if sampler is not None else None
+        e2e_ms = e0.elapsed_time(e1)
+        status = moe.device_status()   # a bounded wait that ran out would have unwound the launch early: not a valid timing
+
+        # untimed check of one step's result against the layer-by-layer launches of the same layers (bit for bit)
+        check = inputs[0].clone()
+        if fresh:
+            moe.encode_stack_rows(stack, check)
+        else:
+            moe.encode_stack(stack, check)
+        ref = inputs[0].clone()
+        for l, lw in enumerate(layers):
+            if fresh:
+                moe.encode_layer(lw, ref[l], ref[l])
+            else:
+                moe.encode_layer(lw, ref, ref)
+        output_ok = bool(torch.equal(check.view(torch.int16), ref.view(torch.int16))) and bool(torch.isfinite(check.float()).all())
+        status |= moe.device_status()
+
+        phase_us = None
+        if trace and launch == "fused":
+            tr = torch.zeros((NL + 17, 8), dtype=torch.int64, device="cuda")
+            moe.set_trace(tr)
+            step(0)
+            moe.set_trace(None)
+            torch.cuda.synchronize()
+            st = tr[:NL].cpu().numpy().astype("float64")
+            names = ["norm", "logits", "select", "sort", "phase1", "barrier", "phase2"]
+            phase_us = {n: round(float((st[:, i + 1] - st[:, i]).mean() / 1e3), 2) for i, n in enumerate(names)}
+            if NL > 1:
+                phase_us["combine_to_next_layer"] = round(float((st[1:, 0] - st[:-1, 7]).mean() / 1e3), 2)
+                phase_us["layer_period"] = round(float((st[1:, 0] - st[:-1, 0]).mean() / 1e3), 2)
+            # SM-cycle counters of CTA 0, per layer: a computing warp's wait for a stage and its work on it, per FFN
+            # phase; the copy-issuing warp's time spent issuing (mostly waiting for a free stage)
+            cyc = tr[NL:NL + 17].cpu().numpy().astype("float64") / NL
+            phase_us["cta0_kcycles_per_layer"] = {
+                "phase1_wait": round(float(cyc[:8, 0].mean() / 1e3), 2), "phase1_compute": round(float(cyc[:8, 1].mean() / 1e3), 2),
+                "phase2_wait": round(float(cyc[:8, 2].mean() / 1e3), 2), "phase2_compute": round(float(cyc[:8, 3].mean() / 1e3), 2),
+                "phase1_copy_issue": round(float(cyc[8, 0] / 1e3), 2), "phase2_copy_issue": round(float(cyc[8, 2] / 1e3), 2)}
+
+        times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = float(times[0]), float(times[1])
+        hbm_peak, _, peak_kind = measured_peaks()
+        bytes_per_step = statistics.mean(step_bytes[i % n_sets] for i in range(steps))
+        launch_ms = statistics.mean(stack_ms)
+        achieved = bytes_per_step / (launch_ms * 1e-3) / 1e9
+        fused = launch == "fused"
+        traffic = None
+        if fused and (B, rows) in TRAFFIC_PER_LAYER:   # ncu capture of a 2-layer case of this build, scaled by the layer count
+            traffic = TRAFFIC_PER_LAYER[(B, rows)] * NL
+        rec = {
+            "value": world * B * steps / (total_ms * 1e-3), "unit": "tokens/s", "ms_per_step": total_ms / steps,
+            "batch_per_gpu": B, "rows": rows,
+            "distinct_experts_per_layer": round((bytes_per_step / NL - self.blob - E * D * 2 - B * D * 4) / self.blob, 1),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "peak_kind": peak_kind, "traffic": traffic,
+                         "kernel": "stack_mega_kernel (one cooperative launch = the whole pass)" if fused
+                                   else "all kernels of the pass, launched layer by layer",
+                         "launch_ms": launch_ms, "algorithmic_bytes_per_launch": bytes_per_step},
+            "e2e": {"value": world * B * steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": inputs[0].numel() * 2, "d2h_bytes_per_step": inputs[0].numel() * 2},
+            "gpu_launches": int(launches), "device_status": int(status), "output_matches_layer_by_layer": output_ok,
+            "clocks": clocks, "l2": f"inputs larger than L2: {bytes_per_step / 1e6:.0f} MB of distinct weight bytes per step, "
+                                    f"{n_sets} input sets cycled",
+        }
+        if phase_us is not None:
+            rec["phase_us"] = phase_us
+        if cpu_budget and rank == 0:
+            tok_s, cores, sample = cpu_port_tokens_per_s(B, cpu_budget, NL)
+            rec["cpu_baseline"] = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        else:
+            rec["cpu_baseline"] = None
+        moe.close()
+        return rec
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from mference_b200 import _lib as L
-    from mference_b200.moe import MoE, expert_layout, synth_layer, synth_normal
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -174,143 +398,59 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lib = L.load()
+    bench = DecodeBench(args, world, rank, local)
     B, NL = args.batch, args.layers
-    fresh = args.rows == "fresh"
-    _, blob = expert_layout(4, D, F)
-
-    layers = [synth_layer(ROOT_SEED, l, D, F, E) for l in range(NL)]
-    moe = MoE(D, F, E, K, max_tokens=B)
-    if args.launch == "layers":
-        moe.set_generic(2)
-    stack = moe.make_stack(layers)
-    n_sets = N_INPUTS
-    if fresh:   # one [NL, B, D] set of independent rows per input set
-        inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", NL * B * D, dtype=L.DT_BF16).view(NL, B, D) for i in range(n_sets)]
-    else:
-        inputs = [synth_normal(ROOT_SEED + rank, f"x.{i}", B * D, dtype=L.DT_BF16).view(B, D) for i in range(n_sets)]
-    torch.cuda.synchronize()
-
-    # distinct experts per layer for each input set (untimed; same kernels, layer by layer)
-    step_bytes = []
-    idx = torch.empty((B, K), dtype=torch.int32, device="cuda")
-    w = torch.empty((B, K), dtype=torch.float16, device="cuda")
-    for h0 in inputs:
-        total = 0
-        h = None if fresh else h0.clone()
-        for l, lw in enumerate(layers):
-            src = h0[l] if fresh else h
-            xn = torch.empty_like(src)
-            moe.encode_rmsnorm(src, xn, lw.norm_w)
-            moe.encode_router(xn, lw, idx, w)
-            total += layer_bytes(int(torch.unique(idx).numel()), B, blob)
-            if not fresh:
-                nxt = torch.empty_like(h)
-                moe.encode_decode(lw, xn, idx, w, nxt, residual=h)
-                h = nxt
-        step_bytes.append(total)
-    torch.cuda.synchronize()
-    work = [torch.empty_like(t) for t in inputs]
-
-    kev = []   # (start, end) events around the stack call alone
-
-    def step(i, src=None, timed=False):
-        buf = work[i % n_sets]
-        if src is None:
-            buf.copy_(inputs[i % n_sets])
-        if timed:
-            kev.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
-            kev[-1][0].record()
-        if fresh:
-            moe.encode_stack_rows(stack, buf)    # layer l on rows buf[l]; strictly one layer after the other
-        else:
-            moe.encode_stack(stack, buf)
-        if timed:
-            kev[-1][1].record()
-        return buf
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    launches0 = lib.mfb_launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    barrier()
-    ev[0].record()
-    for i in range(args.steps):
-        step(i, timed=True)
-        ev[i + 1].record()
-    barrier()
-    launches = lib.mfb_launch_count() - launches0
-    total_ms = ev[0].elapsed_time(ev[-1])
-    stack_ms = [a.elapsed_time(b) for a, b in kev]   # the pass alone, without the refresh of its input rows
-
-    # end to end through the C ABI with host buffers
-    host_in = [t.cpu().pin_memory() for t in inputs]
-    host_out = torch.empty_like(host_in[0]).pin_memory()
-    for i in range(3):
-        work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
-        host_out.copy_(step(i, src="host"), non_blocking=True)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        work[i % n_sets].copy_(host_in[i % n_sets], non_blocking=True)
-        host_out.copy_(step(i, src="host"), non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller reads the result before the next step
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    e2e_ms = e0.elapsed_time(e1)
-
-    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = float(times[0]), float(times[1])
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    ms_per_step = total_ms / args.steps
-    value = world * B * args.steps / (total_ms * 1e-3)
-    e2e = world * B * args.steps / (e2e_ms * 1e-3)
-    hbm_peak, _, peak_kind = measured_peaks()
-    bytes_per_step = statistics.mean(step_bytes[i % n_sets] for i in range(args.steps))
-    achieved = bytes_per_step / (statistics.mean(stack_ms) * 1e-3) / 1e9
-    fused = args.launch == "fused"
-    cpu_tok_s, cores, sample = cpu_port_tokens_per_s(B, 10.0, NL)
-    io_bytes = inputs[0].numel() * 2
+    head = bench.run(B, args.rows, args.steps, args.warmup, launch=args.launch, trace=args.trace, cpu_budget=10.0,
+                     sampler=ClockSampler(local))
+    bad = head["device_status"] != 0 or not head["output_matches_layer_by_layer"]
     out = {
-        "metric": "moe_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "metric": "moe_decode_tokens_per_s", "value": head["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"configs[1]: {NL}-layer Qwen3.6-A3B MoE FFN stack, decode batch {B}, {args.rows} rows",
                    "hidden": D, "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4,
                    "group_size": 64, "layers": NL, "batch_per_gpu": B, "rows": args.rows, "activation_dtype": "bf16",
                    "accumulate": "f32", "parallelism": "replicas" if world > 1 else "single",
-                   "distinct_experts_per_layer": round((bytes_per_step / NL - blob - E * D * 2 - B * D * 4) / blob, 1),
-                   "l2": f"inputs larger than L2: {bytes_per_step / 1e6:.0f} MB of distinct weight bytes per step, "
-                         f"{n_sets} input sets cycled"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "peak_kind": peak_kind, "traffic": TRAFFIC_PER_LAUNCH.get((B, args.rows, NL)) if fused else None,
-                     "kernel": "stack_mega_kernel (one cooperative launch = the whole pass)" if fused
-                               else "all kernels of the pass, launched layer by layer",
-                     "launch_ms": statistics.mean(stack_ms), "algorithmic_bytes_per_launch": bytes_per_step},
-        "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
+                   "distinct_experts_per_layer": head["distinct_experts_per_layer"], "l2": head["l2"]},
+        "roofline": head["roofline"], "cpu_baseline": head["cpu_baseline"], "e2e": head["e2e"],
+        "gpu_launches": head["gpu_launches"], "device_status": head["device_status"],
+        "output_matches_layer_by_layer": head["output_matches_layer_by_layer"], "clocks": head["clocks"],
     }
-    print(json.dumps(out))
+    if "phase_us" in head:
+        out["phase_us"] = head["phase_us"]
+
+    if args.extras and args.launch == "fused":
+        extras = {}
+        if world == 1:
+            # the rest of the metric in the same run: the other decode batches of configs[1], configs[2] and configs[4]
+            for name, (b, rows, steps) in {"decode_b1": (1, "chained", 50), "decode_b8": (8, "fresh", 30),
+                                           "decode_b64_chained": (64, "chained", 30)}.items():
+                if (b, rows) == (B, args.rows):
+                    continue
+                rec = bench.run(b, rows, steps, 3, trace=args.trace, cpu_budget=4.0)
+                rec["metric"], rec["workload"] = "moe_decode_tokens_per_s", f"configs[1]: decode batch {b}, {rows} rows"
+                bad |= rec["device_status"] != 0 or not rec["output_matches_layer_by_layer"]
+                extras[name] = rec
+            layer0 = bench.layers[0]
+            del bench.layers[1:]          # the prefill workloads use one layer: release the rest of the pool
+            torch.cuda.empty_cache()
+            extras["prefill"] = prefill_case("prefill", 4096, 20, 3, layer0, cpu_budget=5.0)
+            extras["ragged"] = prefill_case("ragged", 0, 5, 3, layer0, cpu_budget=0.0)
+            extras["ragged"]["cpu_baseline"] = dict(extras["prefill"]["cpu_baseline"] or {}) or None
+            if extras["ragged"]["cpu_baseline"]:
+                extras["ragged"]["cpu_baseline"]["sample"] += " (the sample of the prefill workload: same layer, same cost per token row)"
+            bad |= any(extras[k]["device_status"] != 0 for k in ("prefill", "ragged"))
+        else:
+            del bench.layers[:]
+            torch.cuda.empty_cache()
+            extras["ep"] = ep_case(world, rank, local, 10, 3)
+        out["extras"] = extras
+    if rank == 0:
+        print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+    if bad:
+        sys.exit("bench: a device status word was set or an output check failed")
 
 
 def zipf_logit_bias(num_experts: int, exponent: float = 1.1):
@@ -332,24 +472,24 @@ def ragged_mix_offsets():
     return np.concatenate([[0], np.cumsum(sizes)])
 
 
-def run_prefill(args):
-    """configs[2]: T token rows through one Q layer - RMSNorm, router with a Zipf(1.1) logit bias, sort by expert, the
-    ragged grouped GEMM on the tensor cores (routed experts + the shared expert), weighted reduce + residual."""
+def prefill_case(workload, tokens, steps, warmup, layer=None, cpu_budget=5.0, sampler=None):
+    """configs[2] ('prefill': `tokens` rows, Zipf(1.1) logit bias) or configs[4] ('ragged': the 86,064-row mix, unbiased
+    router) through one Q layer - RMSNorm, router, sort by expert, the ragged grouped GEMM on the tensor cores (routed
+    experts + the shared expert), weighted reduce + residual.  Returns the record of the measurement."""
+    import copy
     import torch
     from mference_b200 import _lib as L
     from mference_b200.moe import MoE, synth_layer, synth_normal
 
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     lib = L.load()
-    ragged = args.workload == "ragged"
+    ragged = workload == "ragged"
     offsets = ragged_mix_offsets() if ragged else None
-    T = int(offsets[-1]) if ragged else args.tokens
-    layer = synth_layer(ROOT_SEED, 0, D, F, E)
-    if not ragged:
-        layer.logit_bias = torch.from_numpy(zipf_logit_bias(E)).cuda()
+    T = int(offsets[-1]) if ragged else tokens
+    layer = copy.copy(layer) if layer is not None else synth_layer(ROOT_SEED, 0, D, F, E)
+    layer.logit_bias = None if ragged else torch.from_numpy(zipf_logit_bias(E)).cuda()
     moe = MoE(D, F, E, K, max_tokens=T, tensor_core_prefill=True)
     n_sets = N_INPUTS
-    inputs = [synth_normal(ROOT_SEED, f"x.prefill.{i}", T * D, dtype=L.DT_BF16).view(T, D) for i in range(n_sets)]
+    inputs = [synth_normal(ROOT_SEED, f"x.{workload}.{i}", T * D, dtype=L.DT_BF16).view(T, D) for i in range(n_sets)]
     out = torch.empty_like(inputs[0])
     # group sizes of the first input set (untimed)
     idx = torch.empty((T, K), dtype=torch.int32, device="cuda")
@@ -363,15 +503,15 @@ def run_prefill(args):
     def step(i):
         moe.encode_layer_prefill(layer, inputs[i % n_sets], out)
 
-    for i in range(args.warmup):
+    for i in range(warmup):
         step(i)
     torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
+    if sampler is not None:
+        sampler.start()
     launches0 = lib.mfb_launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     ev[0].record()
-    for i in range(args.steps):
+    for i in range(steps):
         step(i)
         ev[i + 1].record()
     torch.cuda.synchronize()
@@ -384,42 +524,68 @@ def run_prefill(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
-    for i in range(args.steps):
+    for i in range(steps):
         dev_in.copy_(host_in[i % n_sets], non_blocking=True)
         moe.encode_layer_prefill(layer, dev_in, out)
         host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    clocks = sampler.stop() if sampler is not None else None
     e2e_ms = e0.elapsed_time(e1)
     status = moe.device_status()
 
-    ms = total_ms / args.steps
+    ms = total_ms / steps
     flops = 2 * 3 * D * F * (T * K + T) + 2 * T * D * E      # routed pairs + shared rows, plus the gate GEMV
     _, tf_peak, peak_kind = measured_peaks()
     achieved = flops / (ms * 1e-3) / 1e12
     io_bytes = T * D * 2
-    print(json.dumps({
-        "metric": "moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f16xf16->f32", "data": "synthetic",
-        "config": {"workload": (f"configs[4]: ragged continuous-batch mix, 48 sequences x (1 decode row + prefill chunks of 256/512/1024) "
-                                f"= {T} rows in {len(offsets) - 1} segments packed into one batch, one Qwen3.6-A3B MoE layer, unbiased router"
-                                if ragged else
-                                f"configs[2]: prefill gather-QMM, {T} tokens, one Qwen3.6-A3B MoE layer, Zipf(1.1) router bias"),
-                   "hidden": D, "intermediate": F, "experts": E, "top_k": K, "shared_experts": 1, "bits": 4, "group_size": 64,
-                   "pairs": T * K, "largest_group": int(counts.max()), "smallest_group": int(counts.min()),
-                   "experts_used": int((counts > 0).sum()),
-                   "l2": f"{n_sets} input sets cycled; 453 MB of expert weights per step exceed L2"},
+    cpu = None
+    if cpu_budget:
+        tok_s, cores, sample = cpu_port_prefill_tokens_per_s(64, cpu_budget, zipf=not ragged)
+        cpu = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    rec = {
+        "metric": "moe_prefill_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+        "workload": (f"configs[4]: ragged continuous-batch mix, 48 sequences x (1 decode row + prefill chunks of 256/512/1024) "
+                     f"= {T} rows in {len(offsets) - 1} segments packed into one batch, one Qwen3.6-A3B MoE layer, unbiased router"
+                     if ragged else
+                     f"configs[2]: prefill gather-QMM, {T} tokens, one Qwen3.6-A3B MoE layer, Zipf(1.1) router bias"),
+        "pairs": T * K, "largest_group": int(counts.max()), "smallest_group": int(counts.min()),
+        "experts_used": int((counts > 0).sum()),
+        "l2": f"{n_sets} input sets cycled; 453 MB of expert weights per step exceed L2",
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
                      "peak_kind": peak_kind, "traffic": None, "kernel": "whole layer (tc_ffn_kernel<1>, <2> dominate)",
                      "algorithmic_flops_per_step": flops},
-        "cpu_baseline": None,
-        "e2e": {"value": T / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": io_bytes,
+        "cpu_baseline": cpu,
+        "e2e": {"value": T / (e2e_ms / steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": io_bytes,
                 "d2h_bytes_per_step": io_bytes},
-        "gpu_launches": int(launches), "device_status": status, "clocks": clocks,
-    }))
+        "gpu_launches": int(launches), "device_status": int(status), "clocks": clocks,
+    }
+    moe.close()
+    return rec
+
+
+def run_prefill(args):
+    import torch
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rec = prefill_case(args.workload, args.tokens, args.steps, args.warmup, cpu_budget=8.0,
+                       sampler=ClockSampler(torch.cuda.current_device()))
+    line = {"metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+            "config": {"workload": rec["workload"], "hidden": D, "intermediate": F, "experts": E, "top_k": K,
+                       "shared_experts": 1, "bits": 4, "group_size": 64, "pairs": rec["pairs"],
+                       "largest_group": rec["largest_group"], "smallest_group": rec["smallest_group"],
+                       "experts_used": rec["experts_used"], "l2": rec["l2"]}}
+    for k in ("roofline", "cpu_baseline", "e2e", "gpu_launches", "device_status", "clocks"):
+        line[k] = rec[k]
+    print(json.dumps(line))
+    if rec["device_status"]:
+        sys.exit("bench: device status word set")
+
+
+def ep_case(world, rank, local, steps, warmup):
+    return None
 
 
 def run_ep(args):
@@ -533,6 +699,10 @@ def main():
                          "ragged: configs[4], the 86,064-row continuous-batch mix through the same layer; "
                          "ep: the same prefill layer with experts sharded over --gpus ranks (NCCL all-to-all)")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill token rows")
+    ap.add_argument("--trace", action="store_true", help="decode: add the fused kernel's per-phase times (one untimed step) as phase_us")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="decode: only the headline measurement (default: also decode batch 1 / 8 / 64 chained, configs[2] and "
+                         "configs[4] at 1 GPU, the expert-parallel layer of configs[3] at N > 1, under the line's `extras` key)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

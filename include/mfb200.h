@@ -103,6 +103,8 @@ typedef struct mfb_moe_config {
     float rms_eps;          /* 1e-6 in the reference (RealForwardRunner.swift:2583) */
     uint32_t max_tokens;    /* scratch arena capacity in token rows per call */
     uint32_t flags;         /* MFB_FLAG_* */
+    uint32_t max_layers;    /* most layers one mfb_moe_stack / mfb_moe_stack_rows call may be given, and the number of
+                               distinct layers whose tensor maps the handle keeps; 0 = 64 */
 } mfb_moe_config;
 
 #define MFB_FLAG_PREFILL_TENSOR_CORE 1u /* allocate the arena of the tcgen05 grouped-GEMM path */
@@ -150,6 +152,16 @@ int32_t mfb_moe_set_generic(mfb_moe* moe, int32_t on);
 int32_t mfb_moe_set_trace(mfb_moe* moe, uint64_t* device_stamps);
 /* Reads and clears the device status word that kernels set when a bounded wait runs out. Synchronises `stream`. */
 int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* status);
+
+/* Device pointer to the handle's fp32 down-projection rows [max_tokens, top_k + 1, d] (slot top_k = shared expert)
+ * as the last mfb_moe_experts / mfb_moe_decode / mfb_moe_layer / mfb_moe_stack call left them: what the reference's
+ * phase-2 kernels hold before the weighted reduce (Sources/Mference/Metal/MoE/moe.metal:349-404).  Lets a caller
+ * (and the parity tests) look at the unrounded partial sums.  Owned by the handle. */
+int32_t mfb_moe_partial_rows(mfb_moe* moe, const float** rows);
+/* Self-test of the bounded waits (no counterpart in the reference): launches one CTA that waits on a barrier nothing
+ * arrives at; after limit_cycles SM cycles (1 .. 20,000,000) the wait gives up, the kernel sets the device status
+ * word and returns.  mfb_moe_device_status then reports MFB_ERR_DEVICE_STATUS once, and the handle stays usable. */
+int32_t mfb_moe_selftest_wait(mfb_moe* moe, void* stream, uint64_t limit_cycles);
 
 /* ---- router -------------------------------------------------------------------------------------------- */
 

@@ -58,7 +58,8 @@ class MoEConfig(C.Structure):
                 ("bits", C.c_uint32), ("shared_bits", C.c_uint32), ("group_size", C.c_uint32),
                 ("scale_dtype", C.c_uint32), ("x_dtype", C.c_uint32), ("activation", C.c_uint32),
                 ("router_mode", C.c_uint32), ("swiglu_limit", C.c_float), ("route_scale", C.c_float),
-                ("rms_eps", C.c_float), ("max_tokens", C.c_uint32), ("flags", C.c_uint32)]
+                ("rms_eps", C.c_float), ("max_tokens", C.c_uint32), ("flags", C.c_uint32),
+                ("max_layers", C.c_uint32)]
 
 
 class LayerWeightsC(C.Structure):
@@ -80,6 +81,8 @@ SIGNATURES = {
     "mfb_moe_set_generic": (_I32, [_V, _I32]),
     "mfb_moe_set_trace": (_I32, [_V, _V]),
     "mfb_moe_device_status": (_I32, [_V, _V, C.POINTER(_U32)]),
+    "mfb_moe_partial_rows": (_I32, [_V, C.POINTER(_V)]),
+    "mfb_moe_selftest_wait": (_I32, [_V, _V, _U64]),
     "mfb_router_logits": (_I32, [_V, _V, _V, _U32, _U32, _V, _V, _V]),
     "mfb_router_select": (_I32, [_V, _V, _V, _U32, _V, _V, _V, _V]),
     "mfb_router_topk": (_I32, [_V, _V, _V, _U32, _U32, C.POINTER(LayerWeightsC), _V, _V]),

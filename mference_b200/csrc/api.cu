@@ -87,7 +87,7 @@ bool use_fast(const mfb_moe* m, uint32_t n_tokens) {
 }
 
 FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens, const uint16_t* route_w,
-                       const void* residual, void* y) {
+                       const void* residual, void* y, const WideMaps* maps) {
     const mfb_moe_config& c = m->cfg;
     Arena& a = m->a;
     FastParams P;
@@ -98,7 +98,65 @@ FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens
     P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
     P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.dbg = nullptr; P.actp = a.actp; P.partial = a.partial; P.route_w = route_w;
     P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
+    P.maps = maps;
     return P;
+}
+
+// Tensor maps of the layers a handle has been given, for the row-stationary decode phases.  A layer is recognised by
+// the fields the maps are built from; its maps live in one slot of a device array allocated when the handle is
+// created.  Slots are recycled oldest first, never one that the current call already uses.
+struct WideKey {
+    const void* pool; uint64_t slot_stride; const void* shared_blob; uint32_t has_table;
+    mfb_expert_offsets routed_off, shared_off;
+};
+struct WideCache {
+    WideMaps* dev = nullptr;
+    std::vector<WideKey> keys;
+    std::vector<uint64_t> stamp;   // call counter of the last use, 0 = empty
+    uint64_t call = 0;
+    uint32_t cap = 0;
+};
+
+WideKey wide_key(const mfb_layer_weights* w) {
+    WideKey k;
+    memset(&k, 0, sizeof k);
+    k.pool = w->pool; k.slot_stride = w->slot_stride; k.shared_blob = w->shared_blob; k.has_table = w->slot_of != nullptr;
+    k.routed_off = w->routed_off;
+    if (w->shared_blob) k.shared_off = w->shared_off;
+    return k;
+}
+
+// Device pointer to the maps of layer `w` (built and uploaded on `s` when the layer is new); *out = NULL when the
+// handle has no row-stationary form.  Calls of one mfb_* entry share one `call` number (begin_wide_call).
+int32_t wide_maps_for(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const WideMaps** out) {
+    *out = nullptr;
+    WideCache* wc = static_cast<WideCache*>(m->wide_cache);
+    if (!wc) return MFB_OK;
+    const WideKey k = wide_key(w);
+    uint32_t victim = 0;
+    uint64_t oldest = ~0ull;
+    for (uint32_t i = 0; i < wc->cap; ++i) {
+        if (wc->stamp[i] && memcmp(&wc->keys[i], &k, sizeof k) == 0) {
+            wc->stamp[i] = wc->call;
+            *out = wc->dev + i;
+            return MFB_OK;
+        }
+        if (wc->stamp[i] < oldest) { oldest = wc->stamp[i]; victim = i; }
+    }
+    MFB_REQUIRE(oldest < wc->call, MFB_ERR_CAPACITY, "more than %u distinct layers in one call (mfb_moe_config.max_layers)", wc->cap);
+    WideMaps host;
+    const int32_t rc = wide_encode_maps(m->cfg, *w, &host);
+    if (rc) return rc;
+    // pageable source: the runtime stages it before returning
+    MFB_CUDA(cudaMemcpyAsync(wc->dev + victim, &host, sizeof host, cudaMemcpyHostToDevice, s));
+    wc->keys[victim] = k;
+    wc->stamp[victim] = wc->call;
+    *out = wc->dev + victim;
+    return MFB_OK;
+}
+
+void begin_wide_call(mfb_moe* m) {
+    if (m->wide_cache) ++static_cast<WideCache*>(m->wide_cache)->call;
 }
 
 uint32_t max_groups_for(const mfb_moe* m, uint32_t n_tokens, bool shared) {
@@ -175,6 +233,7 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     MFB_REQUIRE(m != nullptr, MFB_ERR_ALLOC, "out of host memory");
     m->cfg = c;
     if (m->cfg.rms_eps <= 0.0f) m->cfg.rms_eps = 1e-6f;
+    if (m->cfg.max_layers == 0) m->cfg.max_layers = 64;
     cudaGetDevice(&m->device);
     cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, m->device);
     const uint64_t T = c.max_tokens, K = c.top_k, E = c.num_experts;
@@ -208,6 +267,26 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
         ok(dev_alloc(a.xp, ft * c.d));
         if (c.shared_bits && c.shared_bits != c.bits) ok(dev_alloc(a.xp2, ft * c.d));
         ok(dev_alloc(a.actp, ft * (K + 1) * c.f));
+        // everything a stack call needs is allocated here, so that no later call allocates: the per-layer weight
+        // table of the fused kernel and, for shapes with a row-stationary form, the tensor maps of max_layers layers
+        const uint32_t cap = m->cfg.max_layers;
+        { MegaLayer* p = nullptr; ok(dev_alloc(p, cap)); m->mega_dev = p; }
+        m->mega_host = calloc(cap, sizeof(MegaLayer));
+        if (!m->mega_host) ok(cudaErrorMemoryAllocation);
+        m->mega_cap = cap;
+        if (wide_supported(c)) {
+            WideCache* wc = new (std::nothrow) WideCache();
+            if (!wc) ok(cudaErrorMemoryAllocation);
+            else {
+                m->wide_cache = wc;
+                wc->cap = cap;
+                wc->keys.resize(cap);
+                wc->stamp.assign(cap, 0);
+                ok(dev_alloc(wc->dev, cap));
+            }
+        }
+        // a cooperative launch needs one CTA per SM resident at once: otherwise stacks run layer by layer
+        if (m->coop && e == cudaSuccess && !stack_mega_fits(c, m->sm_count, fast_smem_stack(c, (uint32_t)ft, m->wide_cache != nullptr))) m->coop = false;
     }
     if (c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) {
         const uint64_t rows = m->max_rows + TC_ROW_PAD;
@@ -218,10 +297,13 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     if (e == cudaSuccess && a.xs16) e = cudaMemset(a.xs16, 0, (m->max_rows + TC_ROW_PAD) * c.d * sizeof(__half));
     if (e == cudaSuccess && a.acts16) e = cudaMemset(a.acts16, 0, (m->max_rows + TC_ROW_PAD) * c.f * sizeof(__half));
     if (e != cudaSuccess) {
-        free_arena(a);
-        delete m;
         set_error("arena allocation failed: %s", cudaGetErrorString(e));
+        mfb_moe_destroy(m);
         return e == cudaErrorMemoryAllocation ? MFB_ERR_ALLOC : MFB_ERR_CUDA;
+    }
+    if (c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) {
+        const int32_t rc = tc_init(m);
+        if (rc) { mfb_moe_destroy(m); return rc; }
     }
     *out = m;
     return MFB_OK;
@@ -231,6 +313,11 @@ extern "C" int32_t mfb_moe_destroy(mfb_moe* moe) {
     if (!moe) return MFB_OK;
     tc_release(moe);
     free_arena(moe->a);
+    if (moe->wide_cache) {
+        WideCache* wc = static_cast<WideCache*>(moe->wide_cache);
+        cudaFree(wc->dev);
+        delete wc;
+    }
     cudaFree(moe->mega_dev);
     cudaFree(moe->mega_bar);
     free(moe->mega_host);
@@ -257,6 +344,20 @@ extern "C" int32_t mfb_moe_device_status(mfb_moe* moe, void* stream, uint32_t* s
     MFB_CUDA(cudaMemsetAsync(moe->a.status, 0, sizeof(uint32_t), (cudaStream_t)stream));
     MFB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (*status) { set_error("device status word = 0x%x", *status); return MFB_ERR_DEVICE_STATUS; }
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_partial_rows(mfb_moe* moe, const float** rows) {
+    MFB_REQUIRE(moe && rows, MFB_ERR_INVALID_ARGUMENT, "partial_rows: NULL argument");
+    *rows = moe->a.partial;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_moe_selftest_wait(mfb_moe* moe, void* stream, uint64_t limit_cycles) {
+    MFB_REQUIRE(moe != nullptr, MFB_ERR_INVALID_ARGUMENT, "handle is NULL");
+    MFB_REQUIRE(limit_cycles >= 1 && limit_cycles <= 20000000ull, MFB_ERR_INVALID_ARGUMENT,
+                "selftest_wait: limit must be 1..20,000,000 cycles (about 10 ms)");
+    MFB_CUDA(launch_wait_selftest((cudaStream_t)stream, moe->a.status, (long long)limit_cycles));
     return MFB_OK;
 }
 
@@ -343,8 +444,10 @@ extern "C" int32_t mfb_moe_combine(mfb_moe* moe, void* stream, uint32_t n_tokens
 extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                                   uint32_t n_tokens, const uint32_t* idx, const uint16_t* route_w, const void* residual,
                                   void* y) {
-    if (moe && w && x && idx && route_w && y && n_tokens && use_fast(moe, n_tokens) && ldx == moe->cfg.d) {
-        int32_t rc = check_weights(moe, w, false);
+    int32_t rc = check_handle(moe, n_tokens);   // capacity first: the fast path below writes n_tokens rows of the arena
+    if (rc) return rc;
+    if (w && x && idx && route_w && y && n_tokens && use_fast(moe, n_tokens) && ldx == moe->cfg.d) {
+        rc = check_weights(moe, w, false);
         if (rc) return rc;
         const mfb_moe_config& c = moe->cfg;
         Arena& a = moe->a;
@@ -353,13 +456,16 @@ extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_we
         MFB_CUDA(launch_fast_prep(s, x, (int)c.x_dtype, nullptr, n_tokens, c.d, c.rms_eps, false, nullptr, a.xp, c.bits, a.xp2, c.shared_bits));
         MFB_CUDA(launch_group(s, idx, route_w, n_tokens, c.top_k, c.num_experts, all_slots(moe), shared ? 1 : 0, 0, a, a.sorted,
                               a.offsets, a.counts, a.groups, a.n_groups, nullptr));
-        const FastParams P = fast_params(moe, w, n_tokens, route_w, residual, y);
+        const WideMaps* maps = nullptr;
+        begin_wide_call(moe);
+        if (n_tokens > 16 && (rc = wide_maps_for(moe, s, w, &maps)) != MFB_OK) return rc;
+        const FastParams P = fast_params(moe, w, n_tokens, route_w, residual, y, maps);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
         MFB_CUDA(launch_combine(s, a.partial, route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, residual, y,
                                 (int)c.x_dtype));
         return MFB_OK;
     }
-    int32_t rc = mfb_moe_experts(moe, stream, w, x, ldx, n_tokens, idx, route_w, nullptr, 0, 1);
+    rc = mfb_moe_experts(moe, stream, w, x, ldx, n_tokens, idx, route_w, nullptr, 0, 1);
     if (rc) return rc;
     return mfb_moe_combine(moe, stream, n_tokens, route_w, w->shared_blob != nullptr, residual, y);
 }
@@ -384,7 +490,10 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
         MFB_CUDA(launch_route_small(s, a.logits, n_tokens, c.num_experts, c.top_k, (int)c.router_mode,
                                     (const __nv_bfloat16*)w->per_expert_scale, w->correction_bias, c.route_scale, shared ? 1 : 0,
                                     a.idx, a.route_w, a.sorted, a.groups, a.n_groups));
-        const FastParams P = fast_params(moe, w, n_tokens, a.route_w, h_in, h_out);
+        const WideMaps* maps = nullptr;
+        begin_wide_call(moe);
+        if (n_tokens > 16 && (rc = wide_maps_for(moe, s, w, &maps)) != MFB_OK) return rc;
+        const FastParams P = fast_params(moe, w, n_tokens, a.route_w, h_in, h_out, maps);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
         MFB_CUDA(launch_combine(s, a.partial, a.route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, h_in, h_out,
                                 (int)c.x_dtype));
@@ -396,9 +505,14 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
     return mfb_moe_decode(moe, stream, w, a.xn, c.d, n_tokens, a.idx, a.route_w, h_in, h_out);
 }
 
-// Builds (or reuses) the device table of per-layer weights for the fused stack kernel.
-static int32_t upload_layer_table(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* layers, uint32_t n_layers) {
+// Builds (or reuses) the device table of per-layer weights for the fused stack kernel.  *all_maps: every layer has
+// tensor maps (the row-stationary phases may run).
+static int32_t upload_layer_table(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* layers, uint32_t n_layers, bool want_maps,
+                                  bool* all_maps) {
+    MFB_REQUIRE(n_layers <= m->mega_cap, MFB_ERR_CAPACITY, "%u layers exceed mfb_moe_config.max_layers = %u", n_layers, m->mega_cap);
     std::vector<MegaLayer> host(n_layers);
+    *all_maps = want_maps && m->wide_cache != nullptr;
+    begin_wide_call(m);
     for (uint32_t l = 0; l < n_layers; ++l) {
         const mfb_layer_weights& w = layers[l];
         MegaLayer& o = host[l];
@@ -407,17 +521,13 @@ static int32_t upload_layer_table(mfb_moe* m, cudaStream_t s, const mfb_layer_we
         o.per_expert_scale = (const __nv_bfloat16*)w.per_expert_scale; o.correction_bias = w.correction_bias;
         o.norm_w = (const __nv_bfloat16*)w.norm_w; o.pool = w.pool; o.slot_stride = w.slot_stride; o.slot_of = w.slot_of;
         o.shared_blob = w.shared_blob; o.routed_off = w.routed_off; o.shared_off = w.shared_off;
+        if (*all_maps) {
+            const int32_t rc = wide_maps_for(m, s, &w, &o.maps);
+            if (rc) return rc;
+        }
     }
     const size_t bytes = (size_t)n_layers * sizeof(MegaLayer);
-    if (m->mega_host && m->mega_count == n_layers && memcmp(m->mega_host, host.data(), bytes) == 0) return MFB_OK;
-    if (n_layers > m->mega_cap) {
-        cudaFree(m->mega_dev); free(m->mega_host);
-        m->mega_dev = nullptr; m->mega_host = nullptr; m->mega_cap = 0;
-        MFB_CUDA(cudaMalloc(&m->mega_dev, bytes));
-        m->mega_host = malloc(bytes);
-        MFB_REQUIRE(m->mega_host != nullptr, MFB_ERR_ALLOC, "out of host memory");
-        m->mega_cap = n_layers;
-    }
+    if (m->mega_count == n_layers && memcmp(m->mega_host, host.data(), bytes) == 0) return MFB_OK;
     memcpy(m->mega_host, host.data(), bytes);
     m->mega_count = n_layers;
     // the source is pageable host memory: the runtime stages it before returning, so reusing mega_host is safe
@@ -436,12 +546,14 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
     if (n_layers == 0 || n_tokens == 0) return MFB_OK;
     const mfb_moe_config& c = moe->cfg;
     cudaStream_t s = (cudaStream_t)stream;
-    if (use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens) <= FAST_SMEM_LIMIT) {
+    const bool want_maps = n_tokens > 16 && moe->wide_cache != nullptr;
+    if (use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens, want_maps) <= FAST_SMEM_LIMIT) {
         for (uint32_t l = 0; l < n_layers; ++l) {
             rc = check_weights(moe, &layers[l], true);
             if (rc) return rc;
         }
-        rc = upload_layer_table(moe, s, layers, n_layers);
+        bool all_maps = false;
+        rc = upload_layer_table(moe, s, layers, n_layers, want_maps, &all_maps);
         if (rc) return rc;
         Arena& a = moe->a;
         MegaParams M;
@@ -452,6 +564,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
         M.hidden = rows; M.layer_stride = layer_stride; M.n_tokens = n_tokens;
         M.xn = a.xn; M.xp = a.xp; M.xp2 = a.xp2; M.logits = a.logits; M.idx = a.idx; M.route_w = a.route_w; M.actp = a.actp; M.partial = a.partial;
         M.bar_counter = moe->mega_bar; M.abort = moe->mega_bar + 1; M.status = a.status; M.trace = moe->trace;
+        M.wide = all_maps ? 1 : 0;
         MFB_CUDA(launch_stack_mega(s, M, c, moe->sm_count));
         return MFB_OK;
     }

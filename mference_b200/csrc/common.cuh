@@ -86,6 +86,7 @@ struct mfb_moe {
     uint32_t mega_cap = 0, mega_count = 0;
     uint32_t* mega_bar = nullptr;
     bool coop = false;
+    void* wide_cache = nullptr;  // tensor maps of the layers this handle has seen (row-stationary decode phases; opaque here)
     uint64_t* trace = nullptr;   // device buffer for phase time stamps (mfb_moe_set_trace), not owned
 };
 

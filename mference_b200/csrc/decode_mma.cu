@@ -24,6 +24,9 @@
 #include "common.cuh"
 #include "decode_mma.cuh"
 #include "select.cuh"
+#include "tmap.cuh"
+
+#include <cstring>
 
 namespace mfb {
 
@@ -51,7 +54,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait: returns false when the limit runs out (the caller records it and unwinds).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = MBAR_WAIT_CYCLES) {
     const uint32_t addr = smem_u32(bar);
     const long long t0 = clock64();
     for (;;) {
@@ -62,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if (clock64() - t0 > MBAR_WAIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(32);   // a waiting warp should not take issue slots from the computing ones
     }
 }
@@ -659,6 +662,313 @@ __device__ __forceinline__ bool run_phase(const FastParams& P, const PhaseGeom& 
     return ok;
 }
 
+// ------------------------------------------------------------------------------------------ one FFN phase, row-stationary form
+// Used for batches above 16 rows.  The k-split form above hands every warp a slice of the contraction and pays for
+// it per unit with an exchange of partial sums through shared memory, a barrier and a separate epilogue; with
+// hundreds of units per CTA that serial tail costs as much as the arithmetic.  Here a warp owns sixteen matrix rows
+// for the WHOLE contraction: its accumulators hold finished sums, the epilogue runs on registers, and nothing is
+// exchanged.  The price is that a stage must hold a k-slice of 128 rows, i.e. row pieces that are not contiguous in
+// memory - which is what tiled TMA is for:
+//   stage     two tiles of [128 rows x 128 bytes of codes] (phase 1: gate and up rows of one row block; phase 2: two
+//             consecutive row blocks of down), each one cp.async.bulk.tensor.3d over (row bytes, rows, pool slot) in
+//             the 128-byte swizzle, plus the matching 256-element slice of the unit's (up to eight) activation rows,
+//             one bulk copy per row.  Four stages.
+//   scales    per sixteen groups of the contraction: scale and bias of both tiles as four tensor copies of
+//             [128 rows x 32 bytes] (32-byte swizzle; 16-byte rows unswizzled when a row has eight groups),
+//             double-buffered beside the ring with barriers of their own.
+// Bank conflicts: MMA row g of a warp's sixteen is tile row 2g (g < 4) or 2(g-4)+1, so the four lane groups of a
+// half warp read rows whose swizzle patterns differ in the upper two bits: every 8-byte load of the codes and of the
+// scales falls into distinct banks.  Activation rows sit 528 bytes apart (16 bytes of stagger).
+namespace wide {
+
+constexpr uint32_t TILE_ROWS = 128, TILE_ROW_BYTES = 128, TILE_BYTES = TILE_ROWS * TILE_ROW_BYTES;
+constexpr uint32_t NT = 2;                        // tiles per stage
+constexpr uint32_t KC = 256;                      // codes per k chunk: 128 bytes of 4-bit codes
+constexpr uint32_t GPC = KC / 64;                 // 64-element groups per chunk
+constexpr uint32_t X_STRIDE = KC * 2 + 16;        // bytes between the activation rows of a stage
+constexpr uint32_t STAGE_BYTES = 37 * 1024;       // NT tiles + 8 activation rows, rounded up to the swizzle alignment
+constexpr uint32_t STAGES = 4;
+constexpr uint32_t SCALE_BUF_BYTES = 16 * 1024;   // scale and bias of both tiles for sixteen groups
+constexpr uint32_t RING_BYTES = STAGES * STAGE_BYTES + 2 * SCALE_BUF_BYTES;
+static_assert(NT * TILE_BYTES + 8 * X_STRIDE <= STAGE_BYTES, "stage layout");
+
+struct Geom {
+    uint32_t k, rows, tiles, nkc, sbg, nsb, kc_per_sb, srb;
+};
+
+// PHASE 1: contraction over d, 128-row blocks of f (gate and up of the same rows);
+// PHASE 2: contraction over f, 256-row blocks of d.
+__host__ __device__ inline Geom geom(int phase, uint32_t d, uint32_t f) {
+    Geom g;
+    g.k = phase == 1 ? d : f;
+    g.rows = phase == 1 ? f : d;
+    g.tiles = phase == 1 ? f / TILE_ROWS : d / (NT * TILE_ROWS);
+    g.nkc = g.k / KC;
+    const uint32_t gpr = g.k / 64;
+    g.sbg = gpr < 16 ? gpr : 16;
+    g.nsb = gpr / g.sbg;
+    g.kc_per_sb = g.sbg / GPC;
+    g.srb = g.sbg * 2;
+    return g;
+}
+
+struct Ctx {
+    uint8_t* ring;        // STAGES stages, then the two scale buffers; 1024-byte aligned
+    uint64_t* full;       // [STAGES]
+    uint64_t* empty;      // [STAGES]
+    uint64_t* sfull;      // [2]
+    uint64_t* sempty;     // [2]
+    const uint32_t* pref; // exclusive prefix of units per group
+};
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint32_t c0, uint32_t c1, uint32_t c2, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
+
+// Makes a tensor map that the host rewrote since an earlier launch (a recycled slot of the handle's map array)
+// visible to the tensor copies of this thread's CTA.
+__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+struct UnitRef {
+    const CUtensorMap* maps;   // the nine maps of the unit's weights (routed pool or shared blob)
+    uint32_t slot, pair_start, pair_count;
+    bool shared, ok;
+};
+
+__device__ __forceinline__ UnitRef unit_ref(const FastParams& P, uint32_t g) {
+    UnitRef v;
+    const mfb_group grp = P.groups[g];
+    v.shared = grp.expert >= P.num_experts;
+    v.pair_start = grp.pair_start;
+    v.pair_count = grp.pair_count;
+    v.ok = true;
+    v.slot = 0;
+    if (v.shared) {
+        v.maps = P.maps->m[1];
+        v.ok = P.shared_blob != nullptr;
+    } else {
+        int32_t slot = (int32_t)grp.expert;
+        if (P.slot_of) slot = P.slot_of[grp.expert];
+        v.ok = slot >= 0;
+        v.slot = slot < 0 ? 0u : (uint32_t)slot;
+        v.maps = P.maps->m[0];
+    }
+    return v;
+}
+
+// Runs this CTA's share [first, last) of one phase.  `seq` / `sseq` count the stages / scale blocks this CTA has
+// pushed through the ring since its barriers were initialised (both phases and all layers share ring and barriers).
+template <int PHASE, int SDT>
+__device__ __forceinline__ bool run(const FastParams& P, const Geom& geo, const Ctx& C, uint32_t n_groups, uint32_t first,
+                                    uint32_t last, uint32_t& seq, uint32_t& sseq, uint32_t warp, uint32_t lane) {
+    if (first >= last) return true;
+    bool ok = true;
+    uint32_t g = 0;
+    seek_group(C.pref, n_groups, first, g);
+    uint32_t tt = (first - C.pref[g]) / geo.tiles, tile = (first - C.pref[g]) % geo.tiles;
+    UnitRef G = unit_ref(P, g);
+    uint8_t* const sbufs = C.ring + STAGES * STAGE_BYTES;
+    uint32_t my_seq = seq, my_sseq = sseq, ok_units = 0;
+    constexpr int DBG = PHASE == 1 ? 0 : 2;
+#define MFB_ADVANCE_UNIT()                                                                              \
+    do {                                                                                                \
+        if (++tile == geo.tiles) {                                                                      \
+            tile = 0; ++tt;                                                                             \
+            if (tt * 8 >= G.pair_count && g + 1 < n_groups) { ++g; tt = 0; G = unit_ref(P, g); }        \
+        }                                                                                               \
+    } while (0)
+    if (warp == CW) {
+        // ------------------------------------------------------------ copy-issuing warp
+        fence_proxy_async();   // activation rows written through the generic proxy by other CTAs before the grid barrier
+        if (lane < 18) tensormap_acquire(&P.maps->m[lane / 9][lane % 9]);
+        __syncwarp();
+        for (uint32_t u = first; u < last && ok; ++u) {
+            if (G.ok) {
+                ++ok_units;
+                const uint32_t cols = min(8u, G.pair_count - tt * 8), pair0 = G.pair_start + tt * 8;
+                const uint32_t row0 = PHASE == 1 ? tile * TILE_ROWS : tile * NT * TILE_ROWS;
+                // source of this lane's activation row (lanes 2 .. 2 + cols)
+                const uint8_t* xsrc = nullptr;
+                if (lane >= 2 && lane - 2 < cols) {
+                    if (PHASE == 1) xsrc = reinterpret_cast<const uint8_t*>(P.xp + (size_t)P.sorted[pair0 + lane - 2].token * P.d);
+                    else xsrc = reinterpret_cast<const uint8_t*>(P.actp + (size_t)(pair0 + lane - 2) * P.f);
+                }
+                for (uint32_t sb = 0; sb < geo.nsb && ok; ++sb) {
+                    const long long t0 = P.dbg ? clock64() : 0;
+                    const uint32_t sbuf = my_sseq & 1u, sph = (my_sseq >> 1) & 1u;
+                    if (!mbar_wait(&C.sempty[sbuf], sph ^ 1u)) { ok = false; break; }
+                    if (lane == 0) mbar_expect_tx(&C.sfull[sbuf], 2 * NT * TILE_ROWS * geo.srb);
+                    __syncwarp();
+                    if (lane < 2 * NT) {
+                        const uint32_t tl = lane >> 1, arr = lane & 1u;
+                        const CUtensorMap* map = G.maps + (PHASE == 1 ? 3 + 2 * tl + arr : 7 + arr);
+                        tma_load_3d(sbufs + sbuf * SCALE_BUF_BYTES + lane * TILE_ROWS * geo.srb, map, sb * geo.srb,
+                                    PHASE == 1 ? row0 : row0 + tl * TILE_ROWS, G.slot, &C.sfull[sbuf]);
+                    }
+                    ++my_sseq;
+                    for (uint32_t kc = sb * geo.kc_per_sb; kc < (sb + 1) * geo.kc_per_sb; ++kc) {
+                        const uint32_t s = my_seq % STAGES, ph = (my_seq / STAGES) & 1u;
+                        if (!mbar_wait(&C.empty[s], ph ^ 1u)) { ok = false; break; }
+                        uint8_t* st = C.ring + s * STAGE_BYTES;
+                        if (lane == 0) mbar_expect_tx(&C.full[s], NT * TILE_BYTES + cols * KC * 2);
+                        __syncwarp();
+                        if (lane < NT) {
+                            const CUtensorMap* map = G.maps + (PHASE == 1 ? lane : 2);
+                            tma_load_3d(st + lane * TILE_BYTES, map, kc * TILE_ROW_BYTES, PHASE == 1 ? row0 : row0 + lane * TILE_ROWS,
+                                        G.slot, &C.full[s]);
+                        } else if (xsrc) {
+                            bulk_g2s(st + NT * TILE_BYTES + (lane - 2) * X_STRIDE, xsrc + (size_t)kc * KC * 2, KC * 2, &C.full[s]);
+                        }
+                        ++my_seq;
+                    }
+                    if (P.dbg) dbg_add(P.dbg, warp, lane, DBG, t0);
+                }
+            }
+            MFB_ADVANCE_UNIT();
+        }
+    } else {
+        // ------------------------------------------------------------ eight computing warps, sixteen rows each
+        const uint32_t gq = lane >> 2, t = lane & 3;
+        const uint32_t rho = gq < 4 ? 2 * gq : 2 * (gq - 4) + 1;
+        const uint32_t row_lo = 16 * warp + rho;                                   // tile-local; the upper MMA row is row_lo + 8
+        const uint32_t wbase = row_lo * TILE_ROW_BYTES + ((((t >> 1) ^ (rho & 1u)) << 4) | ((t & 1u) << 3));
+        const uint32_t swz = (rho & 6u) << 4;
+        const uint32_t xoff = NT * TILE_BYTES + gq * X_STRIDE + t * 32;
+        const long long t_phase = P.dbg ? clock64() : 0;
+        for (uint32_t u = first; u < last && ok; ++u) {
+            const uint32_t cols = min(8u, G.pair_count - tt * 8), pair0 = G.pair_start + tt * 8;
+            if (G.ok) {
+                ++ok_units;
+                float acc[NT][4];
+#pragma unroll
+                for (int tl = 0; tl < (int)NT; ++tl)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[tl][c] = 0.0f;
+                for (uint32_t sb = 0; sb < geo.nsb && ok; ++sb) {
+                    const uint32_t sbuf = my_sseq & 1u, sph = (my_sseq >> 1) & 1u;
+                    if (!mbar_wait(&C.sfull[sbuf], sph)) { ok = false; break; }
+                    const uint8_t* sbase = sbufs + sbuf * SCALE_BUF_BYTES;
+                    for (uint32_t kci = 0; kci < geo.kc_per_sb; ++kci) {
+                        const uint32_t s = my_seq % STAGES, ph = (my_seq / STAGES) & 1u;
+                        long long t0 = P.dbg ? clock64() : 0;
+                        if (!mbar_wait(&C.full[s], ph)) { ok = false; break; }
+                        if (P.dbg) { dbg_add(P.dbg, warp, lane, DBG, t0); t0 = clock64(); }
+                        const uint8_t* st = C.ring + s * STAGE_BYTES;
+                        // scale and bias of this chunk's four groups for the lane's two rows of both tiles
+                        const uint32_t jj = kci * GPC;
+                        const uint32_t soff = geo.srb == 32 ? row_lo * 32 + ((((jj >> 3) ^ (row_lo >> 2)) & 1u) << 4) + (jj & 7u) * 2
+                                                            : row_lo * 16 + jj * 2;
+                        ScaleRow<GPC> sr[NT][4];   // [tile][scale lo, scale hi, bias lo, bias hi]
+#pragma unroll
+                        for (int tl = 0; tl < (int)NT; ++tl) {
+                            const uint8_t* sa = sbase + (2 * tl) * TILE_ROWS * geo.srb + soff;
+                            const uint8_t* ba = sa + TILE_ROWS * geo.srb;
+                            sr[tl][0].load(reinterpret_cast<const uint16_t*>(sa));
+                            sr[tl][1].load(reinterpret_cast<const uint16_t*>(sa + 8 * geo.srb));
+                            sr[tl][2].load(reinterpret_cast<const uint16_t*>(ba));
+                            sr[tl][3].load(reinterpret_cast<const uint16_t*>(ba + 8 * geo.srb));
+                        }
+#pragma unroll
+                        for (int j = 0; j < (int)GPC; ++j) {
+                            uint32_t bf[8];
+                            {
+                                const uint4 lo = *reinterpret_cast<const uint4*>(st + xoff + j * 128);
+                                const uint4 hi = *reinterpret_cast<const uint4*>(st + xoff + j * 128 + 16);
+                                bf[0] = lo.x; bf[1] = lo.y; bf[2] = lo.z; bf[3] = lo.w;
+                                bf[4] = hi.x; bf[5] = hi.y; bf[6] = hi.z; bf[7] = hi.w;
+                            }
+                            const float2 sx = group_sum<4>(bf);
+                            const uint32_t woff = wbase + ((32u * j) ^ swz);
+#pragma unroll
+                            for (int tl = 0; tl < (int)NT; ++tl) {
+                                const uint2 a = *reinterpret_cast<const uint2*>(st + tl * TILE_BYTES + woff);
+                                const uint2 b = *reinterpret_cast<const uint2*>(st + tl * TILE_BYTES + woff + 8 * TILE_ROW_BYTES);
+                                const uint32_t wl[2] = {a.x, a.y}, wh[2] = {b.x, b.y};
+                                uint32_t pl[8], phh[8];
+                                Unpack<4>::run(wl, pl);
+                                Unpack<4>::run(wh, phh);
+                                float dsum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    mma16816(dsum, pl[2 * q], phh[2 * q], pl[2 * q + 1], phh[2 * q + 1], bf[2 * q], bf[2 * q + 1]);
+                                const float s_lo = sr[tl][0].template at<SDT>(j), s_hi = sr[tl][1].template at<SDT>(j);
+                                const float b_lo = sr[tl][2].template at<SDT>(j), b_hi = sr[tl][3].template at<SDT>(j);
+                                acc[tl][0] = fmaf(s_lo, dsum[0], acc[tl][0]); acc[tl][0] = fmaf(b_lo, sx.x, acc[tl][0]);
+                                acc[tl][1] = fmaf(s_lo, dsum[1], acc[tl][1]); acc[tl][1] = fmaf(b_lo, sx.y, acc[tl][1]);
+                                acc[tl][2] = fmaf(s_hi, dsum[2], acc[tl][2]); acc[tl][2] = fmaf(b_hi, sx.x, acc[tl][2]);
+                                acc[tl][3] = fmaf(s_hi, dsum[3], acc[tl][3]); acc[tl][3] = fmaf(b_hi, sx.y, acc[tl][3]);
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&C.empty[s]);
+                        ++my_seq;
+                        if (P.dbg) dbg_add(P.dbg, warp, lane, DBG + 1, t0);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&C.sempty[sbuf]);
+                    ++my_sseq;
+                }
+                if (!ok) break;
+                // ---- epilogue on registers: the lane holds rows (row_lo, row_lo + 8) x token columns (2t, 2t + 1)
+                if (PHASE == 1) {
+                    const bool clamp = !G.shared && P.limit > 0.0f;   // moe_swiglu_clamp (moe.metal:27-34), routed experts only
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t r = tile * TILE_ROWS + row_lo + 8 * h;
+                        const uint32_t act_col = (r & ~15u) + perm_pos(r & 15u, 4);
+                        const float act_scale = perm_scale(r & 15u, 4);
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const uint32_t n = 2 * t + c;
+                            if (n >= cols) continue;
+                            float gate = acc[0][2 * h + c] * CODE_UNSCALE, up = acc[1][2 * h + c] * CODE_UNSCALE;
+                            if (clamp) {
+                                gate = fminf(gate, P.limit);
+                                up = fminf(fmaxf(up, -P.limit), P.limit);
+                            }
+                            float a = hidden_act(gate, (int)P.activation) * up;
+                            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                            P.actp[(size_t)(pair0 + n) * P.f + act_col] = __float2half_rn(a * act_scale);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint32_t n = 2 * t + c;
+                        if (n >= cols) continue;
+                        const mfb_pair pr = P.sorted[pair0 + n];
+                        float* out = P.partial + ((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + tile * NT * TILE_ROWS + row_lo;
+#pragma unroll
+                        for (int tl = 0; tl < (int)NT; ++tl) {
+                            out[tl * TILE_ROWS] = acc[tl][c] * CODE_UNSCALE;
+                            out[tl * TILE_ROWS + 8] = acc[tl][2 + c] * CODE_UNSCALE;
+                        }
+                    }
+                }
+            } else if (PHASE == 2) {
+                // an expert that is not resident contributes nothing: its rows of the partials are cleared
+                for (uint32_t o = warp * 32 + lane; o < NT * TILE_ROWS * cols; o += CW * 32) {
+                    const mfb_pair pr = P.sorted[pair0 + o / (NT * TILE_ROWS)];
+                    P.partial[((size_t)pr.token * (P.top_k + 1) + pr.rank) * P.d + tile * NT * TILE_ROWS + o % (NT * TILE_ROWS)] = 0.0f;
+                }
+            }
+            MFB_ADVANCE_UNIT();
+        }
+        if (PHASE == 1) fence_proxy_async();   // the hidden activations are read by bulk copies in phase 2
+        if (P.dbg) dbg_add(P.dbg, warp, lane, 5 + DBG, t_phase);
+    }
+#undef MFB_ADVANCE_UNIT
+    // every warp walks the same unit list, so the counters agree; on an abort they no longer matter
+    seq += ok_units * geo.nkc;
+    sseq += ok_units * geo.nsb;
+    return ok;
+}
+
+}  // namespace wide
+
 // Rank-ordered weighted combine of a slice of (token, column) outputs from the fp32 partial rows: residual first,
 // shared expert, then ranks ascending (moe_phase2_down_reduce_k8, moe.metal:349-404; same order as combine_kernel).
 __device__ __forceinline__ void combine_slice(const FastParams& P, uint32_t begin, uint32_t end, bool with_shared) {
@@ -678,6 +988,7 @@ __device__ __forceinline__ void combine_slice(const FastParams& P, uint32_t begi
 // ------------------------------------------------------------------------------------------ separate kernels
 struct FastShared {
     uint64_t full1[MAX_STAGES], empty1[MAX_STAGES], full2[MAX_STAGES], empty2[MAX_STAGES];
+    uint64_t wfull[wide::STAGES], wempty[wide::STAGES], sfull[2], sempty[2];   // row-stationary form
     uint32_t pref1[MAX_GROUPS + 1], pref2[MAX_GROUPS + 1], wpref1[MAX_GROUPS + 1];
     uint32_t range[4];   // this CTA's [first, last) units of phase 1 and of phase 2
     uint32_t flag, n_groups;
@@ -690,6 +1001,8 @@ __device__ __forceinline__ void init_barriers(FastShared& S) {
             mbar_init(&S.full1[s], 1); mbar_init(&S.empty1[s], CW);
             mbar_init(&S.full2[s], 1); mbar_init(&S.empty2[s], CW);
         }
+        for (uint32_t s = 0; s < wide::STAGES; ++s) { mbar_init(&S.wfull[s], 1); mbar_init(&S.wempty[s], CW); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&S.sfull[b], 1); mbar_init(&S.sempty[b], CW); }
         fence_barrier_init();
     }
     __syncthreads();
@@ -728,6 +1041,50 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) ffn_phase_kernel(const FastPa
     uint32_t seq = 0;
     const uint32_t first = S.range[NMAT == 2 ? 0 : 2], last = S.range[NMAT == 2 ? 1 : 3];   // cut with this phase's weights
     if (!run_phase<NMAT, NGW>(P, geo, C, n_groups, first, last, seq, warp, lane)) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+}
+
+// Unit weights of the row-stationary form: a unit's cost is its k loop, the token columns in use add next to nothing.
+__device__ __forceinline__ UnitBases wide_unit_bases() { return UnitBases{64u, 64u}; }
+
+__device__ __forceinline__ uint8_t* align_1k(uint8_t* p) {
+    return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~(uintptr_t)1023);
+}
+
+// Phase 1 or phase 2 in the row-stationary form, as a kernel of its own (batches above 16 rows).
+template <int PHASE>
+__global__ void __launch_bounds__(FAST_THREADS, 1) ffn_wide_kernel(const FastParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ FastShared S;
+    uint8_t* smem = align_1k(smem_raw);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const wide::Geom geo = wide::geom(PHASE, P.d, P.f);
+    init_barriers(S);
+    const uint32_t n_groups = *P.n_groups;
+    if (warp == 0) {
+        const UnitBases ub = wide_unit_bases();
+        uint32_t* wpref2 = reinterpret_cast<uint32_t*>(smem);   // the stage ring is not in use yet
+        warp_unit_prefix2<true>(P.groups, n_groups, geo.tiles, geo.tiles, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
+        warp_unit_ranges<true>(S, P.groups, n_groups, geo.tiles, geo.tiles, ub, wpref2, lane);
+    }
+    __syncthreads();
+    const wide::Ctx C{smem, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1};
+    uint32_t seq = 0, sseq = 0;
+    const uint32_t first = S.range[0], last = S.range[1];
+    const bool ok = P.scale_dtype == MFB_DT_BF16 ? wide::run<PHASE, MFB_DT_BF16>(P, geo, C, n_groups, first, last, seq, sseq, warp, lane)
+                                                 : wide::run<PHASE, MFB_DT_F16>(P, geo, C, n_groups, first, last, seq, sseq, warp, lane);
+    if (!ok) atomicOr(P.status, STATUS_MBAR_TIMEOUT);
+}
+
+// Self-test of the bounded wait every pipeline above relies on: one CTA, one mbarrier that nothing ever arrives at.
+// The wait gives up after `limit` SM cycles, the kernel records it in the status word and returns normally.
+__global__ void wait_selftest_kernel(uint32_t* status, long long limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(&bar, 0u, limit)) atomicOr(status, STATUS_MBAR_TIMEOUT);
 }
 
 // ------------------------------------------------------------------------------------------ prep: RMSNorm + layouts
@@ -841,6 +1198,7 @@ __device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLay
             xp_out[(i & ~15u) + perm_pos(i & 15u, M.bits)] = __float2half_rn(v * perm_scale(i & 15u, M.bits));
             if (xp2_out) xp2_out[(i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = __float2half_rn(v * perm_scale(i & 15u, M.shared_bits));
         }
+        fence_proxy_async();   // the row-stationary phases fetch these rows with bulk copies
     }
     __syncthreads();
 }
@@ -1042,10 +1400,16 @@ __device__ __forceinline__ void mega_group_mask(const MegaParams& M, FastShared&
     __syncthreads();
 }
 
-template <int NGW, bool LARGE_BATCH>
+// MODE 0: at most 16 rows (one-warp scan for the sort, flat unit weights); 1: more rows, k-split FFN phases;
+// 2: more rows, row-stationary FFN phases (every layer carries tensor maps).
+template <int NGW, int MODE>
 __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaParams M) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool LARGE_BATCH = MODE >= 1, WIDE = MODE == 2;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ FastShared S;
+    // the tensor copies of the row-stationary form want their tiles on a 1 KB boundary; the other instantiations keep
+    // the array itself as the base (a run-time base pointer costs them registers they do not have)
+    uint8_t* const smem = WIDE ? align_1k(smem_raw) : smem_raw;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t max_bits = M.shared_bits > M.bits ? M.shared_bits : M.bits;
     const PhaseGeom geo1 = phase_geom(2, M.d, M.f, NGW, max_bits, RING_BYTES);
@@ -1055,8 +1419,10 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     // ---- shared memory carve-up.  Region A holds the stage ring of whichever phase runs plus the k-split exchange
     // buffers; during the router phase it stages gate rows.  The routing lists follow it.
     uint8_t* region_a = smem;
-    const uint32_t region_a_bytes = RING_BYTES + RED_BYTES;
+    const uint32_t region_a_bytes = WIDE ? wide::RING_BYTES : RING_BYTES + RED_BYTES;
     float* red = reinterpret_cast<float*>(smem + RING_BYTES);
+    const wide::Geom wgeo1 = wide::geom(1, M.d, M.f), wgeo2 = wide::geom(2, M.d, M.f);
+    const uint32_t tiles1 = WIDE ? wgeo1.tiles : geo1.tiles, tiles2 = WIDE ? wgeo2.tiles : geo2.tiles;
     mfb_pair* sorted_s = reinterpret_cast<mfb_pair*>(smem + region_a_bytes);
     mfb_group* groups_s = reinterpret_cast<mfb_group*>(sorted_s + (n_pairs + M.n_tokens));
     uint32_t* idx_s = reinterpret_cast<uint32_t*>(groups_s + (M.num_experts + 1));
@@ -1068,7 +1434,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     __half* xp2_s = xp_s + M.d;
 
     init_barriers(S);
-    uint32_t epoch = 0, seq1 = 0, seq2 = 0;
+    uint32_t epoch = 0, seq1 = 0, seq2 = 0;   // row-stationary form: seq1 counts stages, seq2 scale blocks
     bool alive = true;
     // SM clock against the global timer over the whole launch (row 16 of the cycle counters): cycles per ns
     auto clock_pair = [&](int slot) {
@@ -1171,10 +1537,10 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         }
         const uint32_t n_groups = S.n_groups;
         if (warp == 0) {
-            const UnitBases ub = unit_bases(LARGE_BATCH);
+            const UnitBases ub = WIDE ? wide_unit_bases() : unit_bases(LARGE_BATCH);
             uint32_t* wpref2 = reinterpret_cast<uint32_t*>(region_a);   // the stage ring is not in use yet
-            warp_unit_prefix2<LARGE_BATCH>(groups_s, n_groups, geo1.tiles, geo2.tiles, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
-            warp_unit_ranges<LARGE_BATCH>(S, groups_s, n_groups, geo1.tiles, geo2.tiles, ub, wpref2, lane);
+            warp_unit_prefix2<LARGE_BATCH>(groups_s, n_groups, tiles1, tiles2, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
+            warp_unit_ranges<LARGE_BATCH>(S, groups_s, n_groups, tiles1, tiles2, ub, wpref2, lane);
         }
         __syncthreads();
 
@@ -1189,10 +1555,17 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         P.actp = M.actp; P.partial = M.partial; P.route_w = w_s;
         P.dbg = M.trace ? reinterpret_cast<unsigned long long*>(M.trace + (size_t)M.n_layers * 8) : nullptr;
         P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
+        P.maps = Ly.maps;
         stamp(4);
 
         // ---- phase 1: this CTA's contiguous share of the (group, token tile, row tile) units
-        {
+        if constexpr (WIDE) {
+            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1};
+            const uint32_t first = S.range[0], last = S.range[1];
+            const bool ok = M.scale_dtype == MFB_DT_BF16 ? wide::run<1, MFB_DT_BF16>(P, wgeo1, C, n_groups, first, last, seq1, seq2, warp, lane)
+                                                         : wide::run<1, MFB_DT_F16>(P, wgeo1, C, n_groups, first, last, seq1, seq2, warp, lane);
+            if (!ok) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+        } else {
             PhaseCtx C{region_a, S.full1, S.empty1, red, S.pref1};
             const uint32_t first = S.range[0], last = S.range[1];
             if (!run_phase<2, NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
@@ -1201,7 +1574,13 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         if (!(alive = grid_barrier(M, S, epoch))) break;
         stamp(6);
         // ---- phase 2: down projections of every (group, token tile, 128-row block) into the fp32 partial rows
-        {
+        if constexpr (WIDE) {
+            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref2};
+            const uint32_t first = S.range[2], last = S.range[3];
+            const bool ok = M.scale_dtype == MFB_DT_BF16 ? wide::run<2, MFB_DT_BF16>(P, wgeo2, C, n_groups, first, last, seq1, seq2, warp, lane)
+                                                         : wide::run<2, MFB_DT_F16>(P, wgeo2, C, n_groups, first, last, seq1, seq2, warp, lane);
+            if (!ok) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+        } else {
             PhaseCtx C{region_a, S.full2, S.empty2, red, S.pref2};
             const uint32_t first = S.range[2], last = S.range[3];
             if (!run_phase<1, 4>(P, geo2, C, n_groups, first, last, seq2, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
@@ -1236,23 +1615,64 @@ bool fast_supported(const mfb_moe_config& c) {
     return g1.n_stages >= 2 && g2.n_stages >= 2;
 }
 
+bool wide_supported(const mfb_moe_config& c) {
+    if (!fast_supported(c)) return false;   // the small-batch instantiations and the router steps come from the same kernel
+    if (c.bits != 4 || !(c.shared_bits == 0 || c.shared_bits == 4)) return false;
+    return c.d % 1024 == 0 && (c.f == 512 || c.f % 1024 == 0);
+}
+
+int32_t wide_encode_maps(const mfb_moe_config& c, const mfb_layer_weights& w, WideMaps* out) {
+    memset(out, 0, sizeof *out);
+    for (int sh = 0; sh < 2; ++sh) {
+        const uint8_t* base = sh ? w.shared_blob : w.pool;
+        if (!base) continue;
+        const mfb_expert_offsets& off = sh ? w.shared_off : w.routed_off;
+        const uint32_t* o = &off.gate_w;
+        // the third coordinate is the pool slot; a slot table may name any int16 slot, the identity mapping names experts
+        const uint64_t slots = sh ? 1 : (w.slot_of ? 32768ull : (uint64_t)c.num_experts);
+        const uint64_t blob_stride = w.slot_stride;
+        for (int m = 0; m < 3; ++m) {   // gate, up: [f rows, d codes]; down: [d rows, f codes]
+            const uint64_t k = m < 2 ? c.d : c.f, rows = m < 2 ? c.f : c.d, gpr = k / 64;
+            const uint64_t row_bytes = k / 2, srow_bytes = gpr * 2;
+            const uint32_t srb = (uint32_t)(gpr < 16 ? gpr : 16) * 2;
+            {
+                const uint64_t dims[3] = {row_bytes, rows, slots}, strides[2] = {row_bytes, sh ? rows * row_bytes : blob_stride};
+                const uint32_t box[3] = {wide::TILE_ROW_BYTES, wide::TILE_ROWS, 1};
+                const int32_t rc = encode_tensor_map(&out->m[sh][m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base + o[3 * m], dims, strides,
+                                                     box, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc) return rc;
+            }
+            for (int a = 0; a < 2; ++a) {
+                const uint64_t dims[3] = {srow_bytes, rows, slots}, strides[2] = {srow_bytes, sh ? rows * srow_bytes : blob_stride};
+                const uint32_t box[3] = {srb, wide::TILE_ROWS, 1};
+                const int32_t rc = encode_tensor_map(&out->m[sh][3 + 2 * m + a], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base + o[3 * m + 1 + a],
+                                                     dims, strides, box, srb == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE);
+                if (rc) return rc;
+            }
+        }
+    }
+    return MFB_OK;
+}
+
 size_t fast_smem1(const mfb_moe_config&) { return (size_t)RING_BYTES + RED_BYTES; }
 size_t fast_smem2(const mfb_moe_config&, uint32_t) { return (size_t)RING_BYTES + RED_BYTES; }
 
-size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens) {
+size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens, bool wide_form) {
     const size_t pairs = (size_t)n_tokens * c.top_k;
     const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
                          ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 6 : 0);
-    if ((size_t)c.d * (MEGA_MAX_EB * 4 + (CW + 1) * MEGA_MAX_TT * 2) > (size_t)RING_BYTES + RED_BYTES)
+    const size_t region_a = wide_form && n_tokens > 16 ? (size_t)wide::RING_BYTES : (size_t)RING_BYTES + RED_BYTES;
+    if ((size_t)c.d * (MEGA_MAX_EB * 4 + (CW + 1) * MEGA_MAX_TT * 2) > region_a)
         return (size_t)1 << 30;   // the router staging does not fit: the caller falls back to the per-layer launches
-    return (size_t)RING_BYTES + RED_BYTES + lists + 64;
+    return region_a + lists + 64 + 1024;   // + slack for the 1 KB alignment of the ring
 }
 
 template <int NGW>
 static cudaError_t fast_init_ngw() {
     cudaError_t e = cudaFuncSetAttribute(ffn_phase_kernel<2, NGW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(stack_mega_kernel<NGW, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess && NGW >= 2) e = cudaFuncSetAttribute(stack_mega_kernel<(NGW >= 2 ? NGW : 2), 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     return e;
 }
 
@@ -1260,10 +1680,28 @@ static cudaError_t fast_init_ngw() {
 // attribute call happens while a caller captures a CUDA graph).
 cudaError_t fast_init() {
     cudaError_t e = cudaFuncSetAttribute(ffn_phase_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(ffn_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(ffn_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FAST_SMEM_LIMIT);
     if (e == cudaSuccess) e = fast_init_ngw<1>();
     if (e == cudaSuccess) e = fast_init_ngw<2>();
     if (e == cudaSuccess) e = fast_init_ngw<4>();
     return e;
+}
+
+// Whether `blocks` CTAs of the fused kernel can be co-resident on the current device with `smem` bytes of dynamic
+// shared memory each (a cooperative launch needs all of them resident at once).
+bool stack_mega_fits(const mfb_moe_config& c, int sm_count, size_t smem) {
+    int per_sm = 0;
+    const void* fn = c.d / 512 == 1 ? (const void*)stack_mega_kernel<1, 0> : c.d / 512 == 2 ? (const void*)stack_mega_kernel<2, 0>
+                                                                                            : (const void*)stack_mega_kernel<4, 0>;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, FAST_THREADS, smem) != cudaSuccess) return false;
+    return per_sm >= 1 && sm_count >= 1;
+}
+
+cudaError_t launch_wait_selftest(cudaStream_t s, uint32_t* status, long long limit_cycles) {
+    wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_cycles);
+    count_launches(1);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __nv_bfloat16* w, uint32_t n_tokens, uint32_t d,
@@ -1274,9 +1712,22 @@ cudaError_t launch_fast_prep(cudaStream_t s, const void* h, int dtype, const __n
     return cudaGetLastError();
 }
 
-// Phase 1 and phase 2 as two launches; the caller follows with the combine kernel over P.partial.
+// Phase 1 and phase 2 as two launches; the caller follows with the combine kernel over P.partial.  Batches above 16
+// rows whose layer carries tensor maps (P.maps) take the row-stationary kernels, like the fused kernel does.
 cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_config& c, int sm_count, uint32_t max_groups) {
     const uint32_t max_bits = cfg_max_bits(c), tts = (P.n_tokens + 7) / 8;
+    if (P.maps && P.n_tokens > 16) {
+        const wide::Geom g1 = wide::geom(1, c.d, c.f), g2 = wide::geom(2, c.d, c.f);
+        const size_t smem = (size_t)wide::RING_BYTES + 1024;
+        const uint32_t u1 = max_groups * g1.tiles * tts, u2 = max_groups * g2.tiles * tts;
+        const uint32_t grid1 = u1 < (uint32_t)sm_count ? u1 : (uint32_t)sm_count, grid2 = u2 < (uint32_t)sm_count ? u2 : (uint32_t)sm_count;
+        ffn_wide_kernel<1><<<grid1, FAST_THREADS, smem, s>>>(P);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        ffn_wide_kernel<2><<<grid2, FAST_THREADS, smem, s>>>(P);
+        count_launches(2);
+        return cudaGetLastError();
+    }
     const PhaseGeom g1 = phase_geom(2, c.d, c.f, c.d / 512, max_bits, RING_BYTES);
     const PhaseGeom g2 = phase_geom(1, c.f, c.d, 4, max_bits, RING_BYTES);
     const size_t smem = (size_t)RING_BYTES + RED_BYTES;
@@ -1301,14 +1752,16 @@ cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe
     MegaParams copy = M;
     void* args[] = {&copy};
     const void* fn = nullptr;
-    const bool mask_sort = M.n_tokens > 16;   // several rounds of the one-warp scan cost more than the all-threads form; also selects the unit weights
+    // above 16 rows: the all-threads form of the routing-table sort (several rounds of the one-warp scan cost more) and
+    // per-phase unit weights; with tensor maps on every layer additionally the row-stationary FFN phases
+    const int mode = M.n_tokens > 16 ? (M.wide ? 2 : 1) : 0;
     switch (c.d / 512) {
-        case 1: fn = mask_sort ? (const void*)stack_mega_kernel<1, true> : (const void*)stack_mega_kernel<1, false>; break;
-        case 2: fn = mask_sort ? (const void*)stack_mega_kernel<2, true> : (const void*)stack_mega_kernel<2, false>; break;
-        case 4: fn = mask_sort ? (const void*)stack_mega_kernel<4, true> : (const void*)stack_mega_kernel<4, false>; break;
+        case 1: fn = mode ? (const void*)stack_mega_kernel<1, 1> : (const void*)stack_mega_kernel<1, 0>; break;
+        case 2: fn = mode == 2 ? (const void*)stack_mega_kernel<2, 2> : mode ? (const void*)stack_mega_kernel<2, 1> : (const void*)stack_mega_kernel<2, 0>; break;
+        case 4: fn = mode == 2 ? (const void*)stack_mega_kernel<4, 2> : mode ? (const void*)stack_mega_kernel<4, 1> : (const void*)stack_mega_kernel<4, 0>; break;
         default: return cudaErrorInvalidValue;
     }
-    e = cudaLaunchCooperativeKernel(fn, dim3((unsigned)sm_count), dim3(FAST_THREADS), args, fast_smem_stack(c, M.n_tokens), s);
+    e = cudaLaunchCooperativeKernel(fn, dim3((unsigned)sm_count), dim3(FAST_THREADS), args, fast_smem_stack(c, M.n_tokens, mode == 2), s);
     count_launches(1);
     return e;
 }

@@ -185,6 +185,9 @@ extern "C" int32_t mfb_pool_fill_async(mfb_pool* p, void* stream, const int32_t*
 extern "C" int32_t mfb_pool_publish(mfb_pool* p, void* stream, const int32_t* experts, const int32_t* slots,
                                     const uint8_t* miss, uint32_t n) {
     MFB_REQUIRE(p && experts && slots && miss, MFB_ERR_INVALID_ARGUMENT, "pool_publish: NULL argument");
+    for (uint32_t i = 0; i < n; ++i)   // validated before anything changes: the eviction order indexes per-expert counters by these ids
+        MFB_REQUIRE(!miss[i] || (experts[i] >= 0 && (uint32_t)experts[i] < p->num_experts), MFB_ERR_INVALID_ARGUMENT,
+                    "pool_publish: expert %d out of range", experts[i]);
     std::lock_guard<std::mutex> g(p->lock);
     for (uint32_t i = 0; i < n; ++i)
         if (miss[i] && slots[i] >= 0 && (uint32_t)slots[i] < p->slot_count) set_slot_expert(*p, (uint32_t)slots[i], experts[i]);

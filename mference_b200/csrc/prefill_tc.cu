@@ -28,7 +28,10 @@
 // nothing is shuffled.
 #include <cuda.h>
 
+#include <new>
+
 #include "prefill_tc.cuh"
+#include "tmap.cuh"
 
 namespace mfb {
 
@@ -550,12 +553,14 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
 // Rows from n_routed on belong to the shared expert's group and follow its code width.  A thread converts sixteen
 // consecutive elements: two 16-byte loads, the permutation in registers, two 16-byte stores.
 __global__ void tc_gather_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t d,
-                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, uint32_t n_routed, uint32_t bits,
-                                 uint32_t shared_bits, __half* __restrict__ xs16) {
+                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, uint32_t n_routed, uint32_t n_tokens,
+                                 uint32_t bits, uint32_t shared_bits, __half* __restrict__ xs16) {
     const uint32_t pos = blockIdx.x;
     if (pos >= n_rows) return;
     const uint32_t width = pos < n_routed ? bits : shared_bits;
-    const size_t src = (size_t)sorted[pos].token * ldx;
+    const uint32_t token = sorted[pos].token;
+    if (token >= n_tokens) return;   // an entry no group refers to (a caller's list shorter than n_tokens * top_k)
+    const size_t src = (size_t)token * ldx;
     const bool vec = x_dtype != MFB_DT_F32 && (ldx & 7u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     for (uint32_t k = threadIdx.x * 16; k < d; k += blockDim.x * 16) {
         uint16_t in[16];
@@ -621,26 +626,9 @@ struct TcState {
 constexpr size_t TC_SMEM_BYTES = TC_STAGES * tc_tile_n(2) * 128 + 1024;   // activation tiles only (phase 2 is the larger)
 
 int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
-    const cuuint64_t dims[2] = {inner, rows};
-    const cuuint64_t strides[1] = {inner * sizeof(__half)};
-    const cuuint32_t box[2] = {TC_KC, TC_BOX_ROWS};
-    const cuuint32_t estr[2] = {1, 1};
-    // the driver entry point is looked up at run time: the library must load on machines without a GPU driver
-    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
-    MFB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &found));
-    MFB_REQUIRE(sym != nullptr && found == cudaDriverEntryPointSuccess, MFB_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
-    const CUresult r = reinterpret_cast<encode_fn>(sym)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr,
-                                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
-        return MFB_ERR_CUDA;
-    }
-    return MFB_OK;
+    const uint64_t dims[2] = {inner, rows}, strides[1] = {inner * sizeof(__half)};
+    const uint32_t box[2] = {TC_KC, TC_BOX_ROWS};
+    return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 }  // namespace
@@ -648,6 +636,28 @@ int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
 bool tc_supported(const mfb_moe_config& c) {
     // scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512
     return c.d % 512 == 0 && c.f % 512 == 0;
+}
+
+// Everything the tensor-core path needs besides its launches, built once when the handle is created: the tensor maps
+// over the arena's gathered rows and hidden activations, the token-tile prefix arrays and the kernels' opt-in to
+// large dynamic shared memory.  The per-call path only launches.
+int32_t tc_init(mfb_moe* m) {
+    const mfb_moe_config& c = m->cfg;
+    Arena& a = m->a;
+    if (!a.xs16 || !a.acts16 || !tc_supported(c)) return MFB_OK;
+    TcState* st = new (std::nothrow) TcState();
+    MFB_REQUIRE(st != nullptr, MFB_ERR_ALLOC, "out of host memory");
+    m->tma = st;
+    st->rows_cap = m->max_rows + TC_ROW_PAD;
+    int32_t rc = make_map(&st->map_x, a.xs16, c.d, st->rows_cap);
+    if (rc) return rc;
+    rc = make_map(&st->map_h, a.acts16, c.f, st->rows_cap);
+    if (rc) return rc;
+    MFB_CUDA(cudaMalloc(&st->prefix, 2 * (MFB_MAX_EXPERTS + 2) * sizeof(uint32_t)));
+    MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+    MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+    st->ready = true;
+    return MFB_OK;
 }
 
 void tc_release(mfb_moe* m) {
@@ -663,25 +673,13 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     Arena& a = m->a;
     MFB_REQUIRE(a.xs16 && a.acts16, MFB_ERR_INVALID_ARGUMENT, "tensor-core path: the handle was created without MFB_FLAG_PREFILL_TENSOR_CORE");
     TcState* st = static_cast<TcState*>(m->tma);
-    if (!st) {
-        st = new TcState();
-        m->tma = st;
-    }
-    if (!st->ready) {
-        st->rows_cap = m->max_rows + TC_ROW_PAD;
-        int32_t rc = make_map(&st->map_x, a.xs16, c.d, st->rows_cap);
-        if (rc) return rc;
-        rc = make_map(&st->map_h, a.acts16, c.f, st->rows_cap);
-        if (rc) return rc;
-        MFB_CUDA(cudaMalloc(&st->prefix, 2 * (MFB_MAX_EXPERTS + 2) * sizeof(uint32_t)));
-        MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
-        MFB_CUDA(cudaFuncSetAttribute(tc_ffn_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
-        st->ready = true;
-    }
-    const uint32_t n_rows = n_tokens * c.top_k + (routed_only ? 0u : n_tokens);
+    MFB_REQUIRE(st && st->ready, MFB_ERR_INVALID_ARGUMENT, "tensor-core path: the handle's tensor maps were not built");
+    // the shared expert's rows follow the routed pairs only when the layer has one (the grouping appends them then)
+    const bool with_shared = !routed_only && w->shared_blob != nullptr;
+    const uint32_t n_rows = n_tokens * c.top_k + (with_shared ? n_tokens : 0u);
     TcParams P;
     P.pool = (const uint8_t*)w->pool; P.slot_stride = w->slot_stride; P.slot_of = w->slot_of;
-    P.shared_blob = routed_only ? nullptr : (const uint8_t*)w->shared_blob;
+    P.shared_blob = with_shared ? (const uint8_t*)w->shared_blob : nullptr;
     P.routed_off = w->routed_off; P.shared_off = w->shared_off;
     P.d = c.d; P.f = c.f; P.num_experts = c.num_experts; P.bits = c.bits; P.shared_bits = c.shared_bits;
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
@@ -690,7 +688,7 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     P.acts16 = a.acts16; P.partial = partial; P.slots = slots; P.status = a.status;
 
     tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, st->prefix, st->prefix + MFB_MAX_EXPERTS + 2);
-    tc_gather_kernel<<<n_rows, 128, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, n_tokens * c.top_k, c.bits,
+    tc_gather_kernel<<<n_rows, 128, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, n_tokens * c.top_k, n_tokens, c.bits,
                                             c.shared_bits ? c.shared_bits : c.bits, a.xs16);
     // upper bounds of the work items (the kernels read the exact counts from the prefix arrays)
     const uint32_t items1 = ((n_rows + tc_tile_n(1) - 1) / tc_tile_n(1) + max_groups) * (c.f / TC_M);

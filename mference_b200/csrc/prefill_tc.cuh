@@ -9,6 +9,8 @@ constexpr uint32_t TC_TILE_N = 256;   // token rows per tile of the grouped GEMM
 constexpr uint32_t TC_ROW_PAD = 256;  // spare rows behind the gathered activations so a tile may over-read
 
 bool tc_supported(const mfb_moe_config& c);
+// Builds the tensor maps, prefix arrays and kernel attributes of the path (called once by mfb_moe_create).
+int32_t tc_init(mfb_moe* m);
 void tc_release(mfb_moe* m);
 // partial[(token*slots + rank), :] = ffn_expert(x[token]) for every sorted pair of every group.
 int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,

@@ -112,11 +112,11 @@ class MoE:
     def __init__(self, d: int, f: int, num_experts: int, top_k: int, *, bits: int = 4, shared_bits: int = 4,
                  scale_dtype: int = L.DT_F16, x_dtype: int = L.DT_BF16, activation: int = L.ACT_SILU,
                  router_mode: int = L.ROUTER_SOFTMAX_TOPK, swiglu_limit: float = 0.0, route_scale: float = 1.0,
-                 rms_eps: float = 1e-6, max_tokens: int = 1, tensor_core_prefill: bool = False):
+                 rms_eps: float = 1e-6, max_tokens: int = 1, tensor_core_prefill: bool = False, max_layers: int = 0):
         self.lib = L.load()
         cfg = L.MoEConfig(d, f, num_experts, top_k, bits, shared_bits, 64, scale_dtype, x_dtype, activation,
                           router_mode, swiglu_limit, route_scale, rms_eps, max_tokens,
-                          L.FLAG_PREFILL_TENSOR_CORE if tensor_core_prefill else 0)
+                          L.FLAG_PREFILL_TENSOR_CORE if tensor_core_prefill else 0, max_layers)
         self.cfg = cfg
         self.handle = C.c_void_p()
         L.check(self.lib.mfb_moe_create(C.byref(cfg), C.byref(self.handle)))
@@ -239,6 +239,23 @@ class MoE:
         """Attach (or detach with None) a zeroed uint64 [n_layers + 17, 8] CUDA tensor: per-phase global-timer stamps
         of every layer, then 17 rows of cycle counters of CTA 0 (see mfb_moe_set_trace in the header)."""
         L.check(self.lib.mfb_moe_set_trace(self.handle, _ptr(stamps)))
+
+    def partial_rows(self, n_tokens: int) -> torch.Tensor:
+        """fp32 [n_tokens, top_k + 1, d] view of the handle's down-projection rows (slot top_k = shared expert) as the
+        last decode / layer / stack call left them (mfb_moe_partial_rows)."""
+        p = C.c_void_p()
+        L.check(self.lib.mfb_moe_partial_rows(self.handle, C.byref(p)))
+        shape = (n_tokens, self.cfg.top_k + 1, self.cfg.d)
+
+        class _Ptr:
+            pass
+        holder = _Ptr()
+        holder.__cuda_array_interface__ = {"shape": shape, "typestr": "<f4", "data": (p.value, False), "version": 2}
+        return torch.as_tensor(holder, device="cuda")
+
+    def selftest_wait(self, limit_cycles: int = 2_000_000):
+        """Launches the bounded-wait self-test: device_status() reports the timeout bit afterwards."""
+        L.check(self.lib.mfb_moe_selftest_wait(self.handle, _stream(), limit_cycles))
 
     def device_status(self) -> int:
         st = C.c_uint32()

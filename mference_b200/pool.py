@@ -68,7 +68,8 @@ class ExpertPool:
         n = len(plan.experts)
         ex = (C.c_int32 * max(n, 1))(*plan.experts)
         sl = (C.c_int32 * max(n, 1))(*plan.assigned_slots)
-        ms = (C.c_uint8 * max(n, 1))(*[1 if i in set(plan.misses) else 0 for i in range(n)])
+        missing = set(plan.misses)
+        ms = (C.c_uint8 * max(n, 1))(*[1 if i in missing else 0 for i in range(n)])
         return n, ex, sl, ms
 
     def fill_async(self, plan: ExpertCachePlan, host_blobs, stream: int = 0):
@@ -78,11 +79,14 @@ class ExpertPool:
             return
         n, ex, sl, ms = self._arrays(plan)
         ptrs = (C.c_void_p * max(n, 1))()
-        blob_bytes = 0
+        blob_bytes = None
         for i in plan.misses:
             t = host_blobs[plan.experts[i]]
             ptrs[i] = t.data_ptr()
-            blob_bytes = t.numel() * t.element_size()
+            size = t.numel() * t.element_size()
+            if blob_bytes is not None and size != blob_bytes:   # one byte count serves every copy of the call
+                raise L.MfbError(L.ERR_IO, f"expert blobs of different sizes in one fill ({blob_bytes} and {size} bytes)")
+            blob_bytes = size
         L.check(self.lib.mfb_pool_fill_async(self.handle, C.c_void_p(stream), ex, sl, ms, n, ptrs, blob_bytes))
 
     def publish(self, plan: ExpertCachePlan, stream: int = 0):

@@ -721,3 +721,13 @@ int mfbo_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Number of threads of the following parallel loops (the timed CPU baseline uses every host core even when the
+ * launcher exported OMP_NUM_THREADS=1 for its ranks). */
+void mfbo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -146,6 +146,7 @@ void mfbo_rmsnorm(const float* x, const uint16_t* w_bf16, uint32_t n_rows, uint3
 void mfbo_ref_moe_layer_f32(const mfbo_layer* L, const float* x, uint32_t n_tokens, const uint32_t* idx,
                             const uint16_t* w_f16, const float* residual, float* y);
 int mfbo_num_threads(void);
+void mfbo_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

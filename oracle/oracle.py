@@ -294,6 +294,10 @@ def num_threads() -> int:
     return lib().mfbo_num_threads()
 
 
+def set_num_threads(n: int) -> None:
+    lib().mfbo_set_num_threads(C.c_int(int(n)))
+
+
 # ----------------------------------------------------------------------------- grouping / reduce / norm
 
 class GroupingError(ValueError):

@@ -8,6 +8,8 @@ from helpers import TOL_REL_L2, make_x, to_dev16, upload_layer
 
 pytestmark = pytest.mark.gpu
 
+ROOT = 0xB2000001
+
 
 def _route(W, x, dtype=O.DT_BF16):
     lg = O.router_logits(x, dtype, W.router)
@@ -298,3 +300,123 @@ def test_phase_trace_of_the_fused_stack_kernel():
     assert (flat[1:] >= flat[:-1]).all()          # phases within a layer and layers in order
     clocks = trace[NL + 16].cpu().numpy()
     assert clocks[5] > clocks[4] and clocks[7] > clocks[6]   # SM clock and global timer advanced over the launch
+
+
+def test_fast_shape_capacity_is_checked_on_the_host():
+    """A handle created for two rows refuses three rows of a fast-path shape with ERR_CAPACITY and launches nothing."""
+    import torch
+    from mference_b200 import MfbError, _lib as L
+    from mference_b200.moe import MoE
+    d, f, E, K = 512, 256, 4, 2
+    W = O.LayerWeights(d, f, E, K)
+    moe = MoE(d, f, E, K, max_tokens=2)
+    lw = upload_layer(W)
+    x = torch.zeros((3, d), dtype=torch.bfloat16, device="cuda")
+    idx = torch.zeros((3, K), dtype=torch.int32, device="cuda")
+    w = torch.zeros((3, K), dtype=torch.float16, device="cuda")
+    before = moe.lib.mfb_launch_count()
+    with pytest.raises(MfbError) as ei:
+        moe.encode_decode(lw, x, idx, w, torch.empty_like(x))
+    assert ei.value.code == L.ERR_CAPACITY
+    with pytest.raises(MfbError) as ei:
+        moe.encode_layer(lw, x, torch.empty_like(x))
+    assert ei.value.code == L.ERR_CAPACITY
+    assert moe.lib.mfb_launch_count() == before
+    assert moe.device_status() == 0
+
+
+@pytest.mark.parametrize("T", [1, 8, 19, 64])
+def test_fp32_partial_rows_of_the_fast_path_match_the_oracle(T):
+    """The decode fast path judged below the output rounding: its fp32 down-projection rows per (token, rank slot)
+    against the oracle's per-pair rows.  What remains is the fp16 rounding of the hidden activations (the reference
+    stores them as fp16 too, half an ulp is 4.9e-4 relative): bound 8e-4, well under the layer tolerance."""
+    import torch
+    from mference_b200.moe import MoE
+    d, f, E, K = 2048, 512, 24, 8
+    W = O.LayerWeights(d, f, E, K)
+    x = make_x("x.partial", T, d)
+    idx, w = _route(W, x)
+    y, moe, lw, _ = _run_decode(W, x, idx, w)
+    part = moe.partial_rows(T).cpu().numpy()            # [T, K + 1, d]
+    pairs = np.zeros(T * K, dtype=O.PAIR_DTYPE)
+    for t in range(T):
+        for r in range(K):
+            pairs[t * K + r] = (t, idx[t, r], r, 0)
+    ref = O.pair_partials(W, x, O.DT_BF16, pairs).reshape(T, K, d)   # the routed slots; slot K is the shared expert's
+    assert moe.device_status() == 0
+    worst = max(O.rel_l2(part[t, r], ref[t, r]) for t in range(T) for r in range(K))
+    assert worst <= 8e-4, worst
+
+
+@pytest.mark.parametrize("T", [1, 8, 64])
+def test_fused_stack_kernel_on_the_headline_shape(T):
+    """256 experts, top-8 + shared, hidden 2048 / intermediate 512 - the benchmark's layer shape and work split (about
+    9 / 58 / 223 expert groups per layer): the fused kernel against the layer-by-layer launches bit for bit, chained
+    and with separate rows per layer, and sampled rows against the oracle."""
+    import torch
+    from mference_b200.moe import MoE, synth_layer, synth_normal
+    from mference_b200 import DT_BF16
+    d, f, E, K, NL = 2048, 512, 256, 8, 4
+    layers = [synth_layer(ROOT, l, d, f, E) for l in range(NL)]
+    moe = MoE(d, f, E, K, max_tokens=T)
+    stack = moe.make_stack(layers)
+    h0 = synth_normal(ROOT, "x.headline", T * d, dtype=DT_BF16).view(T, d)
+    a = h0.clone()
+    moe.encode_stack(stack, a)
+    b = h0.clone()
+    for lw in layers:
+        nxt = torch.empty_like(b)
+        moe.encode_layer(lw, b, nxt)
+        b = nxt
+    assert moe.device_status() == 0
+    assert torch.isfinite(a.float()).all()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    rows = synth_normal(ROOT, "rows.headline", NL * T * d, dtype=DT_BF16).view(NL, T, d)
+    c = rows.clone()
+    moe.encode_stack_rows(stack, c)
+    assert moe.device_status() == 0
+    idx = torch.empty((T, K), dtype=torch.int32, device="cuda")
+    w = torch.empty((T, K), dtype=torch.float16, device="cuda")
+    for l, lw in enumerate(layers):
+        ref = torch.empty_like(rows[l])
+        moe.encode_layer(lw, rows[l], ref)
+        assert torch.equal(c[l].view(torch.int16), ref.view(torch.int16)), l
+        # oracle on up to eight rows of this layer, teacher-forced on the kernel's own normalised rows and routes
+        xn = torch.empty_like(rows[l])
+        moe.encode_rmsnorm(rows[l], xn, lw.norm_w)
+        moe.encode_router(xn, lw, idx, w)
+        sample = sorted(set(np.linspace(0, T - 1, num=min(T, 8)).astype(int).tolist()))
+        xn_bits = xn.view(torch.int16).cpu().numpy().view(np.uint16)[sample]
+        idx_h = idx.cpu().numpy().view(np.uint32)[sample]
+        w_h = w.view(torch.int16).cpu().numpy().view(np.uint16)[sample]
+        W = O.LayerWeights(d, f, E, K, layer=l, experts=sorted(set(idx_h.reshape(-1).tolist())))
+        lg = O.router_logits(xn_bits, O.DT_BF16, W.router)
+        idx_o, w_o = O.topk_softmax(lg, K)
+        assert np.array_equal(idx_o, idx_h)
+        res = rows[l].float().cpu().numpy()[sample]
+        want = O.moe_layer(W, xn_bits, O.DT_BF16, idx_h, w_h, res)
+        got = c[l].float().cpu().numpy()[sample]
+        for i in range(len(sample)):
+            assert O.rel_l2(got[i], want[i]) <= TOL_REL_L2, (l, sample[i], O.rel_l2(got[i], want[i]))
+    assert moe.device_status() == 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_handle_stays_usable():
+    """One CTA waits about a millisecond on a barrier nothing arrives at: the kernel returns, the status word carries
+    the time-out, reading it clears it, and the next decode call on the same handle is exact again."""
+    import torch
+    from mference_b200 import _lib as L
+    W = O.LayerWeights(512, 256, 8, 2)
+    x = make_x("x.wait", 3, 512)
+    idx, w = _route(W, x)
+    y0, moe, lw, (xd, idxd, wd, _) = _run_decode(W, x, idx, w)
+    assert moe.device_status() == 0
+    moe.selftest_wait(2_000_000)
+    torch.cuda.synchronize()
+    assert moe.device_status() == 1          # STATUS_MBAR_TIMEOUT, through MFB_ERR_DEVICE_STATUS
+    assert moe.device_status() == 0          # cleared by the read
+    y1 = torch.empty_like(xd)
+    moe.encode_decode(lw, xd, idxd, wd, y1)
+    torch.cuda.synchronize()
+    assert np.array_equal(y1.float().cpu().numpy(), y0)
+    assert moe.device_status() == 0

@@ -190,3 +190,36 @@ def test_ragged_continuous_batch_mix_full_size():
     y_gen = _prefill_layer(d, f, E, K, xs.shape[0], 4, 4, False, xs, layer, generic=True)
     err = float((y[sample].float() - y_gen.float()).norm() / y_gen.float().norm())
     assert err <= TOL_REL_L2, err
+
+
+def test_tensor_core_layer_prefill_without_a_shared_expert():
+    """A layer with no shared expert through the tensor-core layer call: no rows are gathered behind the routed pairs
+    (the grouping does not append any), and the result equals the generic kernels'."""
+    import torch
+    from mference_b200.moe import MoE
+    d, f, E, K, T = 512, 512, 8, 2, 70
+    W = O.LayerWeights(d, f, E, K, shared=False)
+    h = make_x("h.noshared", T, d, std=2.0)
+    lw = upload_layer(W)
+    assert lw.shared_blob is None
+    hd = to_dev16(h, O.DT_BF16)
+    tc = MoE(d, f, E, K, shared_bits=0, max_tokens=T, tensor_core_prefill=True)
+    # poison the tail of the arena's sort scratch: stale entries there must never be dereferenced
+    tc.encode_layer_prefill(upload_layer(O.LayerWeights(d, f, E, K, shared=False, layer=1)), hd, torch.empty_like(hd))
+    out_tc = torch.empty_like(hd)
+    tc.encode_layer_prefill(lw, hd, out_tc)
+    assert tc.device_status() == 0
+    gen = MoE(d, f, E, K, shared_bits=0, max_tokens=T)
+    out_gen = torch.empty_like(hd)
+    gen.encode_layer(lw, hd, out_gen)
+    a, b = out_tc.float().cpu().numpy(), out_gen.float().cpu().numpy()
+    assert np.isfinite(a).all()
+    assert O.rel_l2(a, b) <= TOL_REL_L2
+    # and against the oracle, teacher-forced on the kernel's normalised rows
+    xn = torch.empty_like(hd)
+    tc.encode_rmsnorm(hd, xn, lw.norm_w)
+    xn_bits = xn.view(torch.int16).cpu().numpy().view(np.uint16)
+    lg = O.router_logits(xn_bits, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, K)
+    ref = O.moe_layer(W, xn_bits, O.DT_BF16, idx, w, O.bf16_to_f32(h))
+    assert O.rel_l2(a, ref) <= TOL_REL_L2

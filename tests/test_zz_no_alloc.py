@@ -38,6 +38,15 @@ def test_static_router_matches_handle_router_twice(d, num_experts, top_k):
         torch.cuda.synchronize()
         assert torch.equal(idx, ref_idx)
         assert torch.equal(w.view(torch.int16), ref_w.view(torch.int16))
+        # and directly against the CPU oracle: same experts in the same rank order
+        import numpy as np
+        from oracle import oracle as O
+        x_bits = x.view(torch.int16).cpu().numpy().view(np.uint16)
+        rw_bits = layer.router_w.view(torch.int16).cpu().numpy().view(np.uint16)
+        o_idx, o_w = O.topk_softmax(O.router_logits(x_bits, O.DT_BF16, rw_bits), top_k)
+        assert np.array_equal(idx.cpu().numpy().view(np.uint32), o_idx)
+        got_w = w.float().cpu().numpy()
+        assert np.abs(got_w - O.f16_to_f32(o_w)).max() <= 1e-3
 
 
 def test_static_router_rejects_more_rows_than_the_scratch_holds():
