@@ -345,10 +345,14 @@ class DecodeBench:
             # SM-cycle counters of CTA 0, per layer: a computing warp's wait for a stage and its work on it, per FFN
             # phase; the copy-issuing warp's time spent issuing (mostly waiting for a free stage)
             cyc = tr[NL:NL + 17].cpu().numpy().astype("float64") / NL
+            cw = [r for r in range(16) if cyc[r, 1] > 0 or cyc[r, 3] > 0]     # the computing warps (8 or 16)
+            cp = 16 if len(cw) == 16 else 8                                     # the copy-issuing warp follows them
             phase_us["cta0_kcycles_per_layer"] = {
-                "phase1_wait": round(float(cyc[:8, 0].mean() / 1e3), 2), "phase1_compute": round(float(cyc[:8, 1].mean() / 1e3), 2),
-                "phase2_wait": round(float(cyc[:8, 2].mean() / 1e3), 2), "phase2_compute": round(float(cyc[:8, 3].mean() / 1e3), 2),
-                "phase1_copy_issue": round(float(cyc[8, 0] / 1e3), 2), "phase2_copy_issue": round(float(cyc[8, 2] / 1e3), 2)}
+                "computing_warps": len(cw),
+                "phase1_wait": round(float(cyc[cw, 0].mean() / 1e3), 2), "phase1_compute": round(float(cyc[cw, 1].mean() / 1e3), 2),
+                "phase2_wait": round(float(cyc[cw, 2].mean() / 1e3), 2), "phase2_compute": round(float(cyc[cw, 3].mean() / 1e3), 2),
+                "phase1_total": round(float(cyc[cw, 5].mean() / 1e3), 2), "phase2_total": round(float(cyc[cw, 7].mean() / 1e3), 2),
+                "phase1_copy_issue": round(float(cyc[cp, 0] / 1e3), 2), "phase2_copy_issue": round(float(cyc[cp, 2] / 1e3), 2)}
 
         times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
         if world > 1:
