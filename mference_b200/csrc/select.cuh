@@ -12,24 +12,33 @@ __device__ __forceinline__ float sqrtsoftplus(float x) {
 }
 
 // One warp per token row.  Blocked ownership as in router_topk_select_k8_par (moe.metal:262-345): lane L owns
-// experts [L*per, L*per + per); every round takes a lane-local strict-greater ascending maximum and a
-// shuffle argmax that prefers the lower index on equal scores, which reproduces the serial insertion scan
-// (strictly greater wins, equal keeps the earlier expert).  The weight tail runs on lane 0 in the serial order.
+// experts [L*per, L*per + per); every round takes a lane-local strict-greater ascending maximum (the lowest index
+// among equal scores of the lane) and a warp-wide maximum that prefers the lower index on equal scores, which
+// reproduces the serial insertion scan (strictly greater wins, equal keeps the earlier expert).  The warp-wide step
+// is two hardware reductions: the maximum of an order-preserving integer image of the scores, then the minimum
+// expert index among the lanes that hold it.  The weight tail runs in the serial rank order.
 constexpr int SEL_MAX_PER_LANE = MFB_MAX_EXPERTS / 32;
 constexpr uint32_t SEL_NONE = 0xFFFFFFFFu;
 
-// Selection for one row by one warp; lane r < top_k returns the rank-r expert and its fp16 weight bits.
-__device__ __forceinline__ void select_row(const float* __restrict__ lg, uint32_t num_experts, uint32_t top_k, int mode,
-                                           const __nv_bfloat16* __restrict__ per_expert_scale,
-                                           const float* __restrict__ correction_bias, float route_scale, uint32_t lane,
-                                           uint32_t& out_expert, uint16_t& out_weight) {
-    const uint32_t per = (num_experts + 31) / 32, base = lane * per;
-    float ch[SEL_MAX_PER_LANE];
+// Order-preserving map of fp32 (no NaN) onto uint32: a < b  <=>  key(a) < key(b); -0 and +0 differ, which the
+// equality test below must not see, so -0 is folded onto +0 first.
+__device__ __forceinline__ uint32_t sel_key(float v) {
+    const uint32_t b = __float_as_uint(v + 0.0f);   // -0 + 0 = +0
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+template <int PER>
+__device__ __forceinline__ void select_row_per(const float* __restrict__ lg, uint32_t num_experts, uint32_t top_k, int mode,
+                                               const __nv_bfloat16* __restrict__ per_expert_scale,
+                                               const float* __restrict__ correction_bias, float route_scale, uint32_t lane,
+                                               uint32_t& out_expert, uint16_t& out_weight) {
+    const uint32_t base = lane * PER;
+    float ch[PER];
 #pragma unroll
-    for (int j = 0; j < SEL_MAX_PER_LANE; ++j) {
+    for (int j = 0; j < PER; ++j) {
         const uint32_t e = base + j;
         float v = -INFINITY;
-        if ((uint32_t)j < per && e < num_experts) {
+        if (e < num_experts) {
             v = lg[e];
             if (mode == MFB_ROUTER_SQRTSOFTPLUS) v = sqrtsoftplus(v) + (correction_bias ? correction_bias[e] : 0.0f);
         }
@@ -42,23 +51,19 @@ __device__ __forceinline__ void select_row(const float* __restrict__ lg, uint32_
         float bv = -INFINITY;
         uint32_t bi = SEL_NONE;
 #pragma unroll
-        for (int j = 0; j < SEL_MAX_PER_LANE; ++j)
+        for (int j = 0; j < PER; ++j)
             if (!(taken & (1u << j)) && ch[j] > bv) { bv = ch[j]; bi = base + j; }
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_down_sync(0xFFFFFFFFu, bv, off);
-            const uint32_t oi = __shfl_down_sync(0xFFFFFFFFu, bi, off);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        bi = __shfl_sync(0xFFFFFFFFu, bi, 0);
-        bv = __shfl_sync(0xFFFFFFFFu, bv, 0);
-        if (bi != SEL_NONE && bi >= base && bi < base + per) taken |= 1u << (bi - base);
+        const uint32_t best_key = __reduce_max_sync(0xFFFFFFFFu, bi == SEL_NONE ? 0u : sel_key(bv));
+        const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, (bi != SEL_NONE && sel_key(bv) == best_key) ? bi : SEL_NONE);
+        if (win != SEL_NONE && win >= base && win < base + PER) taken |= 1u << (win - base);
         if (lane == r) {
             // fewer experts than top_k: the serial scan leaves index 0 with score -inf (moe.metal:321-330)
-            my_idx = bi == SEL_NONE ? 0u : bi;
-            my_score = bi == SEL_NONE ? -INFINITY : bv;
+            my_idx = win == SEL_NONE ? 0u : win;
+            const uint32_t kb = (best_key & 0x80000000u) ? (best_key & 0x7FFFFFFFu) : ~best_key;
+            my_score = win == SEL_NONE ? -INFINITY : __uint_as_float(kb);
         }
     }
-    // weight tail, serial order on values gathered to lane 0 (top_k <= 16 < 32)
+    // weight tail, serial order on values gathered from the rank lanes (top_k <= 16 < 32)
     float score = my_score;
     if (mode == MFB_ROUTER_SQRTSOFTPLUS) score = lane < top_k ? sqrtsoftplus(lg[my_idx]) : 0.0f;
     const float max_s = __shfl_sync(0xFFFFFFFFu, score, 0);
@@ -78,6 +83,17 @@ __device__ __forceinline__ void select_row(const float* __restrict__ lg, uint32_
         out_expert = my_idx;
         out_weight = __half_as_ushort(__float2half_rn(wgt));
     }
+}
+
+// Selection for one row by one warp; lane r < top_k returns the rank-r expert and its fp16 weight bits.
+__device__ __forceinline__ void select_row(const float* __restrict__ lg, uint32_t num_experts, uint32_t top_k, int mode,
+                                           const __nv_bfloat16* __restrict__ per_expert_scale,
+                                           const float* __restrict__ correction_bias, float route_scale, uint32_t lane,
+                                           uint32_t& out_expert, uint16_t& out_weight) {
+    const uint32_t per = (num_experts + 31) / 32;
+    if (per <= 4) select_row_per<4>(lg, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, lane, out_expert, out_weight);
+    else if (per <= 8) select_row_per<8>(lg, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, lane, out_expert, out_weight);
+    else select_row_per<SEL_MAX_PER_LANE>(lg, num_experts, top_k, mode, per_expert_scale, correction_bias, route_scale, lane, out_expert, out_weight);
 }
 
 }  // namespace mfb
