@@ -134,19 +134,20 @@ def cpu_port_tokens_per_s(batch: int, budget_s: float, layers: int = LAYERS):
     return tok_s, O.num_threads(), f"1 of {layers} layers x {rows} token rows x {reps} repeats, scaled x{layers}"
 
 
-def cpu_port_prefill_tokens_per_s(sample_rows: int, budget_s: float, zipf: bool):
+def cpu_port_prefill_tokens_per_s(sample_rows: int, budget_s: float, zipf: bool, shape=None):
     """CPU port of the reference's scalar prefill path on a sample of the batch's rows: router, grouping by expert,
     the per-pair scalar int4 loop (oracle mfbo_pair_partials, the restatement of the reference's test-local loop) and
     the token-major weighted reduce.  Tokens/s of the sample; the cost per token row does not depend on the batch."""
     import numpy as np
     from oracle import oracle as O
     T = sample_rows
-    W0 = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=[])
+    D, F, E, K, bits, sbits = shape or (2048, 512, 256, 8, 4, 4)   # layer shape (default: the Q layer)
+    W0 = O.LayerWeights(D, F, E, K, bits=bits, shared_bits=sbits, root=ROOT_SEED, layer=0, experts=[])
     x = O.fill_normal(O.seed_for_label(ROOT_SEED, "x.prefill.cpu"), T * D, dtype=O.DT_BF16).reshape(T, D)
     bias = zipf_logit_bias(E) if zipf else None
     lg = O.router_logits(x, O.DT_BF16, W0.router, logit_bias=bias)
     idx, w = O.topk_softmax(lg, K)
-    W = O.LayerWeights(D, F, E, K, root=ROOT_SEED, layer=0, experts=sorted(set(idx.reshape(-1).tolist())))
+    W = O.LayerWeights(D, F, E, K, bits=bits, shared_bits=sbits, root=ROOT_SEED, layer=0, experts=sorted(set(idx.reshape(-1).tolist())))
     pairs = np.zeros(T * K, dtype=O.PAIR_DTYPE)
     pairs["token"] = np.repeat(np.arange(T), K)
     pairs["expert"] = idx.reshape(-1)
@@ -588,103 +589,184 @@ def run_prefill(args):
         sys.exit("bench: device status word set")
 
 
+VD, VF, VE, VK, VT = 4096, 2048, 256, 6, 2048      # configs[3]: DeepSeek-V4-Flash-shaped layer, 2-bit experts + 4-bit shared
+
+
+def v_layer(first_expert, n_experts):
+    """Seeded V-shape layer holding experts [first_expert, first_expert + n_experts) of the pool, the router and the
+    shared expert (the same bytes on every rank for the same expert)."""
+    import torch
+    from mference_b200 import _lib as L
+    from mference_b200.moe import MoELayerWeights, _ptr, _stream, expert_layout, synth_normal
+    lib = L.load()
+    off, blob = expert_layout(2, VD, VF)
+    stride = (blob + 255) // 256 * 256
+    pool = torch.empty(n_experts * stride, dtype=torch.uint8, device="cuda")
+    # the generator places expert e at base + e * stride: hand it the base of the (virtual) full pool, of which this
+    # tensor is the slice starting at first_expert
+    import ctypes
+    base = ctypes.c_void_p(pool.data_ptr() - first_expert * stride)
+    L.check(lib.mfb_synth_expert_pool(_stream(), ROOT_SEED, 0, first_expert, n_experts, 0, 2, L.DT_F16, VD, VF, base, stride))
+    soff, sblob = expert_layout(4, VD, VF)
+    shared = torch.empty(sblob, dtype=torch.uint8, device="cuda")
+    L.check(lib.mfb_synth_expert_pool(_stream(), ROOT_SEED, 0, 0, 1, 1, 4, L.DT_F16, VD, VF, _ptr(shared), 0))
+    router = synth_normal(ROOT_SEED, "L0.router", VE * VD, std=0.02, dtype=L.DT_BF16).view(VE, VD)
+    return MoELayerWeights(router_w=router, pool=pool, slot_stride=stride, routed_off=off, shared_blob=shared, shared_off=soff,
+                           norm_w=torch.ones(VD, dtype=torch.bfloat16, device="cuda"))
+
+
 def ep_case(world, rank, local, steps, warmup):
-    return None
-
-
-def run_ep(args):
-    """The prefill layer of configs[2] with the experts block-sharded over the ranks: tokens split evenly (strong
-    scaling: the total stays --tokens), one all-to-all each way per layer."""
+    """configs[3]: the V-shape layer (hidden 4096, intermediate 2048, 256 experts top-6, 2-bit experts + 4-bit shared) over
+    2048 tokens, experts block-sharded over the ranks, tokens split evenly (strong scaling), dispatch and combine as
+    one-sided peer stores over NVLink.  Returns the record (on rank 0; None elsewhere)."""
     import copy
     import torch
     import torch.distributed as dist
     from mference_b200 import _lib as L
-    from mference_b200.ep import DeviceOps, ExpertParallelLayer
-    from mference_b200.moe import synth_layer, synth_normal
+    from mference_b200.ep import DeviceOps, PeerExpertParallelLayer
+    from mference_b200.moe import MoE, synth_normal
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local)) if world > 1 else \
-        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1, device_id=torch.device("cuda", local))
     lib = L.load()
-    T = args.tokens // world
-    full = synth_layer(ROOT_SEED, 0, D, F, E)
-    full.logit_bias = torch.from_numpy(zipf_logit_bias(E)).cuda()
-    local_E = E // world
-    mine = copy.copy(full)
-    mine.pool = full.pool[rank * local_E * full.slot_stride:(rank + 1) * local_E * full.slot_stride]
-    mine.shared_blob = None
-    shared = copy.copy(full)
-    shared.pool, shared.slot_stride, shared.routed_off = full.shared_blob, full.shared_blob.numel(), full.shared_off
-    shared.shared_blob = None
-    # a skewed router can send every pair of every rank to one rank: size the receive side for that
-    ops = DeviceOps(D, F, E, K, world, max_tokens=T, max_recv_rows=args.tokens * K)
-    layer = ExpertParallelLayer(ops, world)
-    xs = [synth_normal(ROOT_SEED + rank, f"x.ep.{i}", T * D, dtype=L.DT_BF16).view(T, D) for i in range(N_INPUTS)]
+    T = VT // world
+    local_E = VE // world
+    mine = v_layer(rank * local_E, local_E)          # this rank's slice of the pool + the replicated parts
+    replicated = copy.copy(mine)                     # router, norm (the pool field is not used on the home side)
+    local_w = copy.copy(mine)
+    local_w.shared_blob = None
+    shared_w = copy.copy(mine)
+    shared_w.pool, shared_w.slot_stride, shared_w.routed_off = mine.shared_blob, mine.shared_blob.numel(), mine.shared_off
+    shared_w.shared_blob = None
+    ops = DeviceOps(VD, VF, VE, VK, world, max_tokens=T, max_recv_rows=world * T * VK, bits=2, shared_bits=4)
+    layer = PeerExpertParallelLayer(ops, rank, world, T)
+    xs = [synth_normal(ROOT_SEED, f"x.ep.{i}", VT * VD, dtype=L.DT_BF16).view(VT, VD)[rank * T:(rank + 1) * T].contiguous()
+          for i in range(N_INPUTS)]
     y = torch.empty_like(xs[0])
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        layer.forward(full, mine, shared, xs[i % N_INPUTS], y)
+    for i in range(warmup):
+        layer.forward(replicated, local_w, shared_w, xs[i % N_INPUTS], y)
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = lib.mfb_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(args.steps):
-        layer.forward(full, mine, shared, xs[i % N_INPUTS], y)
+    for i in range(steps):
+        layer.forward(replicated, local_w, shared_w, xs[i % N_INPUTS], y)
     e1.record()
     barrier()
     launches = lib.mfb_launch_count() - launches0
     ms_dev = e0.elapsed_time(e1)
+    # stage breakdown of one more call
+    marks = []
+    layer.forward(replicated, local_w, shared_w, xs[0], y, marks=marks)
+    barrier()
+    stage_us = {b[0]: round(a[1].elapsed_time(b[1]) * 1e3, 1) for a, b in zip(marks[:-1], marks[1:])}
+    y0 = y.clone()
+    status, recv_counts = layer.ex.status(with_counts=True)
+    status |= ops.expert.device_status() | ops.shared.device_status() | ops.home.device_status()
     # end to end with host rows
     host_in = [t.cpu().pin_memory() for t in xs]
     host_out = torch.empty_like(host_in[0]).pin_memory()
     dev_in = torch.empty_like(xs[0])
     barrier()
     e0.record()
-    for i in range(args.steps):
+    for i in range(steps):
         dev_in.copy_(host_in[i % N_INPUTS], non_blocking=True)
-        layer.forward(full, mine, shared, dev_in, y)
+        layer.forward(replicated, local_w, shared_w, dev_in, y)
         host_out.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e1.record()
     barrier()
-    clocks = sampler.stop()
-    t = torch.tensor([ms_dev, e0.elapsed_time(e1), float(sum(layer.last_recv_counts))], dtype=torch.float64, device="cuda")
-    tmax = t.clone()
-    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    recv = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
-    dist.all_gather(recv, t[2:3].clone())
+    t = torch.tensor([ms_dev, e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    recv_all = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
+    dist.all_gather(recv_all, torch.tensor([float(sum(recv_counts))], dtype=torch.float64, device="cuda"))
+    rec = None
     if rank == 0:
-        ms = float(tmax[0]) / args.steps
-        total_tokens = T * world
-        flops = 2 * 3 * D * F * (total_tokens * K + total_tokens) + 2 * total_tokens * D * E
+        # one GPU, the whole batch and the whole pool: the time strong scaling is measured against, and the check
+        full = v_layer(0, VE)
+        one = MoE(VD, VF, VE, VK, bits=2, shared_bits=4, max_tokens=VT, tensor_core_prefill=True)
+        x_all = synth_normal(ROOT_SEED, "x.ep.0", VT * VD, dtype=L.DT_BF16).view(VT, VD)
+        y_all = torch.empty_like(x_all)
+        for _ in range(3):
+            one.encode_layer_prefill(full, x_all, y_all)
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(steps):
+            one.encode_layer_prefill(full, x_all, y_all)
+        s1.record()
+        torch.cuda.synchronize()
+        ms_one = s0.elapsed_time(s1) / steps
+        matches = bool(torch.equal(y0, y_all[:T]))
+        status |= one.device_status()
+        ms = float(t[0]) / steps
+        flops = 2 * 3 * VD * VF * (VT * VK + VT) + 2 * VT * VD * VE
         _, tf_peak, peak_kind = measured_peaks()
         achieved = flops / (ms * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": "moe_prefill_tokens_per_s", "value": total_tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
-            "config": {"workload": f"configs[2] sharded: prefill gather-QMM, {total_tokens} tokens over {world} rank(s), experts "
-                                   f"block-sharded ({local_E} per rank), NCCL all-to-all dispatch and combine",
-                       "tokens_per_rank": T, "pairs_received_per_rank": [int(r.item()) for r in recv],
-                       "parallelism": f"ep{world}", "l2": f"{N_INPUTS} input sets cycled"},
+        pairs_remote = VT * VK * (world - 1) / world
+        try:
+            from oracle import oracle as O
+            O.set_num_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1 to its ranks
+        except Exception:
+            pass
+        tok_s, cores, sample = cpu_port_prefill_tokens_per_s(16, 5.0, zipf=False, shape=(VD, VF, VE, VK, 2, 4))
+        cpu = {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        rec = {
+            "metric": "moe_prefill_tokens_per_s", "value": VT / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "n_gpus": world,
+            "scaling": "strong",
+            "workload": f"configs[3]: DeepSeek-V4-Flash-shaped layer (hidden {VD}, intermediate {VF}, {VE} experts top-{VK} + 1 shared, 2-bit "
+                        f"experts, 4-bit shared), {VT} tokens over {world} ranks, {local_E} experts per rank, dispatch and combine as "
+                        f"one-sided peer stores over NVLink",
+            "one_gpu_ms_per_step": ms_one, "speedup_vs_one_gpu": ms_one / ms, "strong_scaling_efficiency": ms_one / ms / world,
+            "pairs_received_per_rank": [int(r.item()) for r in recv_all],
+            "dispatch_bytes_per_step": int(pairs_remote * VD * 2), "combine_bytes_per_step": int(pairs_remote * VD * 4),
+            "stage_us_rank0": stage_us,
+            "output_matches_single_gpu_layer": matches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak * world, "unit": "TFLOP/s",
                          "frac": achieved / (tf_peak * world), "peak_kind": peak_kind, "traffic": None,
-                         "kernel": "whole layer incl. the two exchanges"},
-            "cpu_baseline": None,
-            "e2e": {"value": total_tokens / (float(tmax[1]) / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": T * D * 2 * world, "d2h_bytes_per_step": T * D * 2 * world},
-            "gpu_launches": int(launches), "clocks": clocks,
-        }))
+                         "kernel": "whole layer incl. both exchanges", "algorithmic_flops_per_step": flops},
+            "cpu_baseline": cpu,
+            "e2e": {"value": VT / (float(t[1]) / steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": VT * VD * 2,
+                    "d2h_bytes_per_step": VT * VD * 2},
+            "gpu_launches": int(launches), "device_status": int(status),
+        }
+    barrier()
+    return rec
+
+
+def run_ep(args):
+    """--workload ep: configs[3] alone (under torchrun with --gpus N ranks; also runs with one rank)."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29577", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    sampler = ClockSampler(local)
+    sampler.start()
+    rec = ep_case(world, rank, local, args.steps, args.warmup)
+    clocks = sampler.stop()
+    if rank == 0:
+        line = {"metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+                "config": {k: rec[k] for k in ("workload", "one_gpu_ms_per_step", "speedup_vs_one_gpu", "strong_scaling_efficiency",
+                                               "pairs_received_per_rank", "dispatch_bytes_per_step", "combine_bytes_per_step",
+                                               "stage_us_rank0", "output_matches_single_gpu_layer")}}
+        line["config"]["parallelism"] = f"ep{world}"
+        line["config"]["l2"] = f"{N_INPUTS} input sets cycled; 2 GB of expert weights"
+        for k in ("roofline", "cpu_baseline", "e2e", "gpu_launches", "device_status"):
+            line[k] = rec[k]
+        line["clocks"] = clocks
+        print(json.dumps(line))
     dist.destroy_process_group()
 
 

@@ -266,6 +266,14 @@ int32_t mfb_moe_group_host(const mfb_pair* pairs, int64_t n_pairs, int64_t query
 int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                                 uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
                                 const uint32_t* n_groups, float* partial);
+/* The same grouped FFN with one destination address per result row instead of a dense array: the row of (token, rank)
+ * is written to row_dest[token * top_k + rank] (device array of device-visible addresses, e.g. a peer GPU's buffer
+ * mapped with CUDA IPC; a NULL entry drops the row).  Entries of `sorted` behind the last group are ignored.  Used by
+ * the expert-parallel layer, whose results go straight to the home rank; tensor-core path only.  No counterpart in the
+ * reference (single device); the per-row arithmetic is that of PrefillGroupedRoutedMoE.encodeStreamedBatched. */
+int32_t mfb_moe_prefill_grouped_rows(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                     uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
+                                     const uint32_t* n_groups, float* const* row_dest);
 /* h2[t,:] = sum_r w[t,r] * partial[t,r,:] in rank order (+ residual).  Replaces
  * PrefillMoE.encodeReduceTokenMajor (Sources/Mference/Kernels/Prefill/MoE/PrefillMoE.swift:11-38). */
 int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w, uint32_t n_tokens,
@@ -328,6 +336,37 @@ int32_t mfb_ep_pack(void* stream, const void* x, uint32_t ldx, uint32_t d, const
 int32_t mfb_ep_combine(void* stream, const float* recv, const uint32_t* inv, const uint16_t* route_w,
                        const float* shared_partial, const void* residual, void* y, uint32_t n_tokens, uint32_t top_k,
                        uint32_t d, uint32_t x_dtype);
+
+/* One-sided exchange over peer memory (NVLink) instead of a collective library: every rank's receive and result
+ * buffers are plain device allocations exported with CUDA IPC; dispatch stores the packed rows straight into the
+ * destination ranks' buffers, the expert side's grouped FFN stores each result row straight into the home rank's
+ * buffer (mfb_moe_prefill_grouped_rows), and arrival is signalled by epoch-valued flags that the other side polls
+ * with a clock limit (a time-out sets the status word read by mfb_ep_status; nothing hangs).  No host
+ * synchronisation and no collective on the data path.  max_pairs = tokens per rank * top_k, equal on all ranks.
+ * Set-up: mfb_ep_create on every rank, mfb_ep_export (4 IPC handles of 64 bytes), all-gather the handles by any
+ * means, mfb_ep_import (world * 4 handles, rank-major).  Per layer, on one stream:
+ *   mfb_ep_dispatch   plan by destination, pack, peer stores, flags; inv[token * top_k + slot] = send position
+ *   mfb_ep_receive    waits for every source; returns the received rows [world * max_pairs, d], their expert ids relative
+ *                     to this rank's first expert (0xFFFFFFFF = no row) and the destination address of each result row
+ *   ... mfb_moe_group + mfb_moe_prefill_grouped_rows on the received rows (top_k = 1) ...
+ *   mfb_ep_return     tells every home rank that its results are in place
+ *   mfb_ep_results    waits for every expert side; returns this rank's fp32 result rows in send order for mfb_ep_combine
+ * One call sequence at a time per handle; the next dispatch may be enqueued right after mfb_ep_combine. */
+typedef struct mfb_ep mfb_ep;
+#define MFB_EP_HANDLE_BYTES 256   /* what mfb_ep_export writes: 4 IPC handles */
+int32_t mfb_ep_create(uint32_t rank, uint32_t world, uint32_t d, uint32_t max_pairs, mfb_ep** out);
+int32_t mfb_ep_destroy(mfb_ep* ep);
+int32_t mfb_ep_export(mfb_ep* ep, void* handles);
+int32_t mfb_ep_import(mfb_ep* ep, const void* all_handles);
+int32_t mfb_ep_dispatch(mfb_ep* ep, void* stream, const void* x, uint32_t ldx, const uint32_t* idx, uint32_t n_tokens,
+                        uint32_t top_k, uint32_t num_experts, uint32_t* inv);
+int32_t mfb_ep_receive(mfb_ep* ep, void* stream, const void** rows, const uint32_t** row_expert, float* const** row_dest,
+                       uint32_t* n_rows);
+int32_t mfb_ep_return(mfb_ep* ep, void* stream);
+int32_t mfb_ep_results(mfb_ep* ep, void* stream, const float** ret);
+/* Reads and clears the exchange's status word (synchronises the stream); counts_host (optional, world entries) receives
+ * the number of rows each source rank sent in the last call. */
+int32_t mfb_ep_status(mfb_ep* ep, void* stream, uint32_t* status, int32_t* counts_host);
 
 /* ---- glue ---------------------------------------------------------------------------------------------- */
 

@@ -98,6 +98,16 @@ SIGNATURES = {
     "mfb_ep_plan": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _V, _V]),
     "mfb_ep_pack": (_I32, [_V, _V, _U32, _U32, _V, _U32, _U32, _V]),
     "mfb_ep_combine": (_I32, [_V, _V, _V, _V, _V, _V, _V, _U32, _U32, _U32, _U32]),
+    "mfb_ep_create": (_I32, [_U32, _U32, _U32, _U32, C.POINTER(_V)]),
+    "mfb_ep_destroy": (_I32, [_V]),
+    "mfb_ep_export": (_I32, [_V, _V]),
+    "mfb_ep_import": (_I32, [_V, _V]),
+    "mfb_ep_dispatch": (_I32, [_V, _V, _V, _U32, _V, _U32, _U32, _U32, _V]),
+    "mfb_ep_receive": (_I32, [_V, _V, C.POINTER(_V), C.POINTER(_V), C.POINTER(_V), C.POINTER(_U32)]),
+    "mfb_ep_return": (_I32, [_V, _V]),
+    "mfb_ep_results": (_I32, [_V, _V, C.POINTER(_V)]),
+    "mfb_ep_status": (_I32, [_V, _V, C.POINTER(_U32), _V]),
+    "mfb_moe_prefill_grouped_rows": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, _V, _V]),
     "mfb_router_topk_static": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _U32, _U32, _U32, _V, _V, C.c_float, _V, _V]),
     "mfb_moe_decode": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, _V, _V]),
     "mfb_moe_experts": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, C.POINTER(_U32), _U32, _I32]),

@@ -623,6 +623,25 @@ extern "C" int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb
     return MFB_OK;
 }
 
+extern "C" int32_t mfb_moe_prefill_grouped_rows(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x,
+                                                uint32_t ldx, uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
+                                                const uint32_t* n_groups, float* const* row_dest) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, false);
+    if (rc) return rc;
+    MFB_REQUIRE(x && sorted && groups && n_groups && row_dest, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped_rows: NULL argument");
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped_rows: row stride smaller than d");
+    const mfb_moe_config& c = moe->cfg;
+    MFB_REQUIRE((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c), MFB_ERR_UNSUPPORTED_SHAPE,
+                "prefill_grouped_rows needs the tensor-core path (MFB_FLAG_PREFILL_TENSOR_CORE, d and f multiples of 512)");
+    if (n_tokens == 0) return MFB_OK;
+    const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
+    const uint32_t max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts);
+    return tc_grouped_ffn(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, sorted, groups, n_groups, max_groups, /*routed_only=*/true,
+                          nullptr, c.top_k, row_dest);
+}
+
 extern "C" int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w,
                                   uint32_t n_tokens, const void* residual, void* y) {
     int32_t rc = check_handle(moe, 0);

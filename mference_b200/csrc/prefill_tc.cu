@@ -66,6 +66,7 @@ struct TcParams {
     const uint32_t* tile_prefix2;  // the same for the 256-row token tiles of phase 2
     __half* acts16;                // [rows, f] hidden activations in sorted-pair order (phase 1 out, phase 2 in)
     float* partial;                // [token * slots + rank, d]
+    float* const* row_dest;        // optional: address of the result row of (token, rank) at [token * slots + rank] (NULL entry = drop)
     uint32_t slots;
     uint32_t* status;
 };
@@ -268,7 +269,7 @@ struct TcShared {
     uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base, abort;
     uint32_t tp[MFB_MAX_EXPERTS + 2];
-    uint32_t out_row[TC_TILE_N];   // phase 2: token * slots + rank of the current item's token columns
+    float* out_ptr[TC_TILE_N];     // phase 2: where the result row of each of the current item's token columns goes
 };
 
 template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
@@ -491,13 +492,15 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                 asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");   // the previous item's table is no longer read
                 for (uint32_t n = te; n < I.n; n += TC_EPI_WARPS * 32) {
                     const mfb_pair pr = P.sorted[I.pair_start + n];
-                    S.out_row[n] = pr.token * P.slots + pr.rank;
+                    const size_t slot = (size_t)pr.token * P.slots + pr.rank;
+                    S.out_ptr[n] = P.row_dest ? P.row_dest[slot] : P.partial + slot * P.d;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
             }
             if (!I.ok) {
                 if (PHASE == 2)   // a non-resident expert contributes nothing: clear its partial rows
-                    for (uint32_t n = col_par; n < I.n; n += COL_WAYS) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
+                    for (uint32_t n = col_par; n < I.n; n += COL_WAYS)
+                        if (S.out_ptr[n]) S.out_ptr[n][out_row] = 0.0f;
                 continue;
             }
             const uint32_t buf = 0, use = item & 1u;
@@ -530,11 +533,11 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                     }
                 } else {
                     const uint32_t live = min(32u, I.n - col0);
-                    float* out = P.partial + out_row;
 #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) {
                         if (i >= live) break;
-                        out[(size_t)S.out_row[col0 + i] * P.d] = v[i];
+                        float* out = S.out_ptr[col0 + i];
+                        if (out) out[out_row] = v[i];
                     }
                 }
             }
@@ -553,10 +556,17 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
 // Rows from n_routed on belong to the shared expert's group and follow its code width.  A thread converts sixteen
 // consecutive elements: two 16-byte loads, the permutation in registers, two 16-byte stores.
 __global__ void tc_gather_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx, uint32_t d,
-                                 const mfb_pair* __restrict__ sorted, uint32_t n_rows, uint32_t n_routed, uint32_t n_tokens,
+                                 const mfb_pair* __restrict__ sorted, const mfb_group* __restrict__ groups,
+                                 const uint32_t* __restrict__ n_groups, uint32_t n_rows, uint32_t n_routed, uint32_t n_tokens,
                                  uint32_t bits, uint32_t shared_bits, __half* __restrict__ xs16) {
     const uint32_t pos = blockIdx.x;
     if (pos >= n_rows) return;
+    {   // rows behind the last group are not part of the call (a routing table with dropped or masked entries)
+        const uint32_t ng = *n_groups;
+        if (ng == 0) return;
+        const mfb_group last = groups[ng - 1];
+        if (pos >= last.pair_start + last.pair_count) return;
+    }
     const uint32_t width = pos < n_routed ? bits : shared_bits;
     const uint32_t token = sorted[pos].token;
     if (token >= n_tokens) return;   // an entry no group refers to (a caller's list shorter than n_tokens * top_k)
@@ -668,7 +678,7 @@ void tc_release(mfb_moe* m) {
 
 int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                        uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups, const uint32_t* n_groups,
-                       uint32_t max_groups, bool routed_only, float* partial, uint32_t slots) {
+                       uint32_t max_groups, bool routed_only, float* partial, uint32_t slots, float* const* row_dest) {
     const mfb_moe_config& c = m->cfg;
     Arena& a = m->a;
     MFB_REQUIRE(a.xs16 && a.acts16, MFB_ERR_INVALID_ARGUMENT, "tensor-core path: the handle was created without MFB_FLAG_PREFILL_TENSOR_CORE");
@@ -685,11 +695,11 @@ int32_t tc_grouped_ffn(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, c
     P.scale_dtype = c.scale_dtype; P.activation = c.activation; P.limit = c.swiglu_limit;
     P.sorted = sorted; P.groups = groups; P.n_groups = n_groups;
     P.tile_prefix1 = st->prefix; P.tile_prefix2 = st->prefix + MFB_MAX_EXPERTS + 2;
-    P.acts16 = a.acts16; P.partial = partial; P.slots = slots; P.status = a.status;
+    P.acts16 = a.acts16; P.partial = partial; P.row_dest = row_dest; P.slots = slots; P.status = a.status;
 
     tc_tile_prefix_kernel<<<1, 32, 0, s>>>(groups, n_groups, st->prefix, st->prefix + MFB_MAX_EXPERTS + 2);
-    tc_gather_kernel<<<n_rows, 128, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, n_rows, n_tokens * c.top_k, n_tokens, c.bits,
-                                            c.shared_bits ? c.shared_bits : c.bits, a.xs16);
+    tc_gather_kernel<<<n_rows, 128, 0, s>>>(x, (int)c.x_dtype, ldx, c.d, sorted, groups, n_groups, n_rows, n_tokens * c.top_k, n_tokens,
+                                            c.bits, c.shared_bits ? c.shared_bits : c.bits, a.xs16);
     // upper bounds of the work items (the kernels read the exact counts from the prefix arrays)
     const uint32_t items1 = ((n_rows + tc_tile_n(1) - 1) / tc_tile_n(1) + max_groups) * (c.f / TC_M);
     const uint32_t items2 = ((n_rows + tc_tile_n(2) - 1) / tc_tile_n(2) + max_groups) * (c.d / TC_M);

@@ -1,5 +1,8 @@
-"""Expert parallelism over 2, 4 or 8 GPUs of one box: one process per GPU, ``torch.distributed`` (NCCL) for the two
-all-to-all exchanges of a layer, the library's kernels for everything else.
+"""Expert parallelism over 2, 4 or 8 GPUs of one box, one process per GPU.  Two forms of the exchange:
+``PeerExpertParallelLayer`` stores rows straight into the peers' buffers over NVLink (CUDA IPC mappings, flags polled
+on the device, no collective and no host synchronisation per layer - the one the benchmark runs);
+``ExpertParallelLayer`` uses ``torch.distributed`` all-to-all calls (NCCL on GPUs, gloo in the CPU tests of the
+exchange logic).  The library's kernels do everything else.
 
 Experts are block-sharded - rank g owns experts [g*E/G, (g+1)*E/G) and only their slice of the pool - tokens stay
 data-parallel, the router weights and the shared expert are replicated.  Per layer:
@@ -60,6 +63,13 @@ class DeviceOps:
     @staticmethod
     def _s():
         return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def ones_for(self, n, device):
+        """fp16 ones [n, 1]: the routing weight of a received row on the expert side (cached)."""
+        cur = getattr(self, "_ones", None)
+        if cur is None or cur.shape[0] < n or cur.device != device:
+            self._ones = torch.ones((n, 1), dtype=torch.float16, device=device)
+        return self._ones[:n]
 
     def route(self, weights, h):
         """RMSNorm + router top-k of the local rows: (xn, idx int32 [T,K], w fp16 [T,K])."""
@@ -142,4 +152,129 @@ class ExpertParallelLayer:
         back = exchange_rows(partial, recv_counts, send_counts, self.group)     # reversed split sizes
         shared_partial = ops.shared_ffn(shared_weights, xn) if shared_weights is not None else None
         ops.combine(back, inv, w, shared_partial, h_in, h_out)
+        return h_out
+
+
+class PeerExchange:
+    """mfb_ep_*: the one-sided exchange over peer memory.  Buffers are created and their CUDA IPC handles swapped once;
+    after that a layer needs no collective call and no host synchronisation."""
+
+    def __init__(self, rank: int, world: int, d: int, max_pairs: int, group=None):
+        self.lib = L.load()
+        self.rank, self.world, self.d, self.cap = rank, world, d, max_pairs
+        self.handle = C.c_void_p()
+        L.check(self.lib.mfb_ep_create(rank, world, d, max_pairs, C.byref(self.handle)))
+        mine = (C.c_uint8 * 256)()
+        L.check(self.lib.mfb_ep_export(self.handle, mine))
+        if world > 1:
+            gathered: List[bytes] = [b""] * world
+            dist.all_gather_object(gathered, bytes(mine), group=group)
+        else:
+            gathered = [bytes(mine)]
+        blob = b"".join(gathered)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        L.check(self.lib.mfb_ep_import(self.handle, buf))
+        if world > 1:
+            dist.barrier(group=group)   # every rank has mapped every buffer before anyone stores into one
+
+    def close(self):
+        if getattr(self, "handle", None) and self.handle.value:
+            self.lib.mfb_ep_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _s():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def dispatch(self, xn, idx, num_experts):
+        T, K = idx.shape
+        inv = torch.empty(T * K, dtype=torch.int32, device=idx.device)
+        L.check(self.lib.mfb_ep_dispatch(self.handle, self._s(), xn.data_ptr(), xn.stride(0), idx.data_ptr(), T, K, num_experts,
+                                         inv.data_ptr()))
+        return inv
+
+    def receive(self):
+        rows, row_expert, row_dest, n = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_uint32()
+        L.check(self.lib.mfb_ep_receive(self.handle, self._s(), C.byref(rows), C.byref(row_expert), C.byref(row_dest), C.byref(n)))
+        return rows.value, row_expert.value, row_dest.value, n.value
+
+    def send_back(self):
+        L.check(self.lib.mfb_ep_return(self.handle, self._s()))
+
+    def results(self) -> int:
+        ret = C.c_void_p()
+        L.check(self.lib.mfb_ep_results(self.handle, self._s(), C.byref(ret)))
+        return ret.value
+
+    def status(self, with_counts: bool = False):
+        st = C.c_uint32()
+        counts = (C.c_int32 * self.world)() if with_counts else None
+        rc = self.lib.mfb_ep_status(self.handle, self._s(), C.byref(st), counts)
+        if rc not in (L.OK, L.ERR_DEVICE_STATUS):
+            L.check(rc)
+        return (st.value, list(counts)) if with_counts else st.value
+
+
+def _view(ptr: int, shape, typestr: str):
+    """A CUDA tensor over library-owned device memory (no copy, no ownership)."""
+    class _Ptr:
+        pass
+    holder = _Ptr()
+    holder.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+    return torch.as_tensor(holder, device="cuda")
+
+
+class PeerExpertParallelLayer:
+    """One MoE layer over `world` ranks with the one-sided exchange: route locally, store the packed rows into the
+    owners' receive buffers, run the grouped expert FFN on what arrived with every result row written straight into
+    its home rank's buffer, reduce at home in rank order.  Same arguments and same result, bit for bit, as
+    `ExpertParallelLayer` (and as the single-GPU prefill layer); nothing in `forward` synchronises the host."""
+
+    def __init__(self, ops: DeviceOps, rank: int, world: int, tokens_per_rank: int, group=None):
+        self.ops, self.rank, self.world = ops, rank, world
+        self.cap = tokens_per_rank * ops.K
+        assert ops.expert.cfg.max_tokens >= world * self.cap, "the expert-side handle must hold world * tokens * top_k rows"
+        self.ex = PeerExchange(rank, world, ops.d, self.cap, group)
+
+    def forward(self, weights, local_weights, shared_weights, h_in, h_out, marks=None):
+        """marks: optional list that receives (name, CUDA event) at the stage boundaries (for the benchmark's breakdown)."""
+        ops, ex = self.ops, self.ex
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        xn, idx, w = ops.route(weights, h_in)
+        mark("routed")
+        inv = ex.dispatch(xn, idx, ops.E)
+        mark("dispatched")
+        # the shared expert does not depend on the exchange: it runs while the rows travel
+        shared_partial = ops.shared_ffn(shared_weights, xn) if shared_weights is not None else None
+        mark("shared")
+        rows_p, expert_p, dest_p, n_rows = ex.receive()
+        mark("received")
+        rows = _view(rows_p, (n_rows, ops.d), "<i2").view(ops.tdt)
+        row_expert = _view(expert_p, (n_rows, 1), "<i4")
+        ones = ops.ones_for(n_rows, rows.device)
+        sp, _, _, groups, n_groups = ops.expert.encode_group(row_expert, ones)
+        w_c = local_weights.c_struct()
+        L.check(ops.lib.mfb_moe_prefill_grouped_rows(ops.expert.handle, ex._s(), C.byref(w_c), rows.data_ptr(), rows.stride(0), n_rows,
+                                                     sp.data_ptr(), groups.data_ptr(), n_groups.data_ptr(), C.c_void_p(dest_p)))
+        ex.send_back()
+        mark("experts")
+        ret_p = ex.results()
+        mark("returned")
+        L.check(ops.lib.mfb_ep_combine(ex._s(), C.c_void_p(ret_p), inv.data_ptr(), w.data_ptr(),
+                                       None if shared_partial is None else shared_partial.data_ptr(), h_in.data_ptr(),
+                                       h_out.data_ptr(), h_in.shape[0], ops.K, ops.d, ops.x_dtype))
+        mark("combined")
         return h_out
