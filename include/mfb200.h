@@ -122,6 +122,18 @@ typedef struct mfb_layer_weights {
     const uint8_t* shared_blob;    /* shared expert blob, or NULL */
     mfb_expert_offsets routed_off;
     mfb_expert_offsets shared_off;
+    /* INT8 affine group-64 gate, as Qwen 3.6 files carry it (Sources/Mference/Metal/MoE/moe.metal:102-157): when
+     * router_scales is non-NULL, router_w holds unsigned byte codes [num_experts, d] and router_scales / router_biases
+     * bf16 [num_experts, d/64]; router_effective_scale (bf16 [d], may be NULL = 1) multiplies the activations first. */
+    const void* router_scales;
+    const void* router_biases;
+    const void* router_effective_scale;
+    /* Qwen shared-expert scalar gate (RealForwardRunner.swift:2925-2941, prefill.metal:37-80): when shared_gate_w is
+     * non-NULL (byte codes [d], bf16 scales / biases [d/64]) the shared expert's output row of every token is multiplied
+     * by sigmoid(fp16(g . x)) before the combine. */
+    const void* shared_gate_w;
+    const void* shared_gate_s;
+    const void* shared_gate_b;
 } mfb_layer_weights;
 
 typedef struct mfb_moe mfb_moe;
@@ -204,6 +216,24 @@ int32_t mfb_router_topk_static(void* stream, const void* x, uint32_t x_dtype, ui
                                const void* router_w, const float* logit_bias, uint32_t num_experts, uint32_t top_k,
                                uint32_t router_mode, const void* per_expert_scale, const float* correction_bias,
                                float route_scale, uint32_t* out_idx, uint16_t* out_w);
+
+/* Routing weights of hash-routed layers: the expert indices are given (a frozen token-id table in the reference), the
+ * weights are sqrt(softplus(logit)) of exactly those experts, normalised over them in rank order and scaled.
+ * Replaces router_hash_weights_k6(_par) (moe.metal:852-896) for any top_k <= MFB_MAX_TOP_K. */
+int32_t mfb_router_hash_weights(void* stream, const float* logits, const uint32_t* idx, uint32_t n_tokens, uint32_t num_experts,
+                                uint32_t top_k, float route_scale, uint16_t* out_w);
+/* INT8 affine group-64 GEMV y[t, r] = sum_i (q[r,i] * s[r,i/64] + b[r,i/64]) * x[t,i] in the summation order of
+ * router_gemv_gemma4_r4 (moe.metal:102-157; host MoE.encodeRouterGemma4, MoE.swift:153-188): the Qwen router's logits
+ * (M = num_experts) and the shared-expert scalar gate (M = 1).  y is f32 [n_tokens, M]. */
+int32_t mfb_gemv_int8(void* stream, const uint8_t* W, const void* scales_bf16, const void* biases_bf16, const void* x,
+                      uint32_t x_dtype, uint32_t ldx, uint32_t n_tokens, const void* effective_scale_bf16, uint32_t M,
+                      uint32_t N, float* y);
+/* INT4 affine group-64 GEMV of a resident projection, up to 8 activation rows per weight read: y[t, r] f32 [n_tokens, M].
+ * Replaces DequantInt4GEMV.encode and its multi-row form (Sources/Mference/Kernels/Quant/DequantInt4GEMV.swift:1-104;
+ * kernels Sources/Mference/Metal/Quant/dequant_int4.metal:248-288, 343-446).  W: [M, N/2] bytes, low nibble = even
+ * element; scales / biases 16-bit [M, N/64] of scale_dtype. */
+int32_t mfb_gemv_int4(void* stream, const uint8_t* W, const void* scales, const void* biases, uint32_t scale_dtype,
+                      const void* x, uint32_t x_dtype, uint32_t ldx, uint32_t n_tokens, uint32_t M, uint32_t N, float* y);
 
 /* ---- decode -------------------------------------------------------------------------------------------- */
 

@@ -66,7 +66,9 @@ class LayerWeightsC(C.Structure):
     _fields_ = [("router_w", C.c_void_p), ("logit_bias", C.c_void_p), ("per_expert_scale", C.c_void_p),
                 ("correction_bias", C.c_void_p), ("norm_w", C.c_void_p), ("pool", C.c_void_p),
                 ("slot_stride", C.c_uint64), ("slot_of", C.c_void_p), ("shared_blob", C.c_void_p),
-                ("routed_off", ExpertOffsets), ("shared_off", ExpertOffsets)]
+                ("routed_off", ExpertOffsets), ("shared_off", ExpertOffsets),
+                ("router_scales", C.c_void_p), ("router_biases", C.c_void_p), ("router_effective_scale", C.c_void_p),
+                ("shared_gate_w", C.c_void_p), ("shared_gate_s", C.c_void_p), ("shared_gate_b", C.c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/mfb200.h declares
@@ -98,6 +100,9 @@ SIGNATURES = {
     "mfb_ep_plan": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _V, _V]),
     "mfb_ep_pack": (_I32, [_V, _V, _U32, _U32, _V, _U32, _U32, _V]),
     "mfb_ep_combine": (_I32, [_V, _V, _V, _V, _V, _V, _V, _U32, _U32, _U32, _U32]),
+    "mfb_router_hash_weights": (_I32, [_V, _V, _V, _U32, _U32, _U32, C.c_float, _V]),
+    "mfb_gemv_int8": (_I32, [_V, _V, _V, _V, _V, _U32, _U32, _U32, _V, _U32, _U32, _V]),
+    "mfb_gemv_int4": (_I32, [_V, _V, _V, _V, _U32, _V, _U32, _U32, _U32, _U32, _U32, _V]),
     "mfb_ep_create": (_I32, [_U32, _U32, _U32, _U32, C.POINTER(_V)]),
     "mfb_ep_destroy": (_I32, [_V]),
     "mfb_ep_export": (_I32, [_V, _V]),

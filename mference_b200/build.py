@@ -14,7 +14,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libmfb200.so")
 
 SOURCES = ["api.cu", "router.cu", "router_static.cu", "glue.cu", "group.cu", "decode.cu", "decode_mma.cu", "prefill_tc.cu",
-           "synth.cu", "pool.cu", "ep.cu"]
+           "synth.cu", "pool.cu", "ep.cu", "quant_gemv.cu"]
 EXTRA = []
 
 NVCC_FLAGS = [

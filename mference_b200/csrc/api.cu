@@ -71,6 +71,11 @@ int32_t check_weights(const mfb_moe* m, const mfb_layer_weights* w, bool need_ro
     MFB_REQUIRE(((uintptr_t)w->pool % 16) == 0 && (w->slot_stride % 16) == 0, MFB_ERR_INVALID_ARGUMENT,
                 "pool base and slot stride must be multiples of 16 bytes");
     MFB_REQUIRE(offsets_aligned(w->routed_off), MFB_ERR_INVALID_ARGUMENT, "routed expert offsets must be multiples of 16 bytes");
+    MFB_REQUIRE((w->router_scales == nullptr) == (w->router_biases == nullptr), MFB_ERR_INVALID_ARGUMENT,
+                "an INT8 gate needs both router_scales and router_biases");
+    MFB_REQUIRE(!w->router_scales || !w->logit_bias, MFB_ERR_INVALID_ARGUMENT, "logit_bias is not supported with an INT8 gate");
+    MFB_REQUIRE(!w->shared_gate_w || (w->shared_gate_s && w->shared_gate_b), MFB_ERR_INVALID_ARGUMENT,
+                "the shared-expert gate needs its scales and biases");
     if (w->shared_blob) {
         MFB_REQUIRE(m->cfg.shared_bits != 0, MFB_ERR_INVALID_ARGUMENT, "shared blob given but the handle has shared_bits = 0");
         MFB_REQUIRE(((uintptr_t)w->shared_blob % 16) == 0 && offsets_aligned(w->shared_off), MFB_ERR_INVALID_ARGUMENT,
@@ -157,6 +162,29 @@ int32_t wide_maps_for(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, co
 
 void begin_wide_call(mfb_moe* m) {
     if (m->wide_cache) ++static_cast<WideCache*>(m->wide_cache)->call;
+}
+
+// Gate logits of a layer into `logits`: the bf16 gate, or the INT8 affine gate when the layer carries one.
+cudaError_t layer_logits(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx, uint32_t n_tokens,
+                         float* logits) {
+    const mfb_moe_config& c = m->cfg;
+    if (w->router_scales)
+        return launch_gemv_int8(s, (const uint8_t*)w->router_w, w->router_scales, w->router_biases, x, (int)c.x_dtype, ldx, n_tokens,
+                                w->router_effective_scale, c.num_experts, c.d, logits);
+    return launch_router_logits(s, x, (int)c.x_dtype, ldx, n_tokens, (const __nv_bfloat16*)w->router_w, c.num_experts, c.d,
+                                w->logit_bias, logits);
+}
+
+// Qwen shared-expert scalar gate: the shared expert's fp32 row of every token (rank slot top_k of `partial`) times
+// sigmoid(fp16(g . x)).  The gate logits use the head of the logits scratch, which the router no longer needs.
+cudaError_t apply_shared_gate(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w, const void* x, uint32_t ldx, uint32_t n_tokens,
+                              float* partial, uint32_t slots) {
+    if (!w->shared_gate_w || !w->shared_blob || n_tokens == 0) return cudaSuccess;
+    const mfb_moe_config& c = m->cfg;
+    cudaError_t e = launch_gemv_int8(s, (const uint8_t*)w->shared_gate_w, w->shared_gate_s, w->shared_gate_b, x, (int)c.x_dtype, ldx,
+                                     n_tokens, nullptr, 1, c.d, m->a.logits);
+    if (e != cudaSuccess) return e;
+    return launch_shared_gate_scale(s, m->a.logits, partial + (size_t)c.top_k * c.d, (uint64_t)slots * c.d, n_tokens, c.d);
 }
 
 uint32_t max_groups_for(const mfb_moe* m, uint32_t n_tokens, bool shared) {
@@ -391,8 +419,10 @@ extern "C" int32_t mfb_router_topk(mfb_moe* moe, void* stream, const void* x, ui
     int32_t rc = check_handle(moe, n_tokens);
     if (rc) return rc;
     MFB_REQUIRE(w && w->router_w && x && out_idx && out_w, MFB_ERR_INVALID_ARGUMENT, "router_topk: NULL argument");
-    rc = mfb_router_logits(moe, stream, x, ldx, n_tokens, w->router_w, w->logit_bias, moe->a.logits);
-    if (rc) return rc;
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "router_topk: row stride smaller than d");
+    MFB_REQUIRE((w->router_scales == nullptr) == (w->router_biases == nullptr) && !(w->router_scales && w->logit_bias),
+                MFB_ERR_INVALID_ARGUMENT, "router_topk: an INT8 gate needs scales and biases and takes no logit bias");
+    MFB_CUDA(layer_logits(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, moe->a.logits));
     return mfb_router_select(moe, stream, moe->a.logits, n_tokens, w->per_expert_scale, w->correction_bias, out_idx, out_w);
 }
 
@@ -427,7 +457,10 @@ extern "C" int32_t mfb_moe_experts(mfb_moe* moe, void* stream, const mfb_layer_w
         }
     }
     if (n_tokens == 0) return MFB_OK;
-    return run_experts(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, idx, route_w, mask, with_shared != 0);
+    rc = run_experts(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, idx, route_w, mask, with_shared != 0);
+    if (rc) return rc;
+    if (with_shared) MFB_CUDA(apply_shared_gate(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, moe->a.partial, moe->cfg.top_k + 1));
+    return MFB_OK;
 }
 
 extern "C" int32_t mfb_moe_combine(mfb_moe* moe, void* stream, uint32_t n_tokens, const uint16_t* route_w,
@@ -461,6 +494,7 @@ extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_we
         if (n_tokens > 16 && (rc = wide_maps_for(moe, s, w, &maps)) != MFB_OK) return rc;
         const FastParams P = fast_params(moe, w, n_tokens, route_w, residual, y, maps);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        MFB_CUDA(apply_shared_gate(moe, s, w, x, ldx, n_tokens, a.partial, c.top_k + 1));
         MFB_CUDA(launch_combine(s, a.partial, route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, residual, y,
                                 (int)c.x_dtype));
         return MFB_OK;
@@ -485,8 +519,7 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
         const bool shared = w->shared_blob != nullptr;
         MFB_CUDA(launch_fast_prep(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, true, a.xn,
                                   a.xp, c.bits, a.xp2, c.shared_bits));
-        MFB_CUDA(launch_router_logits(s, a.xn, (int)c.x_dtype, c.d, n_tokens, (const __nv_bfloat16*)w->router_w, c.num_experts,
-                                      c.d, w->logit_bias, a.logits));
+        MFB_CUDA(layer_logits(moe, s, w, a.xn, c.d, n_tokens, a.logits));
         MFB_CUDA(launch_route_small(s, a.logits, n_tokens, c.num_experts, c.top_k, (int)c.router_mode,
                                     (const __nv_bfloat16*)w->per_expert_scale, w->correction_bias, c.route_scale, shared ? 1 : 0,
                                     a.idx, a.route_w, a.sorted, a.groups, a.n_groups));
@@ -495,6 +528,7 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
         if (n_tokens > 16 && (rc = wide_maps_for(moe, s, w, &maps)) != MFB_OK) return rc;
         const FastParams P = fast_params(moe, w, n_tokens, a.route_w, h_in, h_out, maps);
         MFB_CUDA(launch_fast_ffn(s, P, c, moe->sm_count, max_groups_for(moe, n_tokens, shared)));
+        MFB_CUDA(apply_shared_gate(moe, s, w, a.xn, c.d, n_tokens, a.partial, c.top_k + 1));
         MFB_CUDA(launch_combine(s, a.partial, a.route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, h_in, h_out,
                                 (int)c.x_dtype));
         return MFB_OK;
@@ -547,7 +581,9 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
     const mfb_moe_config& c = moe->cfg;
     cudaStream_t s = (cudaStream_t)stream;
     const bool want_maps = n_tokens > 16 && moe->wide_cache != nullptr;
-    if (use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens, want_maps) <= FAST_SMEM_LIMIT) {
+    bool plain = true;   // the fused kernel computes the bf16 gate itself and has no scalar gate on the shared expert
+    for (uint32_t l = 0; l < n_layers; ++l) plain = plain && !layers[l].router_scales && !layers[l].shared_gate_w;
+    if (plain && use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens, want_maps) <= FAST_SMEM_LIMIT) {
         for (uint32_t l = 0; l < n_layers; ++l) {
             rc = check_weights(moe, &layers[l], true);
             if (rc) return rc;
@@ -676,6 +712,7 @@ extern "C" int32_t mfb_moe_layer_prefill(mfb_moe* moe, void* stream, const mfb_l
     rc = tc_grouped_ffn(moe, s, w, a.xn, c.d, n_tokens, a.sorted, a.groups, a.n_groups, max_groups, /*routed_only=*/false,
                         a.partial, c.top_k + 1);
     if (rc) return rc;
+    MFB_CUDA(apply_shared_gate(moe, s, w, a.xn, c.d, n_tokens, a.partial, c.top_k + 1));
     MFB_CUDA(launch_combine(s, a.partial, a.route_w, n_tokens, c.top_k, c.top_k + 1, c.d, all_slots(moe), shared, h_in, h_out,
                             (int)c.x_dtype));
     return MFB_OK;

@@ -129,6 +129,10 @@ cudaError_t launch_router_select(cudaStream_t s, const float* logits, uint32_t n
 cudaError_t launch_slot_lookup(cudaStream_t s, const uint32_t* idx, uint32_t n_tokens, uint32_t top_k,
                                uint32_t num_experts, const int16_t* slot_of, uint64_t slot_stride,
                                uint64_t* out_offsets, uint32_t* out_all_hit);
+// quant_gemv.cu
+cudaError_t launch_gemv_int8(cudaStream_t s, const uint8_t* W, const void* scales, const void* biases, const void* x, int x_dtype,
+                             uint32_t ldx, uint32_t n_tokens, const void* effective_scale, uint32_t M, uint32_t N, float* y);
+cudaError_t launch_shared_gate_scale(cudaStream_t s, const float* gate, float* rows, uint64_t row_stride, uint32_t n_tokens, uint32_t d);
 // glue.cu
 cudaError_t launch_rmsnorm(cudaStream_t s, const void* x, int in_dtype, const __nv_bfloat16* w, uint32_t n_rows,
                            uint32_t d, float eps, void* out, int out_dtype);

@@ -71,14 +71,22 @@ class DeviceOps:
             self._ones = torch.ones((n, 1), dtype=torch.float16, device=device)
         return self._ones[:n]
 
+    def norm(self, weights, h):
+        xn = torch.empty_like(h)
+        self.home.encode_rmsnorm(h, xn, weights.norm_w)
+        return xn
+
+    def router(self, weights, xn):
+        T = xn.shape[0]
+        idx = torch.empty((T, self.K), dtype=torch.int32, device=xn.device)
+        w = torch.empty((T, self.K), dtype=torch.float16, device=xn.device)
+        self.home.encode_router(xn, weights, idx, w)
+        return idx, w
+
     def route(self, weights, h):
         """RMSNorm + router top-k of the local rows: (xn, idx int32 [T,K], w fp16 [T,K])."""
-        T = h.shape[0]
-        xn = torch.empty_like(h)
-        idx = torch.empty((T, self.K), dtype=torch.int32, device=h.device)
-        w = torch.empty((T, self.K), dtype=torch.float16, device=h.device)
-        self.home.encode_rmsnorm(h, xn, weights.norm_w)
-        self.home.encode_router(xn, weights, idx, w)
+        xn = self.norm(weights, h)
+        idx, w = self.router(weights, xn)
         return xn, idx, w
 
     def plan(self, idx):
@@ -241,6 +249,9 @@ class PeerExpertParallelLayer:
         self.cap = tokens_per_rank * ops.K
         assert ops.expert.cfg.max_tokens >= world * self.cap, "the expert-side handle must hold world * tokens * top_k rows"
         self.ex = PeerExchange(rank, world, ops.d, self.cap, group)
+        # the shared expert needs only the normalised rows: it runs on a stream of its own beside the router and the
+        # dispatch (few CTAs each), and is joined before the combine
+        self.side = torch.cuda.Stream()
 
     def forward(self, weights, local_weights, shared_weights, h_in, h_out, marks=None):
         """marks: optional list that receives (name, CUDA event) at the stage boundaries (for the benchmark's breakdown)."""
@@ -253,13 +264,17 @@ class PeerExpertParallelLayer:
                 marks.append((name, ev))
 
         mark("start")
-        xn, idx, w = ops.route(weights, h_in)
+        xn = ops.norm(weights, h_in)
+        shared_partial = None
+        if shared_weights is not None:
+            main = torch.cuda.current_stream()
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                shared_partial = ops.shared_ffn(shared_weights, xn)
+        idx, w = ops.router(weights, xn)
         mark("routed")
         inv = ex.dispatch(xn, idx, ops.E)
         mark("dispatched")
-        # the shared expert does not depend on the exchange: it runs while the rows travel
-        shared_partial = ops.shared_ffn(shared_weights, xn) if shared_weights is not None else None
-        mark("shared")
         rows_p, expert_p, dest_p, n_rows = ex.receive()
         mark("received")
         rows = _view(rows_p, (n_rows, ops.d), "<i2").view(ops.tdt)
@@ -273,6 +288,8 @@ class PeerExpertParallelLayer:
         mark("experts")
         ret_p = ex.results()
         mark("returned")
+        if shared_partial is not None:
+            torch.cuda.current_stream().wait_stream(self.side)
         L.check(ops.lib.mfb_ep_combine(ex._s(), C.c_void_p(ret_p), inv.data_ptr(), w.data_ptr(),
                                        None if shared_partial is None else shared_partial.data_ptr(), h_in.data_ptr(),
                                        h_out.data_ptr(), h_in.shape[0], ops.K, ops.d, ops.x_dtype))

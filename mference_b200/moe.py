@@ -47,6 +47,13 @@ class MoELayerWeights:
     logit_bias: Optional[torch.Tensor] = None  # f32 [E]
     per_expert_scale: Optional[torch.Tensor] = None
     correction_bias: Optional[torch.Tensor] = None
+    # INT8 gate (router_w then holds uint8 codes [E, d]) and the Qwen shared-expert scalar gate
+    router_scales: Optional[torch.Tensor] = None            # bf16 [E, d/64]
+    router_biases: Optional[torch.Tensor] = None
+    router_effective_scale: Optional[torch.Tensor] = None   # bf16 [d]
+    shared_gate_w: Optional[torch.Tensor] = None            # uint8 [d]
+    shared_gate_s: Optional[torch.Tensor] = None            # bf16 [d/64]
+    shared_gate_b: Optional[torch.Tensor] = None
 
     def c_struct(self) -> L.LayerWeightsC:
         w = L.LayerWeightsC()
@@ -61,6 +68,9 @@ class MoELayerWeights:
         w.shared_blob = None if self.shared_blob is None else self.shared_blob.data_ptr()
         w.routed_off = self.routed_off
         w.shared_off = self.shared_off if self.shared_off is not None else L.ExpertOffsets()
+        for name in ("router_scales", "router_biases", "router_effective_scale", "shared_gate_w", "shared_gate_s", "shared_gate_b"):
+            t = getattr(self, name)
+            setattr(w, name, None if t is None else t.data_ptr())
         return w
 
 

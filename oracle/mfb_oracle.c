@@ -722,6 +722,89 @@ int mfbo_num_threads(void) {
 #endif
 }
 
+/* ------------------------------------------------------------------ quantised gate / projections */
+
+/* Weights of hash-routed layers (moe.metal:852-896, router_hash_weights_k6): the expert indices are given (a frozen
+ * token-id table in the reference); the weights are sqrt(softplus(logit)) of exactly those experts, summed in rank
+ * order, normalised and scaled by route_scale. */
+void mfbo_hash_weights(const float* logits, const uint32_t* idx, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k,
+                       float route_scale, uint16_t* out_w_f16) {
+    for (uint32_t t = 0; t < n_tokens; ++t) {
+        float sc[64], sum = 0.0f;
+        for (uint32_t i = 0; i < top_k; ++i) {
+            sc[i] = sqrtsoftplus(logits[(uint64_t)t * num_experts + idx[(uint64_t)t * top_k + i]]);
+            sum += sc[i];
+        }
+        const float inv = route_scale / (sum + 1e-20f);
+        for (uint32_t i = 0; i < top_k; ++i) out_w_f16[(uint64_t)t * top_k + i] = mfbo_f32_to_f16(sc[i] * inv);
+    }
+}
+
+/* INT8 affine group-64 GEMV in the order of router_gemv_gemma4_r4 (moe.metal:102-157) and of the shared-expert scalar
+ * gate (prefill.metal:37-80): one 32-lane group per output row; for every 64-element group lane l takes elements
+ * 2l and 2l+1:  acc = fma(s, q0*x0 + q1*x1, acc); acc = fma(b, x0 + x1, acc)  with every product and sum rounded to
+ * fp32; the lane sums meet in the xor butterfly fixed for the bf16 gate above.  Codes are unsigned bytes, scales and
+ * biases bf16 per (row, group).  effective_scale (bf16 per element, may be NULL = 1) multiplies the activation first. */
+void mfbo_gemv_int8(const uint8_t* W, const uint16_t* s_bf16, const uint16_t* b_bf16, const uint16_t* x, int x_dtype,
+                    uint32_t ldx, uint32_t n_tokens, const uint16_t* effective_scale_bf16, uint32_t M, uint32_t N, float* y) {
+    const uint32_t groups = N / 64;
+#pragma omp parallel for schedule(static)
+    for (int64_t t = 0; t < (int64_t)n_tokens; ++t) {
+        float* xf = (float*)malloc(sizeof(float) * N);
+        for (uint32_t i = 0; i < N; ++i) {
+            float v = widen16(x[(uint64_t)t * ldx + i], x_dtype);
+            if (effective_scale_bf16) v = v * mfbo_bf16_to_f32(effective_scale_bf16[i]);
+            xf[i] = v;
+        }
+        for (uint32_t r = 0; r < M; ++r) {
+            float lane[32];
+            for (uint32_t l = 0; l < 32; ++l) {
+                float acc = 0.0f;
+                for (uint32_t g = 0; g < groups; ++g) {
+                    const float s = mfbo_bf16_to_f32(s_bf16[(uint64_t)r * groups + g]);
+                    const float b = mfbo_bf16_to_f32(b_bf16[(uint64_t)r * groups + g]);
+                    const uint32_t i0 = g * 64 + 2 * l;
+                    const float q0 = (float)W[(uint64_t)r * N + i0], q1 = (float)W[(uint64_t)r * N + i0 + 1];
+                    const float p0 = q0 * xf[i0], p1 = q1 * xf[i0 + 1];
+                    const float dot = p0 + p1, sx = xf[i0] + xf[i0 + 1];
+                    acc = fmaf(s, dot, acc);
+                    acc = fmaf(b, sx, acc);
+                }
+                lane[l] = acc;
+            }
+            for (uint32_t off = 16; off > 0; off >>= 1) {
+                float nxt[32];
+                for (uint32_t l = 0; l < 32; ++l) nxt[l] = lane[l] + lane[l ^ off];
+                memcpy(lane, nxt, sizeof(lane));
+            }
+            y[(uint64_t)t * M + r] = lane[0];
+        }
+        free(xf);
+    }
+}
+
+/* fp32 reference of the INT4 affine group-64 GEMV y = W x (DequantInt4Gemv.swift:13-42: every row dequantised to
+ * fp32 as Quantization.dequantizeInt4Affine does, then a dot product; accumulated in double here). */
+void mfbo_gemv_int4(const uint8_t* W, const uint16_t* scales, const uint16_t* biases, int scale_dtype, const uint16_t* x,
+                    int x_dtype, uint32_t ldx, uint32_t n_tokens, uint32_t M, uint32_t N, float* y) {
+    const uint32_t groups = N / 64;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)M; ++r) {
+        float* wr = (float*)malloc(sizeof(float) * N);
+        for (uint32_t i = 0; i < N; ++i) {
+            const uint8_t byte = W[(uint64_t)r * (N / 2) + i / 2];
+            const float q = (float)((i & 1) ? (byte >> 4) : (byte & 15));
+            wr[i] = q * widen16(scales[(uint64_t)r * groups + i / 64], scale_dtype) + widen16(biases[(uint64_t)r * groups + i / 64], scale_dtype);
+        }
+        for (uint32_t t = 0; t < n_tokens; ++t) {
+            double acc = 0.0;
+            for (uint32_t i = 0; i < N; ++i) acc += (double)wr[i] * (double)widen16(x[(uint64_t)t * ldx + i], x_dtype);
+            y[(uint64_t)t * M + r] = (float)acc;
+        }
+        free(wr);
+    }
+}
+
 /* Number of threads of the following parallel loops (the timed CPU baseline uses every host core even when the
  * launcher exported OMP_NUM_THREADS=1 for its ranks). */
 void mfbo_set_num_threads(int n) {

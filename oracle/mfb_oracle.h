@@ -145,6 +145,13 @@ void mfbo_rmsnorm(const float* x, const uint16_t* w_bf16, uint32_t n_rows, uint3
  * s*sum(q*x) + b*sum(x) per group (moe.metal:349-404, 408-529), threaded over rows with OpenMP ---- */
 void mfbo_ref_moe_layer_f32(const mfbo_layer* L, const float* x, uint32_t n_tokens, const uint32_t* idx,
                             const uint16_t* w_f16, const float* residual, float* y);
+/* quantised gate / projections (hash-routed weights, INT8 gate GEMV in the reference kernels' order, INT4 GEMV in fp32) */
+void mfbo_hash_weights(const float* logits, const uint32_t* idx, uint32_t n_tokens, uint32_t num_experts, uint32_t top_k,
+                       float route_scale, uint16_t* out_w_f16);
+void mfbo_gemv_int8(const uint8_t* W, const uint16_t* s_bf16, const uint16_t* b_bf16, const uint16_t* x, int x_dtype,
+                    uint32_t ldx, uint32_t n_tokens, const uint16_t* effective_scale_bf16, uint32_t M, uint32_t N, float* y);
+void mfbo_gemv_int4(const uint8_t* W, const uint16_t* scales, const uint16_t* biases, int scale_dtype, const uint16_t* x,
+                    int x_dtype, uint32_t ldx, uint32_t n_tokens, uint32_t M, uint32_t N, float* y);
 int mfbo_num_threads(void);
 void mfbo_set_num_threads(int n);
 

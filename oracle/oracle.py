@@ -290,6 +290,38 @@ def ref_moe_layer_f32(W: LayerWeights, x_f32, idx, w_f16, residual=None) -> np.n
     return y
 
 
+def hash_weights(logits, idx, route_scale=1.0) -> np.ndarray:
+    logits = _c(logits, np.float32); idx = _c(idx, np.uint32)
+    T, E = logits.shape
+    K = idx.shape[1]
+    out = np.empty((T, K), dtype=np.uint16)
+    lib().mfbo_hash_weights(_p(logits), _p(idx), C.c_uint32(T), C.c_uint32(E), C.c_uint32(K), C.c_float(route_scale), _p(out))
+    return out
+
+
+def gemv_int8(W, scales_bf16, biases_bf16, x, x_dtype, effective_scale_bf16=None) -> np.ndarray:
+    """y[t, r] of the INT8 affine group-64 GEMV in the reference kernels' summation order; W uint8 [M, N]."""
+    W = _c(W, np.uint8); s = _c(scales_bf16, np.uint16); b = _c(biases_bf16, np.uint16); x = _c(x, np.uint16)
+    M, N = W.shape
+    T = x.shape[0]
+    es = None if effective_scale_bf16 is None else _c(effective_scale_bf16, np.uint16)
+    y = np.empty((T, M), dtype=np.float32)
+    lib().mfbo_gemv_int8(_p(W), _p(s), _p(b), _p(x), C.c_int(x_dtype), C.c_uint32(x.shape[1]), C.c_uint32(T), _p(es),
+                         C.c_uint32(M), C.c_uint32(N), _p(y))
+    return y
+
+
+def gemv_int4(W, scales, biases, scale_dtype, x, x_dtype) -> np.ndarray:
+    """fp32 reference of the INT4 affine group-64 GEMV; W uint8 [M, N/2] (low nibble = even element)."""
+    W = _c(W, np.uint8); s = _c(scales, np.uint16); b = _c(biases, np.uint16); x = _c(x, np.uint16)
+    M, N = W.shape[0], W.shape[1] * 2
+    T = x.shape[0]
+    y = np.empty((T, M), dtype=np.float32)
+    lib().mfbo_gemv_int4(_p(W), _p(s), _p(b), C.c_int(scale_dtype), _p(x), C.c_int(x_dtype), C.c_uint32(x.shape[1]),
+                         C.c_uint32(T), C.c_uint32(M), C.c_uint32(N), _p(y))
+    return y
+
+
 def num_threads() -> int:
     return lib().mfbo_num_threads()
 
