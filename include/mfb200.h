@@ -342,6 +342,22 @@ int32_t mfb_pool_fill_async(mfb_pool* pool, void* stream, const int32_t* experts
 /* executeExpertCachePlan, second half: the filled slots become hits on the host and, in stream order, on the device. */
 int32_t mfb_pool_publish(mfb_pool* pool, void* stream, const int32_t* experts, const int32_t* slots, const uint8_t* miss,
                          uint32_t n);
+/* reserveSpeculativeSlots (PreadExpertStreamer.swift:344-372): slots for a speculative read of `experts` (already
+ * filtered to the non-resident ones by the caller).  Slots that hold one of the predicted experts or that another
+ * read is filling are never victims; `keep_evictable` evictable slots are left alone so that the real plan which
+ * follows can always place its own misses.  Victims come in the normal eviction order, but no use count and no clock
+ * is written.  Reserved slots are marked in flight and read -1 until the reservation is finished; out_n entries of
+ * (out_experts, out_slots) are the reservation (possibly fewer than n, possibly none). */
+int32_t mfb_pool_reserve_speculative(mfb_pool* pool, const int32_t* experts, uint32_t n, uint32_t keep_evictable,
+                                     int32_t* out_experts, int32_t* out_slots, uint32_t* out_n);
+/* beginAsyncFill, first step (PreadExpertStreamer.swift:452-462): marks a plan's miss slots in flight, so that plans made
+ * while the eager fill runs keep away from them exactly as from speculative reads. */
+int32_t mfb_pool_mark_in_flight(mfb_pool* pool, const int32_t* slots, uint32_t n);
+/* executeSpeculativeReservation, second half (PreadExpertStreamer.swift:374-402) and the completion of beginAsyncFill:
+ * slots whose read landed (loaded[i] != 0) become hits, slots whose read failed stay empty, every in-flight mark is
+ * cleared; the device table follows in stream order (after the copies enqueued with mfb_pool_fill_async). */
+int32_t mfb_pool_finish_speculative(mfb_pool* pool, void* stream, const int32_t* experts, const int32_t* slots,
+                                    const uint8_t* loaded, uint32_t n);
 /* noteAllHitUse (PreadExpertStreamer.swift:427-440): usage accounting when the device-side lookup found every expert. */
 int32_t mfb_pool_note_all_hit(mfb_pool* pool, const int32_t* experts, uint32_t n);
 /* Host mirror of the slot table (num_experts entries). */

@@ -95,6 +95,9 @@ SIGNATURES = {
     "mfb_pool_plan": (_I32, [_V, _V, _U32, _V, _U32, _V, _V, C.POINTER(_U32)]),
     "mfb_pool_fill_async": (_I32, [_V, _V, _V, _V, _V, _U32, _V, _U64]),
     "mfb_pool_publish": (_I32, [_V, _V, _V, _V, _V, _U32]),
+    "mfb_pool_reserve_speculative": (_I32, [_V, _V, _U32, _U32, _V, _V, C.POINTER(_U32)]),
+    "mfb_pool_mark_in_flight": (_I32, [_V, _V, _U32]),
+    "mfb_pool_finish_speculative": (_I32, [_V, _V, _V, _V, _V, _U32]),
     "mfb_pool_note_all_hit": (_I32, [_V, _V, _U32]),
     "mfb_pool_slot_of_host": (_I32, [_V, _V]),
     "mfb_ep_plan": (_I32, [_V, _V, _U32, _U32, _U32, _U32, _V, _V, _V, _V]),

@@ -24,6 +24,7 @@ struct mfb_pool {
     std::vector<uint64_t> slot_last_use;
     std::vector<uint64_t> expert_use_count;
     std::vector<int16_t> slot_of_host;      // mirror of the device table
+    std::vector<char> in_flight;            // slot is being filled by a speculative or eager read: never a victim
     uint64_t use_clock = 0;
     // pinned snapshots of the table for stream-ordered uploads
     static constexpr int RING = 32;
@@ -86,6 +87,7 @@ extern "C" int32_t mfb_pool_create(uint32_t num_experts, uint64_t slot_bytes, ui
     p->slot_last_use.assign(slot_count, 0);
     p->expert_use_count.assign(num_experts, 0);
     p->slot_of_host.assign(num_experts, (int16_t)-1);
+    p->in_flight.assign(slot_count, 0);
     if (!(flags & MFB_POOL_HOST_ONLY)) {
         cudaError_t e = cudaMalloc(&p->slab, p->slot_stride * slot_count);
         if (e == cudaSuccess) e = cudaMalloc(&p->slot_of_dev, num_experts * sizeof(int16_t));
@@ -135,6 +137,8 @@ extern "C" int32_t mfb_pool_plan(mfb_pool* p, const int32_t* experts, uint32_t n
     }
     for (uint32_t i = 0; i < n_avoid; ++i)
         if (avoid_slots[i] >= 0 && (uint32_t)avoid_slots[i] < p->slot_count) reserved[avoid_slots[i]] = 1;
+    for (uint32_t s = 0; s < p->slot_count; ++s)   // slots a speculative or eager read is filling (PreadExpertStreamer.swift:231-236)
+        if (p->in_flight[s]) reserved[s] = 1;
     std::vector<uint32_t> evictable;
     for (uint32_t s = 0; s < p->slot_count; ++s)
         if (!reserved[s]) evictable.push_back(s);
@@ -191,6 +195,56 @@ extern "C" int32_t mfb_pool_publish(mfb_pool* p, void* stream, const int32_t* ex
     std::lock_guard<std::mutex> g(p->lock);
     for (uint32_t i = 0; i < n; ++i)
         if (miss[i] && slots[i] >= 0 && (uint32_t)slots[i] < p->slot_count) set_slot_expert(*p, (uint32_t)slots[i], experts[i]);
+    return upload_table(*p, (cudaStream_t)stream);
+}
+
+extern "C" int32_t mfb_pool_reserve_speculative(mfb_pool* p, const int32_t* experts, uint32_t n, uint32_t keep_evictable,
+                                               int32_t* out_experts, int32_t* out_slots, uint32_t* out_n) {
+    MFB_REQUIRE(p && (experts || n == 0) && out_experts && out_slots && out_n, MFB_ERR_INVALID_ARGUMENT, "pool_reserve_speculative: NULL argument");
+    *out_n = 0;
+    if (n == 0) return MFB_OK;
+    std::lock_guard<std::mutex> g(p->lock);
+    std::vector<uint32_t> evictable;
+    for (uint32_t s = 0; s < p->slot_count; ++s) {
+        bool wanted = false;   // a slot that already holds one of the predicted experts is never a victim
+        for (uint32_t i = 0; i < n && !wanted; ++i) wanted = p->slot_expert[s] >= 0 && p->slot_expert[s] == experts[i];
+        if (!p->in_flight[s] && !wanted) evictable.push_back(s);
+    }
+    std::stable_sort(evictable.begin(), evictable.end(), [&](uint32_t a, uint32_t b) { return evict_before(*p, a, b); });
+    const size_t room = evictable.size() > keep_evictable ? evictable.size() - keep_evictable : 0;
+    const uint32_t budget = (uint32_t)std::min<size_t>(n, room);
+    // no use counts and no clock are written: an unconfirmed guess must not shift the eviction policy
+    for (uint32_t i = 0; i < budget; ++i) {
+        const uint32_t s = evictable[i];
+        p->in_flight[s] = 1;
+        set_slot_expert(*p, s, -1);
+        out_experts[i] = experts[i];
+        out_slots[i] = (int32_t)s;
+    }
+    *out_n = budget;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_pool_mark_in_flight(mfb_pool* p, const int32_t* slots, uint32_t n) {
+    MFB_REQUIRE(p && (slots || n == 0), MFB_ERR_INVALID_ARGUMENT, "pool_mark_in_flight: NULL argument");
+    std::lock_guard<std::mutex> g(p->lock);
+    for (uint32_t i = 0; i < n; ++i)
+        if (slots[i] >= 0 && (uint32_t)slots[i] < p->slot_count) p->in_flight[slots[i]] = 1;
+    return MFB_OK;
+}
+
+extern "C" int32_t mfb_pool_finish_speculative(mfb_pool* p, void* stream, const int32_t* experts, const int32_t* slots,
+                                              const uint8_t* loaded, uint32_t n) {
+    MFB_REQUIRE(p && (n == 0 || (experts && slots && loaded)), MFB_ERR_INVALID_ARGUMENT, "pool_finish_speculative: NULL argument");
+    for (uint32_t i = 0; i < n; ++i)
+        MFB_REQUIRE(!loaded[i] || (experts[i] >= 0 && (uint32_t)experts[i] < p->num_experts), MFB_ERR_INVALID_ARGUMENT,
+                    "pool_finish_speculative: expert %d out of range", experts[i]);
+    std::lock_guard<std::mutex> g(p->lock);
+    for (uint32_t i = 0; i < n; ++i) {
+        if (slots[i] < 0 || (uint32_t)slots[i] >= p->slot_count) continue;
+        if (loaded[i]) set_slot_expert(*p, (uint32_t)slots[i], experts[i]);   // a failed read leaves its slot empty
+        p->in_flight[slots[i]] = 0;                                            // the mark is always cleared
+    }
     return upload_table(*p, (cudaStream_t)stream);
 }
 

@@ -101,6 +101,66 @@ class ExpertPool:
         self.publish(plan, stream)
         return [s * self.slot_stride for s in plan.assigned_slots]
 
+    # ---- speculative / eager staging (PreadExpertStreamer.swift:330-469) ----------------------------------------------
+    def non_resident_experts(self, experts: Sequence[int]) -> List[int]:
+        """The experts of a prediction that no slot holds (what is worth reading ahead), in order, without duplicates."""
+        table = self.slot_of_host()
+        out: List[int] = []
+        for e in experts:
+            if 0 <= e < self.num_experts and table[e] < 0 and e not in out:
+                out.append(e)
+        return out
+
+    def reserve_speculative_slots(self, experts: Sequence[int], keep_evictable: int) -> List[tuple]:
+        """reserveSpeculativeSlots: [(expert, slot)] for as many of `experts` as fit while `keep_evictable` evictable slots
+        stay untouched; the reserved slots are in flight (never victims, reading -1) until the reservation is executed."""
+        n = len(experts)
+        if n == 0:
+            return []
+        ex = (C.c_int32 * n)(*experts)
+        out_e, out_s, out_n = (C.c_int32 * n)(), (C.c_int32 * n)(), C.c_uint32()
+        L.check(self.lib.mfb_pool_reserve_speculative(self.handle, ex, n, max(0, keep_evictable), out_e, out_s, C.byref(out_n)))
+        return [(out_e[i], out_s[i]) for i in range(out_n.value)]
+
+    def execute_speculative_reservation(self, reservation: Sequence[tuple], host_blobs, stream: int = 0) -> int:
+        """executeSpeculativeReservation: copies every reserved expert that `host_blobs` can supply into its slot on
+        `stream`, then publishes exactly those (an expert without a source - the failed read of the reference - leaves
+        its slot empty) and clears every in-flight mark.  Returns the bytes queued."""
+        n = len(reservation)
+        if n == 0:
+            return 0
+        ex = (C.c_int32 * n)(*[e for e, _ in reservation])
+        sl = (C.c_int32 * n)(*[s for _, s in reservation])
+        loaded = (C.c_uint8 * n)(*[1 if host_blobs.get(e) is not None else 0 for e, _ in reservation])
+        ptrs = (C.c_void_p * n)()
+        blob_bytes = None
+        for i, (e, _) in enumerate(reservation):
+            if loaded[i]:
+                t = host_blobs[e]
+                ptrs[i] = t.data_ptr()
+                size = t.numel() * t.element_size()
+                if blob_bytes is not None and size != blob_bytes:
+                    raise L.MfbError(L.ERR_IO, f"expert blobs of different sizes in one fill ({blob_bytes} and {size} bytes)")
+                blob_bytes = size
+        if blob_bytes is not None:
+            L.check(self.lib.mfb_pool_fill_async(self.handle, C.c_void_p(stream), ex, sl, loaded, n, ptrs, blob_bytes))
+        L.check(self.lib.mfb_pool_finish_speculative(self.handle, C.c_void_p(stream), ex, sl, loaded, n))
+        return sum(loaded) * (blob_bytes or 0)
+
+    def begin_async_fill(self, plan: ExpertCachePlan, host_blobs, stream: int = 0) -> bool:
+        """beginAsyncFill: the plan's miss slots are marked in flight (concurrent plans keep away from them), their copies
+        are queued on `stream` and published behind them in stream order; GPU work the caller queues on the same stream
+        afterwards sees the filled slots.  False = at least one source was missing: that slot stays unpublished and the
+        caller must not use the layer's result (the reference's completion(false))."""
+        pairs = [(plan.experts[i], plan.assigned_slots[i]) for i in plan.misses]
+        if not pairs:
+            return True
+        sl = (C.c_int32 * len(pairs))(*[s for _, s in pairs])
+        L.check(self.lib.mfb_pool_mark_in_flight(self.handle, sl, len(pairs)))
+        sizes = {host_blobs[e].numel() * host_blobs[e].element_size() for e, _ in pairs if host_blobs.get(e) is not None}
+        queued = self.execute_speculative_reservation(pairs, host_blobs, stream)
+        return len(sizes) == 1 and queued == len(pairs) * next(iter(sizes))
+
     def note_all_hit_use(self, experts: Sequence[int]):
         ex = (C.c_int32 * max(len(experts), 1))(*experts)
         L.check(self.lib.mfb_pool_note_all_hit(self.handle, ex, len(experts)))

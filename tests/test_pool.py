@@ -132,3 +132,98 @@ def test_decode_through_a_partially_resident_pool_matches_full_residency():
     moe.encode_layer(staged, x, y_pool)
     torch.cuda.synchronize()
     assert torch.equal(y_pool, y_full)
+
+
+# ---- speculative / eager staging (PreadExpertStreamer.swift:330-469) -------------------------------------------------
+
+class _FakeBlob:
+    """Stands in for a pinned host tensor on the host-only pool (nothing is copied there)."""
+
+    def __init__(self, n):
+        self.n = n
+
+    def data_ptr(self):
+        return 0
+
+    def numel(self):
+        return self.n
+
+    def element_size(self):
+        return 1
+
+
+def test_speculative_reservation_protects_predicted_and_in_flight_slots_and_keeps_room():
+    pool = ExpertPool(16, 1024, 6, host_only=True)
+    _warm(pool, [0, 1, 2, 3])                 # slots 0-3 hold experts 0-3, slots 4 and 5 are empty
+    assert pool.non_resident_experts([2, 9, 9, 3, 10, 99]) == [9, 10]
+    # predicted expert 2 is resident: its slot may not be taken; two evictable slots must stay for the real plan
+    res = pool.reserve_speculative_slots([9, 10, 11, 12], keep_evictable=2)
+    # evictable = 6 slots - none in flight - the slot of ... (no predicted expert is among the wanted ids 9-12) = 6,
+    # budget = min(4, 6 - 2) = 4, empty slots go first
+    assert [e for e, _ in res] == [9, 10, 11, 12]
+    assert {s for _, s in res[:2]} == {4, 5}
+    table = pool.slot_of_host()
+    assert all(table[e] == -1 for e in (9, 10, 11, 12))          # nothing is published yet
+    evicted = [e for e in (0, 1, 2, 3) if table[e] == -1]
+    assert len(evicted) == 2                                      # two resident experts gave up their slots
+    # a second prediction while the first is in flight: its slots are never victims, and with keep_evictable = 2 the two
+    # slots left are out of reach
+    assert pool.reserve_speculative_slots([13], keep_evictable=2) == []
+    # a real plan in between keeps away from the in-flight slots too
+    plan = pool.plan_experts_cached([14])
+    assert plan.assigned_slots[0] not in {s for _, s in res}
+    # one read fails (no source for expert 11): its slot stays empty, the others become hits, marks are cleared
+    blobs = {9: _FakeBlob(1024), 10: _FakeBlob(1024), 12: _FakeBlob(1024)}
+    with pytest.raises(L.MfbError):                               # host-only pool: copies are refused, bookkeeping is not
+        pool.execute_speculative_reservation(res, blobs)
+    ex = [e for e, _ in res]
+    sl = [s for _, s in res]
+    import ctypes as C
+    L.check(pool.lib.mfb_pool_finish_speculative(pool.handle, None, (C.c_int32 * 4)(*ex), (C.c_int32 * 4)(*sl),
+                                                 (C.c_uint8 * 4)(1, 1, 0, 1), 4))
+    table = pool.slot_of_host()
+    assert [table[e] for e in (9, 10, 12)] == [sl[0], sl[1], sl[3]] and table[11] == -1
+    assert len(pool.reserve_speculative_slots([13], keep_evictable=0)) == 1     # the marks are gone
+
+
+def test_speculative_reservation_writes_no_policy_bookkeeping():
+    # LFU: expert 0 used three times, expert 1 once.  A speculative guess of expert 1's neighbours must not change which
+    # expert the next real plan evicts.
+    a = ExpertPool(8, 1024, 2, policy=LFU, host_only=True)
+    b = ExpertPool(8, 1024, 2, policy=LFU, host_only=True)
+    for pool in (a, b):
+        _warm(pool, [0, 1])
+        _warm(pool, [0])
+        _warm(pool, [0])
+    assert b.reserve_speculative_slots([5, 6], keep_evictable=2) == []          # no room beyond what must stay evictable
+    for pool in (a, b):
+        plan = pool.plan_experts_cached([7])
+        assert pool.slot_of_host()[1] == -1 and pool.slot_of_host()[0] >= 0     # the less used expert 1 went, in both
+
+
+@pytest.mark.gpu
+def test_speculative_and_eager_fills_move_blobs_and_respect_failures():
+    import torch
+    E, n_bytes = 8, 4096
+    pool = ExpertPool(E, n_bytes, 4)
+    blobs = {e: torch.full((n_bytes,), e + 1, dtype=torch.uint8).pin_memory() for e in range(E)}
+    stream = torch.cuda.current_stream().cuda_stream
+    res = pool.reserve_speculative_slots(pool.non_resident_experts([2, 5]), keep_evictable=2)
+    assert [e for e, _ in res] == [2, 5]
+    assert pool.execute_speculative_reservation(res, blobs, stream) == 2 * n_bytes
+    torch.cuda.synchronize()
+    slab, table = pool.slab_tensor(), pool.slot_of_tensor().cpu().numpy()
+    for e, s in res:
+        assert table[e] == s and bool((slab[s * pool.slot_stride: s * pool.slot_stride + n_bytes] == e + 1).all())
+    # eager fill of a real plan: expert 2 hits, 6 and 7 miss; the source of 7 is missing -> reported, slot unpublished
+    plan = pool.plan_experts_cached([2, 6, 7])
+    assert plan.hits == 1
+    partial = {k: v for k, v in blobs.items() if k != 7}
+    assert pool.begin_async_fill(plan, partial, stream) is False
+    torch.cuda.synchronize()
+    table = pool.slot_of_tensor().cpu().numpy()
+    assert table[6] == plan.assigned_slots[1] and table[7] == -1 and table[2] == plan.assigned_slots[0]
+    plan2 = pool.plan_experts_cached([7])
+    assert pool.begin_async_fill(plan2, blobs, stream) is True
+    torch.cuda.synchronize()
+    assert pool.slot_of_tensor().cpu().numpy()[7] == plan2.assigned_slots[0]
