@@ -343,12 +343,12 @@ class DecodeBench:
             if NL > 1:
                 phase_us["combine_to_next_layer"] = round(float((st[1:, 0] - st[:-1, 7]).mean() / 1e3), 2)
                 phase_us["layer_period"] = round(float((st[1:, 0] - st[:-1, 0]).mean() / 1e3), 2)
-            # SM-cycle counters of CTA 0, per layer: a computing warp's wait for a stage and its work on it, per FFN
+            # SM-cycle counters of one CTA (number 1), per layer: a computing warp's wait for a stage and its work on it, per FFN
             # phase; the copy-issuing warp's time spent issuing (mostly waiting for a free stage)
             cyc = tr[NL:NL + 17].cpu().numpy().astype("float64") / NL
             cw = [r for r in range(16) if cyc[r, 1] > 0 or cyc[r, 3] > 0]     # the computing warps (8 or 16)
             cp = 16 if len(cw) == 16 else 8                                     # the copy-issuing warp follows them
-            phase_us["cta0_kcycles_per_layer"] = {
+            phase_us["cta_kcycles_per_layer"] = {
                 "computing_warps": len(cw),
                 "phase1_wait": round(float(cyc[cw, 0].mean() / 1e3), 2), "phase1_compute": round(float(cyc[cw, 1].mean() / 1e3), 2),
                 "phase2_wait": round(float(cyc[cw, 2].mean() / 1e3), 2), "phase2_compute": round(float(cyc[cw, 3].mean() / 1e3), 2),

@@ -358,9 +358,10 @@ __device__ __forceinline__ uint32_t unit_at_cut(const mfb_group* groups, uint32_
     return pref[lo] + tt * tiles + min(rem / w, tiles - 1);
 }
 
-// Optional cycle accounting of CTA 0 (attached with the phase trace): counter k of warp w at dbg[w*8 + k].
+// Optional cycle accounting of one CTA (attached with the phase trace): counter k of warp w at dbg[w*8 + k].  The
+// CTA is number 1 where there is one: with a single token CTA 0 can be left without a unit.
 __device__ __forceinline__ void dbg_add(unsigned long long* dbg, uint32_t warp, uint32_t lane, int k, long long t0) {
-    if (dbg && blockIdx.x == 0 && lane == 0) atomicAdd(&dbg[warp * 8 + k], (unsigned long long)(clock64() - t0));   // no result: does not stall
+    if (dbg && blockIdx.x == (gridDim.x > 1 ? 1u : 0u) && lane == 0) atomicAdd(&dbg[warp * 8 + k], (unsigned long long)(clock64() - t0));   // no result: does not stall
 }
 
 // Advances `g` until unit u lies in group g (units are visited in increasing order).
@@ -449,6 +450,27 @@ __device__ __forceinline__ bool phase_produce(const FastParams& P, const PhaseGe
                  &C.full[s]);
     }
     return true;
+}
+
+// Single-token mode of the fused kernel: asks L2 for the bytes of one unit of the NEXT phase while this phase still
+// runs (the whole layer's traffic is a fraction of L2 there, and the phase after the grid barrier then starts from
+// L2 hits instead of DRAM latency).  Mirrors phase_produce.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+template <int NMAT>
+__device__ __forceinline__ void phase_prefetch_l2(const PhaseGeom& geo, const GroupRef& G, uint32_t tile, uint32_t lane) {
+    if (!G.ok) return;
+    const uint32_t row0 = tile * geo.tile_rows, row_bytes = geo.k * G.bits / 8;
+    const uint32_t* off = &G.off.gate_w;
+    if (lane < NMAT) {
+        const uint32_t w_off = NMAT == 2 ? off[3 * lane] : off[6];
+        bulk_prefetch_l2(G.blob + w_off + (size_t)row0 * row_bytes, geo.tile_rows * row_bytes);
+    } else if (lane < 3 * NMAT) {
+        const uint32_t i = lane - NMAT, m = i >> 1, sb = i & 1;
+        const uint32_t s_off = NMAT == 2 ? off[3 * m + 1 + sb] : off[7 + sb];
+        bulk_prefetch_l2(G.blob + s_off + (size_t)row0 * geo.gpr * 2, geo.scale_block);
+    }
 }
 
 // B fragments of this warp's k range for token column g of a token tile: registers, loaded from L2 (or from shared
@@ -1142,11 +1164,14 @@ __device__ __forceinline__ bool grid_barrier(const MegaParams& M, FastShared& S,
     __syncthreads();
     if (threadIdx.x == 0) {
         epoch += gridDim.x;
-        __threadfence();
-        atomicAdd(M.bar_counter, 1u);
+        // release at GPU scope: cumulative over what the CTA's threads wrote before the __syncthreads above; the acquire
+        // load of the poll below is its counterpart, so no separate fences
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(M.bar_counter), "r"(1u) : "memory");
         bool ok = true;
         const long long t0 = clock64();
-        while (ld_acquire_u32(M.bar_counter) < epoch) {
+        // one L2 round trip per poll: the abort word and the clock are looked at every sixteenth poll only
+        for (uint32_t polls = 1; ld_acquire_u32(M.bar_counter) < epoch; ++polls) {
+            if (polls & 15u) continue;
             if (ld_acquire_u32(M.abort) != 0u) { ok = false; break; }
             if (clock64() - t0 > GRID_WAIT_CYCLES) {
                 atomicOr(M.status, STATUS_GRID_BARRIER_TIMEOUT);
@@ -1155,7 +1180,6 @@ __device__ __forceinline__ bool grid_barrier(const MegaParams& M, FastShared& S,
                 break;
             }
         }
-        __threadfence();
         S.flag = ok ? 1u : 0u;
     }
     __syncthreads();
@@ -1164,15 +1188,25 @@ __device__ __forceinline__ bool grid_barrier(const MegaParams& M, FastShared& S,
 
 // RMSNorm of one row by the first 256 threads of the CTA, arithmetic and order of rmsnorm_kernel (glue.cu).
 // Writes the row in the activation dtype and in the permuted fp16 layout(s); the outputs may be global or shared.
+// With row_smem the row is read from shared memory (the single-token mode keeps the residual stream there).
 __device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLayer& Ly, FastShared& S, const void* h,
-                                              uint32_t tok, uint16_t* xn_out, __half* xp_out, __half* xp2_out) {
+                                              uint32_t tok, uint16_t* xn_out, __half* xp_out, __half* xp2_out,
+                                              const uint16_t* row_smem = nullptr) {
     const uint32_t d = M.d, tid = threadIdx.x;
     const uint16_t* src = (const uint16_t*)h + (size_t)tok * d;
+    // the gain of this thread's first eight columns is requested now, so that its latency runs beside the reductions
+    constexpr uint32_t GAIN_REGS = 8;
+    float gain[GAIN_REGS];
+#pragma unroll
+    for (uint32_t j = 0; j < GAIN_REGS; ++j) {
+        const uint32_t i = tid + 256 * j;
+        gain[j] = (tid < 256 && i < d && Ly.norm_w) ? __bfloat162float(Ly.norm_w[i]) : 1.0f;
+    }
     float ss = 0.0f;
     if (tid < 256) {
 #pragma unroll 8
         for (uint32_t i = tid; i < d; i += 256) {
-            const float v = widen16(ld_cg_u16(src + i), M.x_dtype);
+            const float v = widen16(row_smem ? row_smem[i] : ld_cg_u16(src + i), M.x_dtype);
             ss = fmaf(v, v, ss);
         }
     }
@@ -1187,9 +1221,20 @@ __device__ __forceinline__ void mega_norm_row(const MegaParams& M, const MegaLay
     __syncthreads();
     const float inv = rsqrtf(S.red[8] / (float)d + M.eps);
     if (tid < 256) {
-#pragma unroll 8
-        for (uint32_t i = tid; i < d; i += 256) {
-            float v = widen16(ld_cg_u16(src + i), M.x_dtype);
+#pragma unroll
+        for (uint32_t j = 0; j < GAIN_REGS; ++j) {
+            const uint32_t i = tid + 256 * j;
+            if (i >= d) break;
+            float v = widen16(row_smem ? row_smem[i] : ld_cg_u16(src + i), M.x_dtype);
+            v = v * inv * gain[j];
+            const uint16_t bits = narrow16(v, M.x_dtype);
+            xn_out[i] = bits;
+            v = fminf(fmaxf(widen16(bits, M.x_dtype), -65504.0f), 65504.0f);
+            xp_out[(i & ~15u) + perm_pos(i & 15u, M.bits)] = __float2half_rn(v * perm_scale(i & 15u, M.bits));
+            if (xp2_out) xp2_out[(i & ~15u) + perm_pos(i & 15u, M.shared_bits)] = __float2half_rn(v * perm_scale(i & 15u, M.shared_bits));
+        }
+        for (uint32_t i = tid + 256 * GAIN_REGS; i < d; i += 256) {
+            float v = widen16(row_smem ? row_smem[i] : ld_cg_u16(src + i), M.x_dtype);
             const float gw = Ly.norm_w ? __bfloat162float(Ly.norm_w[i]) : 1.0f;
             v = v * inv * gw;
             const uint16_t bits = narrow16(v, M.x_dtype);
@@ -1400,6 +1445,72 @@ __device__ __forceinline__ void mega_group_mask(const MegaParams& M, FastShared&
     __syncthreads();
 }
 
+// Single-token mode, gate logits: one warp per expert (expert e by warp e / grid of CTA e % grid).  The gate row does
+// not depend on the activations: its asynchronous copy into the warp's shared-memory row starts at the top of the layer
+// and lands while the norm runs.  Same summation order as router_logits_kernel.
+__device__ __forceinline__ void single_fetch_gate_row(const MegaParams& M, const MegaLayer& Ly, uint32_t e, uint32_t lane, uint16_t* wrow) {
+    if (e < M.num_experts)
+        for (uint32_t c = lane; c < M.d / 8; c += 32) cp_async16(wrow + c * 8, Ly.router_w + (size_t)e * M.d + c * 8);
+    cp_async_commit();
+}
+
+__device__ __forceinline__ void single_logit(const MegaParams& M, const MegaLayer& Ly, uint32_t e, uint32_t lane, const uint16_t* wrow,
+                                             const uint16_t* xn_s) {
+    cp_async_wait_all();
+    __syncwarp();
+    if (e >= M.num_experts) return;
+    float acc = 0.0f;
+#pragma unroll 8
+    for (uint32_t i = lane; i < M.d; i += 32) acc = fmaf(__uint_as_float((uint32_t)wrow[i] << 16), widen16(xn_s[i], M.x_dtype), acc);
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    if (lane == 0) {
+        if (Ly.logit_bias) acc = acc + Ly.logit_bias[e];
+        M.logits[e] = acc;
+    }
+}
+
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+// Single-token mode, combine: every CTA forms the whole new row itself from the fp32 partial rows (rank order, as
+// combine_slice) and keeps it in shared memory as the next layer's input; CTA 0 also stores it.  Four columns per
+// thread, the loads of up to eight ranks in flight together.
+__device__ __forceinline__ void single_combine(const MegaParams& M, const uint16_t* w_s, bool with_shared, uint16_t* h_s, void* h_out) {
+    const uint32_t d = M.d;
+    for (uint32_t c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+        const float* pt = M.partial + c;
+        const uint2 hb = *reinterpret_cast<const uint2*>(h_s + c);
+        float acc[4] = {widen16((uint16_t)(hb.x & 0xFFFFu), M.x_dtype), widen16((uint16_t)(hb.x >> 16), M.x_dtype),
+                        widen16((uint16_t)(hb.y & 0xFFFFu), M.x_dtype), widen16((uint16_t)(hb.y >> 16), M.x_dtype)};
+        if (with_shared) {
+            const float4 sh = ld_cg_f4(pt + (size_t)M.top_k * d);
+            acc[0] += sh.x; acc[1] += sh.y; acc[2] += sh.z; acc[3] += sh.w;
+        }
+        for (uint32_t k0 = 0; k0 < M.top_k; k0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) v[j] = k0 + j < M.top_k ? ld_cg_f4(pt + (size_t)(k0 + j) * d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) {
+                if (k0 + j < M.top_k) {
+                    const float w = __half2float(__ushort_as_half(w_s[k0 + j]));
+                    acc[0] = fmaf(w, v[j].x, acc[0]); acc[1] = fmaf(w, v[j].y, acc[1]);
+                    acc[2] = fmaf(w, v[j].z, acc[2]); acc[3] = fmaf(w, v[j].w, acc[3]);
+                }
+            }
+        }
+        uint2 ob;
+        ob.x = (uint32_t)narrow16(acc[0], M.x_dtype) | ((uint32_t)narrow16(acc[1], M.x_dtype) << 16);
+        ob.y = (uint32_t)narrow16(acc[2], M.x_dtype) | ((uint32_t)narrow16(acc[3], M.x_dtype) << 16);
+        *reinterpret_cast<uint2*>(h_s + c) = ob;
+        if (blockIdx.x == 0) *reinterpret_cast<uint2*>((uint16_t*)h_out + c) = ob;
+    }
+    __syncthreads();
+}
+
 // MODE 0: at most 16 rows (one-warp scan for the sort, flat unit weights); 1: more rows, k-split FFN phases;
 // 2: more rows, row-stationary FFN phases (every layer carries tensor maps).
 template <int NGW, int MODE>
@@ -1415,7 +1526,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     const PhaseGeom geo1 = phase_geom(2, M.d, M.f, NGW, max_bits, RING_BYTES);
     const PhaseGeom geo2 = phase_geom(1, M.f, M.d, 4, max_bits, RING_BYTES);
     const uint32_t n_pairs = M.n_tokens * M.top_k;
-    const bool single = M.n_tokens == 1;
+    const bool single = MODE == 0 && M.n_tokens == 1;   // compiled out of the large-batch forms
     // ---- shared memory carve-up.  Region A holds the stage ring of whichever phase runs plus the k-split exchange
     // buffers; during the router phase it stages gate rows.  The routing lists follow it.
     uint8_t* region_a = smem;
@@ -1432,8 +1543,10 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
     uint16_t* xn_s = reinterpret_cast<uint16_t*>((reinterpret_cast<uintptr_t>(run_s + M.num_experts) + 15) & ~(uintptr_t)15);
     __half* xp_s = reinterpret_cast<__half*>(xn_s + M.d);
     __half* xp2_s = xp_s + M.d;
+    uint16_t* h_s = reinterpret_cast<uint16_t*>(xp2_s + M.d);   // single-token mode: the residual stream's row
 
     init_barriers(S);
+    uint32_t split_groups = 0;
     uint32_t epoch = 0, seq1 = 0, seq2 = 0;   // row-stationary form: seq1 counts stages, seq2 scale blocks
     bool alive = true;
     // SM clock against the global timer over the whole launch (row 16 of the cycle counters): cycles per ns
@@ -1461,11 +1574,23 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         };
         stamp(0);
         if (single) {
-            // every CTA normalises the one row itself (no barrier), computes the logits of its experts, and after
-            // the barrier every CTA repeats the selection: two grid barriers fewer per layer
-            mega_norm_row(M, Ly, S, h, 0, xn_s, xp_s, M.xp2 ? xp2_s : nullptr);
+            // every CTA keeps the row in shared memory and normalises it itself (no barrier), computes the logits of
+            // its experts, and after the barrier every CTA repeats the selection: two grid barriers fewer per layer.
+            // The gate rows do not depend on the row: they are requested first.
+            const uint32_t e_w = blockIdx.x + warp * gridDim.x;
+            uint16_t* gate_row = reinterpret_cast<uint16_t*>(region_a) + (size_t)warp * M.d;
+            single_fetch_gate_row(M, Ly, e_w, lane, gate_row);
+            if (l == 0 || M.layer_stride != 0) {
+                for (uint32_t i = threadIdx.x; i < M.d; i += blockDim.x) h_s[i] = ld_cg_u16((const uint16_t*)h + i);
+                __syncthreads();
+            }
+            mega_norm_row(M, Ly, S, h, 0, xn_s, xp_s, M.xp2 ? xp2_s : nullptr, h_s);
             stamp(1);
-            mega_logits(M, Ly, region_a, xn_s);
+            single_logit(M, Ly, e_w, lane, gate_row, xn_s);
+            for (uint32_t e = e_w + (blockDim.x >> 5) * gridDim.x; e < M.num_experts; e += (blockDim.x >> 5) * gridDim.x) {
+                single_fetch_gate_row(M, Ly, e, lane, gate_row);   // more experts than warps in the grid: further rounds
+                single_logit(M, Ly, e, lane, gate_row, xn_s);
+            }
             if (!(alive = grid_barrier(M, S, epoch))) break;
             stamp(2);
             float* lg_s = red;
@@ -1536,7 +1661,11 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             else mega_group_scan(M, S, idx_s, w_s, run_s, sorted_s, groups_s, shared);
         }
         const uint32_t n_groups = S.n_groups;
-        if (warp == 0) {
+        // one token: every group holds one pair, so the split of the units over the CTAs is that of the first layer
+        // as long as the group count (shared expert or not) stays what it was
+        const bool same_split = single && l > 0 && n_groups == split_groups;
+        split_groups = n_groups;
+        if (warp == 0 && !same_split) {
             const UnitBases ub = WIDE ? wide_unit_bases() : unit_bases(LARGE_BATCH);
             uint32_t* wpref2 = reinterpret_cast<uint32_t*>(region_a);   // the stage ring is not in use yet
             warp_unit_prefix2<LARGE_BATCH>(groups_s, n_groups, tiles1, tiles2, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
@@ -1569,6 +1698,14 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             PhaseCtx C{region_a, S.full1, S.empty1, red, S.pref1};
             const uint32_t first = S.range[0], last = S.range[1];
             if (!run_phase<2, NGW>(P, geo1, C, n_groups, first, last, seq1, warp, lane)) { atomicOr(M.status, STATUS_MBAR_TIMEOUT); atomicExch(M.abort, 1u); }
+            if (single && warp == CW) {   // this CTA's phase-2 units, requested into L2 ahead of the barrier
+                uint32_t g2 = 0;
+                const uint32_t f2 = S.range[2], l2 = S.range[3];
+                for (uint32_t u = f2; u < l2; ++u) {
+                    seek_group(S.pref2, n_groups, u, g2);
+                    phase_prefetch_l2<1>(geo2, group_ref(P, g2), (u - S.pref2[g2]) % geo2.tiles, lane);
+                }
+            }
         }
         stamp(5);
         if (!(alive = grid_barrier(M, S, epoch))) break;
@@ -1588,14 +1725,18 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         if (!(alive = grid_barrier(M, S, epoch))) break;
         stamp(7);
         // ---- rank-ordered weighted combine, a contiguous slice of (token, column) outputs per CTA
-        {
+        if (single) {
+            // no barrier behind it: the next layer reads the row from this CTA's shared memory, and the partial rows are
+            // not written again before two more barriers
+            single_combine(M, w_s, shared, h_s, h);
+        } else {
             const uint32_t total = M.n_tokens * M.d, per = (total + gridDim.x - 1) / gridDim.x;
             const uint32_t begin = min(blockIdx.x * per, total);
             combine_slice(P, begin, min(begin + per, total), shared);
+            // rows of independent layers need no barrier here: the buffers the next layer writes first are not read by
+            // this combine, and the partial rows are not written again before three more barriers
+            if (M.layer_stride == 0 && !(alive = grid_barrier(M, S, epoch))) break;
         }
-        // rows of independent layers need no barrier here: the buffers the next layer writes first are not read by
-        // this combine, and the partial rows are not written again before three more barriers
-        if (M.layer_stride == 0 && !(alive = grid_barrier(M, S, epoch))) break;
     }
     clock_pair(1);
 }
@@ -1660,7 +1801,7 @@ size_t fast_smem2(const mfb_moe_config&, uint32_t) { return (size_t)RING_BYTES +
 size_t fast_smem_stack(const mfb_moe_config& c, uint32_t n_tokens, bool wide_form) {
     const size_t pairs = (size_t)n_tokens * c.top_k;
     const size_t lists = (pairs + n_tokens) * sizeof(mfb_pair) + (c.num_experts + 1) * sizeof(mfb_group) + pairs * 4 +
-                         ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 6 : 0);
+                         ((pairs + 1) & ~(size_t)1) * 2 + c.num_experts * 4 + 16 + (n_tokens == 1 ? (size_t)c.d * 8 : 0);
     const size_t region_a = wide_form && n_tokens > 16 ? (size_t)wide::RING_BYTES : (size_t)RING_BYTES + RED_BYTES;
     if ((size_t)c.d * (MEGA_MAX_EB * 4 + (CW + 1) * MEGA_MAX_TT * 2) > region_a)
         return (size_t)1 << 30;   // the router staging does not fit: the caller falls back to the per-layer launches
