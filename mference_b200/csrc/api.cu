@@ -50,7 +50,7 @@ cudaError_t dev_alloc(T*& p, size_t count) {
 }
 
 void free_arena(Arena& a) {
-    cudaFree(a.logits); cudaFree(a.idx); cudaFree(a.route_w); cudaFree(a.xn); cudaFree(a.sorted);
+    cudaFree(a.logits); cudaFree(a.router_ws); cudaFree(a.idx); cudaFree(a.route_w); cudaFree(a.xn); cudaFree(a.sorted);
     cudaFree(a.chunk_hist); cudaFree(a.offsets); cudaFree(a.counts); cudaFree(a.groups); cudaFree(a.n_groups);
     cudaFree(a.tile_prefix); cudaFree(a.acts); cudaFree(a.partial); cudaFree(a.xs16); cudaFree(a.acts16); cudaFree(a.xp); cudaFree(a.xp2); cudaFree(a.actp);
     cudaFree(a.status);
@@ -172,7 +172,7 @@ cudaError_t layer_logits(mfb_moe* m, cudaStream_t s, const mfb_layer_weights* w,
         return launch_gemv_int8(s, (const uint8_t*)w->router_w, w->router_scales, w->router_biases, x, (int)c.x_dtype, ldx, n_tokens,
                                 w->router_effective_scale, c.num_experts, c.d, logits);
     return launch_router_logits(s, x, (int)c.x_dtype, ldx, n_tokens, (const __nv_bfloat16*)w->router_w, c.num_experts, c.d,
-                                w->logit_bias, logits);
+                                w->logit_bias, logits, m->a.router_ws, m->a.router_ws_floats);
 }
 
 // Qwen shared-expert scalar gate: the shared expert's fp32 row of every token (rank slot top_k of `partial`) times
@@ -272,6 +272,8 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     cudaError_t e = cudaSuccess;
     auto ok = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
     ok(dev_alloc(a.logits, T * E));
+    a.router_ws_floats = router_workspace_floats(c.max_tokens, c.num_experts, c.d);
+    if (a.router_ws_floats) ok(dev_alloc(a.router_ws, a.router_ws_floats));
     ok(dev_alloc(a.idx, T * K));
     ok(dev_alloc(a.route_w, T * K));
     { uint16_t* p = nullptr; ok(dev_alloc(p, T * c.d)); a.xn = p; }
@@ -398,7 +400,8 @@ extern "C" int32_t mfb_router_logits(mfb_moe* moe, void* stream, const void* x, 
     MFB_REQUIRE(x && router_w && logits, MFB_ERR_INVALID_ARGUMENT, "router_logits: NULL argument");
     MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "router_logits: row stride smaller than d");
     MFB_CUDA(launch_router_logits((cudaStream_t)stream, x, (int)moe->cfg.x_dtype, ldx, n_tokens,
-                                  (const __nv_bfloat16*)router_w, moe->cfg.num_experts, moe->cfg.d, logit_bias, logits));
+                                  (const __nv_bfloat16*)router_w, moe->cfg.num_experts, moe->cfg.d, logit_bias, logits,
+                                  moe->a.router_ws, moe->a.router_ws_floats));
     return MFB_OK;
 }
 

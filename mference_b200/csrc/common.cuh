@@ -44,6 +44,8 @@ struct Arena {
     float* logits = nullptr;        // [max_tokens, E]
     uint32_t* idx = nullptr;        // [max_tokens, K]
     uint16_t* route_w = nullptr;    // [max_tokens, K] fp16 bits
+    float* router_ws = nullptr;     // fp32 lane-major copies for the prefill-size gate kernel (router_workspace_floats)
+    size_t router_ws_floats = 0;
     // normalised activations of a layer call, in x_dtype
     void* xn = nullptr;             // [max_tokens, d]
     // grouping
@@ -120,9 +122,13 @@ __device__ __forceinline__ float hidden_act(float g, int act) {
 
 // ---- launch prototypes ----------------------------------------------------------------------------------
 // router.cu
+// `workspace` (optional, router_workspace_floats() floats for a given row capacity): scratch for the fp32 lane-major
+// copies the prefill-size kernel reads; without it batches above 64 rows take the slower self-contained kernel.
+constexpr uint32_t ROUTER_WS_MAX_ROWS = 8192;   // token rows converted at a time
+size_t router_workspace_floats(uint32_t max_tokens, uint32_t num_experts, uint32_t d);
 cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
                                  const __nv_bfloat16* w, uint32_t num_experts, uint32_t d, const float* logit_bias,
-                                 float* logits);
+                                 float* logits, float* workspace = nullptr, size_t workspace_floats = 0);
 cudaError_t launch_router_select(cudaStream_t s, const float* logits, uint32_t n_tokens, uint32_t num_experts,
                                  uint32_t top_k, int mode, const __nv_bfloat16* per_expert_scale,
                                  const float* correction_bias, float route_scale, uint32_t* out_idx, uint16_t* out_w);

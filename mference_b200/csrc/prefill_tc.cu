@@ -269,7 +269,8 @@ struct TcShared {
     uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base, abort;
     uint32_t tp[MFB_MAX_EXPERTS + 2];
-    float* out_ptr[TC_TILE_N];     // phase 2: where the result row of each of the current item's token columns goes
+    float* out_ptr[TC_TILE_N];     // phase 2 with a destination table: where the result row of each token column goes
+    uint32_t out_row[TC_TILE_N];   // phase 2 without one: token * slots + rank of the current item's token columns
 };
 
 template <int PHASE>   // 1: gate / up over x;  2: down over the hidden activations
@@ -493,14 +494,17 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                 for (uint32_t n = te; n < I.n; n += TC_EPI_WARPS * 32) {
                     const mfb_pair pr = P.sorted[I.pair_start + n];
                     const size_t slot = (size_t)pr.token * P.slots + pr.rank;
-                    S.out_ptr[n] = P.row_dest ? P.row_dest[slot] : P.partial + slot * P.d;
+                    if (P.row_dest) S.out_ptr[n] = P.row_dest[slot];
+                    else S.out_row[n] = (uint32_t)slot;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
             }
             if (!I.ok) {
                 if (PHASE == 2)   // a non-resident expert contributes nothing: clear its partial rows
-                    for (uint32_t n = col_par; n < I.n; n += COL_WAYS)
-                        if (S.out_ptr[n]) S.out_ptr[n][out_row] = 0.0f;
+                    for (uint32_t n = col_par; n < I.n; n += COL_WAYS) {
+                        if (!P.row_dest) P.partial[(size_t)S.out_row[n] * P.d + out_row] = 0.0f;
+                        else if (S.out_ptr[n]) S.out_ptr[n][out_row] = 0.0f;
+                    }
                 continue;
             }
             const uint32_t buf = 0, use = item & 1u;
@@ -533,11 +537,20 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                     }
                 } else {
                     const uint32_t live = min(32u, I.n - col0);
+                    if (!P.row_dest) {
+                        float* out = P.partial + out_row;
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i) {
-                        if (i >= live) break;
-                        float* out = S.out_ptr[col0 + i];
-                        if (out) out[out_row] = v[i];
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            if (i >= live) break;
+                            out[(size_t)S.out_row[col0 + i] * P.d] = v[i];
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            if (i >= live) break;
+                            float* out = S.out_ptr[col0 + i];
+                            if (out) out[out_row] = v[i];
+                        }
                     }
                 }
             }

@@ -6,6 +6,8 @@
 // xor butterfly (16, 8, 4, 2, 1), and an optional per-expert bias is added last.  That is the structure of
 // router_gemv_bf16_r4 (Sources/Mference/Metal/MoE/moe.metal:162-185) with its lane sum made concrete, and it
 // makes a block of B token rows bit-identical to B single-row calls.
+#include <algorithm>
+
 #include "common.cuh"
 #include "decode_mma.cuh"
 #include "select.cuh"
@@ -212,6 +214,125 @@ router_logits_tile_kernel(const void* __restrict__ x, int x_dtype, uint32_t ldx,
         }
 }
 
+// ---------------------------------------------------------------------------------------------- prefill-size gate
+// Thousands of token rows: the same sums in the same order, arranged so that the multiply-adds are nearly the only
+// instructions issued.  A first pass (router_lane_major_kernel) widens the activations and the gate to fp32 and stores
+// every 128-element chunk of a row lane-major: position 4*l + s of a chunk holds element 32*s + l, i.e. the four
+// elements lane l adds, in the order it adds them.  The tile kernel then needs no conversion and no address
+// arithmetic: 16-byte asynchronous copies bring [32 token rows + 32 gate rows] x 128 floats per stage into a
+// four-stage ring, and lane l reads its four values of a row with ONE conflict-free 16-byte shared-memory load
+// (consecutive lanes, consecutive 16 bytes).  Sixteen warps as 4 x 4, a warp holds 8 tokens x 8 experts as 64
+// accumulators; per stage it issues 16 loads for 256 multiply-adds.  The 32 lane sums of each dot product are
+// combined by a butterfly in which every step halves the number of values a lane still carries (lanes whose bit
+// `off` is clear keep the lower half of the values, the others the upper half): each value goes through the additions
+// of the xor butterfly 16, 8, 4, 2, 1 with the same partners, and since a + b == b + a in IEEE arithmetic the result
+// is bit-identical to it with 62 instead of 320 shuffles.
+constexpr uint32_t RQ_TM = 32, RQ_TE = 32, RQ_KC = 128, RQ_STAGES = 4;
+#ifndef MFB_RQ_NW
+#define MFB_RQ_NW 8
+#endif
+constexpr int RQ_NW = MFB_RQ_NW, RQ_EW = 128 / RQ_NW;
+constexpr uint32_t RQ_STAGE_FLOATS = (RQ_TM + RQ_TE) * RQ_KC;
+constexpr uint32_t RQ_SMEM_BYTES = RQ_STAGES * RQ_STAGE_FLOATS * 4;
+
+__global__ void router_lane_major_kernel(const void* __restrict__ src, int dtype, uint32_t ld, uint32_t rows, uint32_t d,
+                                         float* __restrict__ dst) {
+    const uint32_t per_row = d / 4;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * per_row) return;
+    const uint32_t row = (uint32_t)(i / per_row), q = (uint32_t)(i % per_row), c = q / 32, l = q % 32;
+    const size_t base = (size_t)row * ld + c * RQ_KC + l;
+    reinterpret_cast<float4*>(dst)[i] = make_float4(load_act(src, base, dtype), load_act(src, base + 32, dtype),
+                                                    load_act(src, base + 64, dtype), load_act(src, base + 96, dtype));
+}
+
+__device__ __forceinline__ void rq_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int N, int OFF>   // one step of the halving butterfly over v[0, N)
+__device__ __forceinline__ void rq_halve(float* v, uint32_t lane) {
+    const bool upper = (lane & OFF) != 0;
+#pragma unroll
+    for (int a = 0; a < N / 2; ++a) {
+        const float keep = upper ? v[a + N / 2] : v[a], send = upper ? v[a] : v[a + N / 2];
+        v[a] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, OFF);
+    }
+}
+
+template <int NW, int EW>   // warps per block (4 token groups x NW/4 expert groups), experts per warp: NW/4 * EW = 32
+__global__ void __launch_bounds__(NW * 32, 1)
+router_logits_lane_major_kernel(const float* __restrict__ xq, uint32_t n_tokens, const float* __restrict__ wq, uint32_t num_experts,
+                                uint32_t d, const float* __restrict__ logit_bias, float* __restrict__ logits) {
+    static_assert((NW / 4) * EW == (int)RQ_TE, "tile shape");
+    constexpr uint32_t THREADS = NW * 32, COPIES = (RQ_TM + RQ_TE) * (RQ_KC / 4) / THREADS, NV = 8 * EW;
+    extern __shared__ __align__(16) float rq_smem[];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t t0 = blockIdx.y * RQ_TM, e0 = blockIdx.x * RQ_TE;
+    const uint32_t wt = (warp & 3u) * 8, we = (warp >> 2) * EW;
+    const uint32_t n_chunks = d / RQ_KC;
+    // copies of one stage: 64 rows x 32 pieces of 16 bytes; rows past the end repeat the last one (their sums are
+    // computed and dropped)
+    const float* src_row[COPIES];
+    uint32_t dst_off[COPIES];
+#pragma unroll
+    for (uint32_t j = 0; j < COPIES; ++j) {
+        const uint32_t piece = tid + j * THREADS, r = piece / 32, p = piece % 32;
+        src_row[j] = r < RQ_TM ? xq + (size_t)min(t0 + r, n_tokens - 1) * d + p * 4
+                               : wq + (size_t)min(e0 + r - RQ_TM, num_experts - 1) * d + p * 4;
+        dst_off[j] = r * RQ_KC + p * 4;
+    }
+    auto issue = [&](uint32_t c) {
+        if (c < n_chunks) {
+            float* st = rq_smem + (c % RQ_STAGES) * RQ_STAGE_FLOATS;
+#pragma unroll
+            for (uint32_t j = 0; j < COPIES; ++j) rq_cp_async16(st + dst_off[j], src_row[j] + (size_t)c * RQ_KC);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[8][EW];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < EW; ++j) acc[i][j] = 0.0f;
+    for (uint32_t c = 0; c + 1 < RQ_STAGES; ++c) issue(c);
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(RQ_STAGES - 2) : "memory");
+        __syncthreads();                 // chunk c has landed for every thread, and chunk c - 1 has been read by every warp
+        issue(c + RQ_STAGES - 1);        // into the stage chunk c - 1 used
+        const float4* st = reinterpret_cast<const float4*>(rq_smem + (c % RQ_STAGES) * RQ_STAGE_FLOATS);
+        float4 xv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xv[i] = st[(wt + i) * (RQ_KC / 4) + lane];
+#pragma unroll
+        for (int j = 0; j < EW; ++j) {
+            const float4 wv = st[(RQ_TM + we + j) * (RQ_KC / 4) + lane];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {   // ascending k for this lane: c*128 + lane, + 32, + 64, + 96
+                acc[i][j] = fmaf(wv.x, xv[i].x, acc[i][j]);
+                acc[i][j] = fmaf(wv.y, xv[i].y, acc[i][j]);
+                acc[i][j] = fmaf(wv.z, xv[i].z, acc[i][j]);
+                acc[i][j] = fmaf(wv.w, xv[i].w, acc[i][j]);
+            }
+        }
+    }
+    // halving butterfly over the NV values (index a = EW i + j): after the step with offset `off` a lane keeps the half
+    // of its values selected by its bit `off`; at the end lane l holds values (NV/32) l ... (NV/32) l + NV/32 - 1
+    float (&v)[NV] = reinterpret_cast<float (&)[NV]>(acc);
+    rq_halve<NV, 16>(v, lane);
+    rq_halve<NV / 2, 8>(v, lane);
+    rq_halve<NV / 4, 4>(v, lane);
+    rq_halve<NV / 8, 2>(v, lane);
+    rq_halve<NV / 16, 1>(v, lane);
+    constexpr uint32_t PER = NV / 32, LPR = EW / PER;   // values per lane; lanes per token row
+    const uint32_t t = t0 + wt + lane / LPR, e = e0 + we + PER * (lane % LPR);
+    if (t < n_tokens) {
+#pragma unroll
+        for (uint32_t j = 0; j < PER; ++j)
+            if (e + j < num_experts) logits[(size_t)t * num_experts + e + j] = logit_bias ? v[j] + logit_bias[e + j] : v[j];
+    }
+}
+
 __global__ void router_select_kernel(const float* __restrict__ logits, uint32_t n_tokens, uint32_t num_experts,
                                      uint32_t top_k, int mode, const __nv_bfloat16* __restrict__ per_expert_scale,
                                      const float* __restrict__ correction_bias, float route_scale,
@@ -318,9 +439,15 @@ __global__ void slot_lookup_kernel(const uint32_t* __restrict__ idx, uint32_t n_
 
 }  // namespace
 
+size_t router_workspace_floats(uint32_t max_tokens, uint32_t num_experts, uint32_t d) {
+    if (max_tokens <= 64 || d % RQ_KC != 0) return 0;
+    const uint64_t rows = max_tokens < ROUTER_WS_MAX_ROWS ? max_tokens : ROUTER_WS_MAX_ROWS;
+    return (size_t)((rows + num_experts) * d);
+}
+
 cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
                                  const __nv_bfloat16* w, uint32_t num_experts, uint32_t d, const float* logit_bias,
-                                 float* logits) {
+                                 float* logits, float* workspace, size_t workspace_floats) {
     if (n_tokens == 0) return cudaSuccess;
     if (n_tokens <= 2) {
         // decode: one expert per warp keeps 64 blocks busy on a 256-expert gate
@@ -330,6 +457,28 @@ cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uin
     } else if (n_tokens <= 64) {
         dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 7) / 8);
         router_logits_kernel<8, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
+    } else if (workspace && d % RQ_KC == 0 && workspace_floats >= (size_t)(num_experts + 1) * d) {
+        // lane-major fp32 copies of the gate and of as many token rows as the workspace holds at a time
+        static bool attr_set = false;   // benign race: the attribute call is idempotent
+        if (!attr_set) {
+            const cudaError_t e = cudaFuncSetAttribute(router_logits_lane_major_kernel<RQ_NW, RQ_EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RQ_SMEM_BYTES);
+            if (e != cudaSuccess) return e;
+            attr_set = true;
+        }
+        float* wq = workspace;
+        float* xq = workspace + (size_t)num_experts * d;
+        const uint32_t cap = (uint32_t)std::min<size_t>((workspace_floats - (size_t)num_experts * d) / d, n_tokens);
+        const uint32_t per_row = d / 4;
+        router_lane_major_kernel<<<(uint32_t)(((size_t)num_experts * per_row + 255) / 256), 256, 0, s>>>(w, MFB_DT_BF16, d, num_experts, d, wq);
+        for (uint32_t t0 = 0; t0 < n_tokens; t0 += cap) {
+            const uint32_t n = std::min(cap, n_tokens - t0);
+            const void* xs = (const uint8_t*)x + (size_t)t0 * ldx * (x_dtype == MFB_DT_F32 ? 4 : 2);
+            router_lane_major_kernel<<<(uint32_t)(((size_t)n * per_row + 255) / 256), 256, 0, s>>>(xs, x_dtype, ldx, n, d, xq);
+            dim3 grid((num_experts + RQ_TE - 1) / RQ_TE, (n + RQ_TM - 1) / RQ_TM);
+            router_logits_lane_major_kernel<RQ_NW, RQ_EW><<<grid, RQ_NW * 32, RQ_SMEM_BYTES, s>>>(xq, n, wq, num_experts, d, logit_bias,
+                                                                                                   logits + (size_t)t0 * num_experts);
+            count_launches(2);
+        }
     } else {
         dim3 grid((num_experts + RL_TE - 1) / RL_TE, (n_tokens + RL_TM - 1) / RL_TM);
         router_logits_tile_kernel<<<grid, 256, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);

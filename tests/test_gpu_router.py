@@ -18,7 +18,10 @@ def _moe(**kw):
 
 
 @pytest.mark.parametrize("T,E,D", [(1, 256, 2048), (2, 256, 2048), (8, 256, 2048), (64, 256, 2048), (300, 256, 2048),
-                                   (5, 40, 256), (3, 33, 64), (17, 100, 4096)])
+                                   (5, 40, 256), (3, 33, 64), (17, 100, 4096),
+                                   # above 64 rows: the lane-major fp32 kernel (d a multiple of 128; ragged row and expert
+                                   # counts, fewer chunks than ring stages) and the self-contained tile kernel (d = 64)
+                                   (130, 100, 1536), (1025, 256, 2048), (97, 33, 256), (70, 20, 64), (65, 1, 128)])
 def test_logits_bit_exact(T, E, D):
     import torch
     W = O.LayerWeights(D, 64, E, 4, experts=[], shared=False)
@@ -43,6 +46,21 @@ def test_logits_fp16_activations_and_row_stride():
     from mference_b200 import DT_F16
     moe = _moe(d=D, num_experts=E, max_tokens=T, x_dtype=DT_F16)
     wide = torch.zeros((T, D + 64), dtype=torch.float16, device="cuda")
+    wide[:, :D] = to_dev16(x, O.DT_F16)
+    out = torch.empty((T, E), dtype=torch.float32, device="cuda")
+    moe.encode_router_logits(wide[:, :D], to_dev16(W.router, O.DT_BF16), out)
+    ref = O.router_logits(x, O.DT_F16, W.router)
+    assert (out.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all()
+
+
+def test_logits_many_rows_fp16_activations_and_row_stride():
+    import torch
+    T, E, D = 97, 48, 512
+    W = O.LayerWeights(D, 64, E, 4, experts=[], shared=False)
+    x = make_x("x16.many", T, D, dtype=O.DT_F16)
+    from mference_b200 import DT_F16
+    moe = _moe(d=D, num_experts=E, max_tokens=T, x_dtype=DT_F16)
+    wide = torch.zeros((T, D + 72), dtype=torch.float16, device="cuda")
     wide[:, :D] = to_dev16(x, O.DT_F16)
     out = torch.empty((T, E), dtype=torch.float32, device="cuda")
     moe.encode_router_logits(wide[:, :D], to_dev16(W.router, O.DT_BF16), out)
