@@ -234,8 +234,17 @@ struct Item {
     uint32_t pair_start, count, row0, n, n_mma, ok, shared, bits;
 };
 
+// What a work item needs to know of its group, resolved once per CTA into shared memory: every role decodes every
+// item, and two dependent global loads (group record, slot table) per decode stalled each of them for a couple of
+// thousand cycles per item - as long as the arithmetic of a short item.
+struct TcGroup {
+    uint32_t pair_start, pair_count;
+    int32_t slot;        // pool slot of a routed expert (-1: not resident); for the shared expert 0 / -1
+    uint32_t shared;
+};
+
 // Work item `it` -> (group, token tile, weight-row tile); the same arithmetic in every role.
-__device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* tp_s, uint32_t n_groups, uint32_t it,
+__device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* tp_s, const TcGroup* grp_s, uint32_t n_groups, uint32_t it,
                                             uint32_t n_row_tiles, uint32_t tile_n) {
     Item I;
     const uint32_t tt = it / n_row_tiles;
@@ -244,22 +253,19 @@ __device__ __forceinline__ Item decode_item(const TcParams& P, const uint32_t* t
         const uint32_t mid = (lo + hi) / 2;
         if (tp_s[mid] <= tt) lo = mid; else hi = mid;
     }
-    const mfb_group g = P.groups[lo];
+    const TcGroup g = grp_s[lo];
     const uint32_t n0 = (tt - tp_s[lo]) * tile_n;
     I.pair_start = g.pair_start + n0;
     I.count = g.pair_count;
     I.n = min(tile_n, g.pair_count - n0);
     I.n_mma = max(16u, (I.n + 15u) & ~15u);
     I.row0 = (it % n_row_tiles) * TC_M;
-    I.shared = g.expert >= P.num_experts;
-    I.ok = 1;
+    I.shared = g.shared;
+    I.ok = g.slot >= 0;
     if (I.shared) {
-        I.blob = P.shared_blob; I.off = P.shared_off; I.ok = P.shared_blob != nullptr; I.bits = P.shared_bits;
+        I.blob = P.shared_blob; I.off = P.shared_off; I.bits = P.shared_bits;
     } else {
-        int64_t slot = g.expert;
-        if (P.slot_of) slot = P.slot_of[g.expert];
-        I.ok = slot >= 0;
-        I.blob = P.pool + (uint64_t)(slot < 0 ? 0 : slot) * P.slot_stride;
+        I.blob = P.pool + (uint64_t)(g.slot < 0 ? 0 : g.slot) * P.slot_stride;
         I.off = P.routed_off; I.bits = P.bits;
     }
     return I;
@@ -269,6 +275,7 @@ struct TcShared {
     uint64_t full_a[TC_STAGES], full_b[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base, abort;
     uint32_t tp[MFB_MAX_EXPERTS + 2];
+    TcGroup grp[MFB_MAX_EXPERTS + 1];
     float* out_ptr[TC_TILE_N];     // phase 2 with a destination table: where the result row of each token column goes
     uint32_t out_row[TC_TILE_N];   // phase 2 without one: token * slots + rank of the current item's token columns
 };
@@ -291,6 +298,15 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
     const uint32_t n_chunks = K / TC_KC, n_row_tiles = rows / TC_M;
     const uint32_t n_groups = *P.n_groups;
     for (uint32_t i = threadIdx.x; i <= n_groups; i += blockDim.x) S.tp[i] = (PHASE == 1 ? P.tile_prefix1 : P.tile_prefix2)[i];
+    for (uint32_t i = threadIdx.x; i < n_groups; i += blockDim.x) {
+        const mfb_group g = P.groups[i];
+        TcGroup t;
+        t.pair_start = g.pair_start; t.pair_count = g.pair_count;
+        t.shared = g.expert >= P.num_experts ? 1u : 0u;
+        if (t.shared) t.slot = P.shared_blob != nullptr ? 0 : -1;
+        else t.slot = P.slot_of ? (int32_t)P.slot_of[g.expert] : (int32_t)g.expert;
+        S.grp[i] = t;
+    }
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&S.full_a[s], TC_DQ_WARPS); mbar_init(&S.full_b[s], 1); mbar_init(&S.empty[s], 1); }
         for (uint32_t b = 0; b < 2; ++b) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], TC_EPI_WARPS); }
@@ -312,7 +328,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         // ---------------------------------------------------------------- activation tiles by TMA
         uint32_t seq = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
             const uint32_t copies = (I.n_mma + TC_BOX_ROWS - 1) / TC_BOX_ROWS;
             for (uint32_t c = 0; c < n_chunks; ++c, ++seq) {
@@ -330,7 +346,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         // ---------------------------------------------------------------- MMA issue
         uint32_t seq = 0, item = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
             const uint32_t buf = 0, use = item & 1u;   // one accumulator buffer; `use` = parity of its uses
             if (!mbar_wait(&S.acc_empty[buf], use ^ 1u)) { fail(); break; }
@@ -382,7 +398,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         auto open_item = [&](uint32_t it) {   // first resident item at or after `it` in this CTA's sequence
             RowSrc R{};
             for (; it < total; it += gridDim.x) {
-                const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+                const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
                 if (!I.ok) continue;
                 const uint32_t w_off = PHASE == 1 ? (mat ? I.off.up_w : I.off.gate_w) : I.off.down_w;
                 const uint32_t s_off = PHASE == 1 ? (mat ? I.off.up_s : I.off.gate_s) : I.off.down_s;
@@ -436,7 +452,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         uint32_t seq = 0;
         bool ok = true;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag && ok; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
             const bool four = I.bits == 4;
             for (uint32_t cb = 0; cb < n_chunks && ok; cb += RING) {   // n_chunks is a multiple of 8
@@ -485,7 +501,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         constexpr uint32_t COL_WAYS = TC_EPI_WARPS / 4;
         uint32_t item = 0;
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
-            const Item I = decode_item(P, S.tp, n_groups, it, n_row_tiles, TILE_N);
+            const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
             const uint32_t out_row = I.row0 + 32 * q + lane;
             if (PHASE == 2) {
                 // where each token column of this item goes: fetched once into shared memory (a dependent global
