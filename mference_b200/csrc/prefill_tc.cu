@@ -45,10 +45,18 @@ constexpr uint32_t TC_DQ_WARPS = 8;   // eight dequantising warps measured faste
 // phase 2, whose accumulator tiles are twice as wide
 __host__ __device__ constexpr uint32_t tc_epi_warps(int phase) { return phase == 1 ? 4 : 8; }
 __host__ __device__ constexpr uint32_t tc_threads(int phase) { return (2 + TC_DQ_WARPS + tc_epi_warps(phase)) * 32; }
-constexpr uint32_t TC_TMEM_COLS = 512;                 // two accumulator buffers of 256 columns
+constexpr uint32_t TC_TMEM_COLS = 512;
 constexpr uint32_t TC_STAGES = 4;
-// token rows per MMA tile: phase 1 keeps gate and up of a tile in one 256-column buffer, phase 2 has one matrix
-__host__ __device__ constexpr uint32_t tc_tile_n(int phase) { return phase == 1 ? TC_TILE_N / 2 : TC_TILE_N; }
+// token rows per MMA tile.  Phase 1 keeps gate and up of a tile (128 columns each) in ONE accumulator buffer, the
+// other 256 tensor-memory columns hold the weight ring.  Phase 2 has one matrix and a weight ring of 128 columns: tiles
+// of 192 rows leave room for TWO accumulator buffers, so the epilogue of an item (a third of the launch when it ran
+// alone) overlaps the MMAs of the next one.
+#ifndef MFB_TC_N2
+#define MFB_TC_N2 192
+#endif
+__host__ __device__ constexpr uint32_t tc_tile_n(int phase) { return phase == 1 ? TC_TILE_N / 2 : MFB_TC_N2; }
+__host__ __device__ constexpr uint32_t tc_acc_bufs(int phase) { return phase == 1 ? 1 : (2 * tc_tile_n(2) + TC_STAGES * 32 <= TC_TMEM_COLS ? 2 : 1); }
+static_assert(tc_tile_n(2) <= TC_TILE_N && tc_tile_n(2) % 64 == 0, "phase-2 tile");
 constexpr long long TC_WAIT_CYCLES = 400000000ll;      // ~0.2 s
 
 struct TcParams {
@@ -288,7 +296,9 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
     constexpr uint32_t STAGE_BYTES = TILE_N * 128;        // shared memory holds only the activation tiles
     // tensor memory: accumulators in columns [0, 256) (phase 1: gate then up, N <= 128 each), the dequantised weight
     // chunks of the ring behind them - a 64-element chunk of a matrix is 32 columns (two fp16 per column)
-    constexpr uint32_t A_COL0 = 256, A_STAGE_COLS = NMAT * 32;
+    constexpr uint32_t ACC_BUFS = tc_acc_bufs(PHASE), ACC_COLS = NMAT * TILE_N;   // columns of one accumulator buffer
+    constexpr uint32_t A_COL0 = ACC_BUFS * ACC_COLS, A_STAGE_COLS = NMAT * 32;
+    static_assert(A_COL0 + TC_STAGES * A_STAGE_COLS <= TC_TMEM_COLS, "tensor memory budget");
     constexpr uint32_t STAGES = TC_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcShared S;
@@ -348,7 +358,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
         for (uint32_t it = blockIdx.x; it < total && !*abort_flag; it += gridDim.x) {
             const Item I = decode_item(P, S.tp, S.grp, n_groups, it, n_row_tiles, TILE_N);
             if (!I.ok) continue;
-            const uint32_t buf = 0, use = item & 1u;   // one accumulator buffer; `use` = parity of its uses
+            const uint32_t buf = item % ACC_BUFS, use = (item / ACC_BUFS) & 1u;   // accumulator buffer and the parity of its uses
             if (!mbar_wait(&S.acc_empty[buf], use ^ 1u)) { fail(); break; }
             tc_fence_after();
             const uint32_t idesc = instr_desc(I.n_mma);
@@ -365,7 +375,7 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                         const uint32_t a_tmem = tmem + A_COL0 + s * A_STAGE_COLS + m * 32;
 #pragma unroll
                         for (uint32_t kk = 0; kk < TC_KC / 16; ++kk)   // 16 k per MMA: 8 TMEM columns of A, 32 bytes of B's swizzled row
-                            umma_f16_ta(tmem + m * TILE_N, a_tmem + kk * 8, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
+                            umma_f16_ta(tmem + buf * ACC_COLS + m * TILE_N, a_tmem + kk * 8, b_desc + kk * 2, idesc, (c | kk) ? 1u : 0u);
                     }
                     umma_commit(&S.empty[s]);   // frees the stage once these MMAs have read it
                 }
@@ -523,10 +533,10 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                     }
                 continue;
             }
-            const uint32_t buf = 0, use = item & 1u;
+            const uint32_t buf = item % ACC_BUFS, use = (item / ACC_BUFS) & 1u;
             if (!mbar_wait(&S.acc_full[buf], use)) { fail(); break; }
             tc_fence_after();
-            const uint32_t taddr = tmem + ((32 * q) << 16);
+            const uint32_t taddr = tmem + ((32 * q) << 16) + buf * ACC_COLS;
             for (uint32_t col0 = col_par * 32; col0 < I.n; col0 += 32 * COL_WAYS) {
                 float v[32];
                 tmem_ld32(taddr + col0, v);
