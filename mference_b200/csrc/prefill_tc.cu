@@ -548,19 +548,31 @@ __global__ void __launch_bounds__(tc_threads(PHASE), 1) tc_ffn_kernel(const TcPa
                     const bool silu = P.activation == MFB_ACT_SILU;
                     __half* out = P.acts16 + (size_t)(I.pair_start + col0) * P.f + fpos;
                     const uint32_t live = min(32u, I.n - col0);
+                    // all 32 columns are computed as independent chains (no early exit inside: one element's clamp, exp,
+                    // reciprocal and conversion depend on each other, and run one after the other they took ~130
+                    // cycles per element - the epilogue held the tensor pipe idle for a quarter of the launch); the
+                    // stores are predicated afterwards
+                    if (silu) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i) {
-                        if (i >= live) break;
-                        float gate = v[i], up = u[i];
-                        if (clamp) {
-                            gate = fminf(gate, P.limit);
-                            up = fminf(fmaxf(up, -P.limit), P.limit);
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            const float gate = clamp ? fminf(v[i], P.limit) : v[i];
+                            const float up = clamp ? fminf(fmaxf(u[i], -P.limit), P.limit) : u[i];
+                            // SiLU with the fast divide (2 ulp): the result is rounded to fp16 right after
+                            const float a = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                            v[i] = fminf(fmaxf(a, -65504.0f), 65504.0f);
                         }
-                        // SiLU with the fast divide (2 ulp): the result is rounded to fp16 right after
-                        float a = (silu ? __fdividef(gate, 1.0f + __expf(-gate)) : hidden_act(gate, (int)P.activation)) * up;
-                        a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                        out[(size_t)i * P.f] = __float2half_rn(a);
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            const float gate = clamp ? fminf(v[i], P.limit) : v[i];
+                            const float up = clamp ? fminf(fmaxf(u[i], -P.limit), P.limit) : u[i];
+                            const float a = hidden_act(gate, (int)P.activation) * up;
+                            v[i] = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                        }
                     }
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i)
+                        if (i < live) out[(size_t)i * P.f] = __float2half_rn(v[i]);
                 } else {
                     const uint32_t live = min(32u, I.n - col0);
                     if (!P.row_dest) {
