@@ -42,9 +42,9 @@ sys.path.insert(0, ROOT)
 D, F, E, K, LAYERS = 2048, 512, 256, 8, 40
 ROOT_SEED = 0xB2000001
 N_INPUTS = 4          # distinct input sets cycled through the steps
-# DRAM bytes (read + write) of one stack_mega_kernel launch from an ncu capture, keyed by (batch, rows, layers); the
-# capture of a 2-layer case is scaled by the layer count since every layer reads its own weights once
-TRAFFIC_PER_LAYER: dict = {}
+# DRAM bytes (read + write) per layer of one stack_mega_kernel launch, from ncu captures of 2-layer cases of this build
+# (profiles/), keyed by (batch, rows); scaled by the layer count since every layer reads its own weights once
+TRAFFIC_PER_LAYER: dict = {(64, "fresh"): 400.2e6, (8, "fresh"): 107.0e6, (1, "chained"): 17.37e6}
 
 
 def measured_peaks():
