@@ -273,7 +273,7 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     auto ok = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
     ok(dev_alloc(a.logits, T * E));
     a.router_ws_floats = router_workspace_floats(c.max_tokens, c.num_experts, c.d);
-    if (a.router_ws_floats) ok(dev_alloc(a.router_ws, a.router_ws_floats));
+    if (a.router_ws_floats) { ok(dev_alloc(a.router_ws, a.router_ws_floats)); ok(router_init()); }
     ok(dev_alloc(a.idx, T * K));
     ok(dev_alloc(a.route_w, T * K));
     { uint16_t* p = nullptr; ok(dev_alloc(p, T * c.d)); a.xn = p; }

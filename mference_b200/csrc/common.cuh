@@ -126,6 +126,7 @@ __device__ __forceinline__ float hidden_act(float g, int act) {
 // copies the prefill-size kernel reads; without it batches above 64 rows take the slower self-contained kernel.
 constexpr uint32_t ROUTER_WS_MAX_ROWS = 8192;   // token rows converted at a time
 size_t router_workspace_floats(uint32_t max_tokens, uint32_t num_experts, uint32_t d);
+cudaError_t router_init();   // once per process, from mfb_moe_create
 cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uint32_t ldx, uint32_t n_tokens,
                                  const __nv_bfloat16* w, uint32_t num_experts, uint32_t d, const float* logit_bias,
                                  float* logits, float* workspace = nullptr, size_t workspace_floats = 0);

@@ -173,7 +173,8 @@ extern "C" int32_t mfb_ep_combine(void* stream, const float* recv, const uint32_
 
 struct mfb_ep {
     uint32_t rank = 0, world = 1, d = 0, cap = 0;
-    uint32_t epoch = 0;
+    uint32_t* epoch_dev = nullptr;   // the call's epoch lives on the device (bumped by a kernel at the start of a dispatch), so
+                                     // that a layer captured into a CUDA graph advances it at every replay
     // own buffers
     uint16_t* recv_x = nullptr;
     int32_t* recv_e = nullptr;
@@ -212,7 +213,7 @@ __global__ void ep_dispatch_kernel(const uint16_t* __restrict__ x, uint32_t ldx,
                                    const int32_t* __restrict__ starts, uint32_t n_pairs, uint32_t top_k, uint32_t world,
                                    uint32_t rank, uint32_t cap, uint16_t* const* __restrict__ peer_recv_x,
                                    int32_t* const* __restrict__ peer_recv_e, uint32_t* const* __restrict__ peer_ctrl,
-                                   uint32_t* __restrict__ done, uint32_t epoch) {
+                                   uint32_t* __restrict__ done, const uint32_t* __restrict__ epoch_p) {
     __shared__ uint32_t s_last;
     for (uint32_t pos = blockIdx.x; pos < n_pairs; pos += gridDim.x) {
         uint32_t g = 0;
@@ -235,17 +236,18 @@ __global__ void ep_dispatch_kernel(const uint16_t* __restrict__ x, uint32_t ldx,
             c[0] = (uint32_t)counts[threadIdx.x];
             c[1] = (uint32_t)starts[threadIdx.x];
             __threadfence_system();
-            st_release_sys(c + 2, epoch);
+            st_release_sys(c + 2, *epoch_p);
         }
         if (threadIdx.x == 0) *done = 0;
     }
 }
 
 // One warp: lane s waits until source rank s has raised flag `which` (2 = rows arrived, 3 = results returned) to `epoch`.
-__global__ void ep_wait_kernel(const uint32_t* __restrict__ ctrl, uint32_t world, uint32_t which, uint32_t epoch,
+__global__ void ep_wait_kernel(const uint32_t* __restrict__ ctrl, uint32_t world, uint32_t which, const uint32_t* __restrict__ epoch_p,
                                uint32_t* __restrict__ status) {
     const uint32_t s = threadIdx.x;
     if (s >= world) return;
+    const uint32_t epoch = *epoch_p;
     const long long t0 = clock64();
     while ((int32_t)(ld_acquire_sys(ctrl + s * 4 + which) - epoch) < 0) {
         if (clock64() - t0 > EP_WAIT_CYCLES) { atomicOr(status, STATUS_MBAR_TIMEOUT); return; }
@@ -268,10 +270,13 @@ __global__ void ep_rows_kernel(const uint32_t* __restrict__ ctrl, const int32_t*
 }
 
 // Expert side, after the grouped FFN: tells every home rank that its result rows are in place.
-__global__ void ep_signal_kernel(uint32_t* const* __restrict__ peer_ctrl, uint32_t world, uint32_t rank, uint32_t epoch) {
+__global__ void ep_signal_kernel(uint32_t* const* __restrict__ peer_ctrl, uint32_t world, uint32_t rank, const uint32_t* __restrict__ epoch_p) {
     __threadfence_system();
-    if (threadIdx.x < world) st_release_sys(peer_ctrl[threadIdx.x] + rank * 4 + 3, epoch);
+    if (threadIdx.x < world) st_release_sys(peer_ctrl[threadIdx.x] + rank * 4 + 3, *epoch_p);
 }
+
+// First kernel of a dispatch: the next epoch (every rank makes the same number of calls, so the epochs agree).
+__global__ void ep_epoch_kernel(uint32_t* epoch_p) { *epoch_p += 1u; }
 
 template <typename T>
 cudaError_t ep_alloc(T*& p, size_t n) { return cudaMalloc((void**)&p, (n ? n : 1) * sizeof(T)); }
@@ -285,7 +290,7 @@ extern "C" int32_t mfb_ep_destroy(mfb_ep* ep) {
         if (p) cudaIpcCloseMemHandle(p);
     cudaFree(ep->recv_x); cudaFree(ep->recv_e); cudaFree(ep->ctrl); cudaFree(ep->ret);
     cudaFree(ep->peer_recv_x); cudaFree(ep->peer_recv_e); cudaFree(ep->peer_ctrl); cudaFree(ep->peer_ret);
-    cudaFree(ep->perm); cudaFree(ep->inv_scratch); cudaFree(ep->done); cudaFree(ep->status);
+    cudaFree(ep->perm); cudaFree(ep->inv_scratch); cudaFree(ep->done); cudaFree(ep->status); cudaFree(ep->epoch_dev);
     cudaFree(ep->counts); cudaFree(ep->starts); cudaFree(ep->local_expert); cudaFree(ep->row_expert); cudaFree(ep->row_dest);
     delete ep;
     return MFB_OK;
@@ -307,12 +312,13 @@ extern "C" int32_t mfb_ep_create(uint32_t rank, uint32_t world, uint32_t d, uint
     ok(ep_alloc(ep->ctrl, (size_t)world * 4));
     ok(ep_alloc(ep->ret, (size_t)max_pairs * d));
     ok(ep_alloc(ep->peer_recv_x, world)); ok(ep_alloc(ep->peer_recv_e, world)); ok(ep_alloc(ep->peer_ctrl, world)); ok(ep_alloc(ep->peer_ret, world));
-    ok(ep_alloc(ep->perm, max_pairs)); ok(ep_alloc(ep->inv_scratch, max_pairs)); ok(ep_alloc(ep->done, 1)); ok(ep_alloc(ep->status, 1));
+    ok(ep_alloc(ep->perm, max_pairs)); ok(ep_alloc(ep->inv_scratch, max_pairs)); ok(ep_alloc(ep->done, 1)); ok(ep_alloc(ep->status, 1)); ok(ep_alloc(ep->epoch_dev, 1));
     ok(ep_alloc(ep->counts, world)); ok(ep_alloc(ep->starts, world)); ok(ep_alloc(ep->local_expert, max_pairs));
     ok(ep_alloc(ep->row_expert, rows)); ok(ep_alloc(ep->row_dest, rows));
     if (e == cudaSuccess) e = cudaMemset(ep->ctrl, 0, (size_t)world * 4 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ep->done, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ep->status, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ep->epoch_dev, 0, sizeof(uint32_t));
     if (e != cudaSuccess) {
         set_error("ep_create: %s", cudaGetErrorString(e));
         mfb_ep_destroy(ep);
@@ -360,14 +366,14 @@ extern "C" int32_t mfb_ep_dispatch(mfb_ep* ep, void* stream, const void* x, uint
     const uint32_t n_pairs = n_tokens * top_k;
     MFB_REQUIRE(n_pairs <= ep->cap, MFB_ERR_CAPACITY, "ep_dispatch: %u pairs exceed the capacity of %u", n_pairs, ep->cap);
     cudaStream_t s = (cudaStream_t)stream;
-    ++ep->epoch;
+    ep_epoch_kernel<<<1, 1, 0, s>>>(ep->epoch_dev);
     ep_plan_kernel<<<1, EP_PLAN_WARPS * 32, 0, s>>>(idx, n_pairs, num_experts / ep->world, ep->world, ep->perm, inv, ep->counts, ep->starts,
                                                     ep->local_expert);
     const uint32_t grid = n_pairs ? n_pairs : 1;
     ep_dispatch_kernel<<<grid, 128, 0, s>>>((const uint16_t*)x, ldx, ep->d, ep->perm, ep->local_expert, ep->counts, ep->starts, n_pairs,
                                             top_k, ep->world, ep->rank, ep->cap, ep->peer_recv_x, ep->peer_recv_e, ep->peer_ctrl, ep->done,
-                                            ep->epoch);
-    count_launches(2);
+                                            ep->epoch_dev);
+    count_launches(3);
     MFB_CUDA(cudaGetLastError());
     return MFB_OK;
 }
@@ -377,7 +383,7 @@ extern "C" int32_t mfb_ep_receive(mfb_ep* ep, void* stream, const void** rows, c
     MFB_REQUIRE(ep && rows && row_expert && row_dest && n_rows, MFB_ERR_INVALID_ARGUMENT, "ep_receive: NULL argument");
     cudaStream_t s = (cudaStream_t)stream;
     const uint32_t total = ep->world * ep->cap;
-    ep_wait_kernel<<<1, 32, 0, s>>>(ep->ctrl, ep->world, 2, ep->epoch, ep->status);
+    ep_wait_kernel<<<1, 32, 0, s>>>(ep->ctrl, ep->world, 2, ep->epoch_dev, ep->status);
     ep_rows_kernel<<<(total + 255) / 256, 256, 0, s>>>(ep->ctrl, ep->recv_e, ep->peer_ret, ep->world, ep->cap, ep->d, ep->row_expert, ep->row_dest);
     count_launches(2);
     MFB_CUDA(cudaGetLastError());
@@ -387,7 +393,7 @@ extern "C" int32_t mfb_ep_receive(mfb_ep* ep, void* stream, const void** rows, c
 
 extern "C" int32_t mfb_ep_return(mfb_ep* ep, void* stream) {
     MFB_REQUIRE(ep != nullptr, MFB_ERR_INVALID_ARGUMENT, "ep_return: NULL argument");
-    ep_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->peer_ctrl, ep->world, ep->rank, ep->epoch);
+    ep_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->peer_ctrl, ep->world, ep->rank, ep->epoch_dev);
     count_launches(1);
     MFB_CUDA(cudaGetLastError());
     return MFB_OK;
@@ -395,7 +401,7 @@ extern "C" int32_t mfb_ep_return(mfb_ep* ep, void* stream) {
 
 extern "C" int32_t mfb_ep_results(mfb_ep* ep, void* stream, const float** ret) {
     MFB_REQUIRE(ep && ret, MFB_ERR_INVALID_ARGUMENT, "ep_results: NULL argument");
-    ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->ctrl, ep->world, 3, ep->epoch, ep->status);
+    ep_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ep->ctrl, ep->world, 3, ep->epoch_dev, ep->status);
     count_launches(1);
     MFB_CUDA(cudaGetLastError());
     *ret = ep->ret;

@@ -33,6 +33,42 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int in_dtype, const _
     }
 }
 
+// The same arithmetic in the same order for 16-bit rows whose length is a multiple of eight: the row crosses global
+// memory once each way in 16-byte pieces and is kept in shared memory between the two passes (the element-wise form
+// above moves 64 bytes per warp instruction and reads the row twice: 27 us for 4096 x 2048 against 9 us of traffic).
+__global__ void rmsnorm_rows16_kernel(const uint16_t* __restrict__ x, int in_dtype, const __nv_bfloat16* __restrict__ w,
+                                      uint32_t d, float eps, uint16_t* __restrict__ out, int out_dtype) {
+    extern __shared__ __align__(16) uint16_t row_s[];
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(x + row * d);
+    for (uint32_t p = threadIdx.x; p < d / 8; p += blockDim.x) reinterpret_cast<uint4*>(row_s)[p] = src[p];
+    __syncthreads();
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = widen16(row_s[i], in_dtype);
+        ss = fmaf(v, v, ss);
+    }
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    const float inv = rsqrtf(red[0] / (float)d + eps);
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {   // element i is read and rewritten by the same thread
+        const float v = widen16(row_s[i], in_dtype);
+        const float g = w ? __bfloat162float(w[i]) : 1.0f;
+        row_s[i] = narrow16(v * inv * g, out_dtype);
+    }
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(out + row * d);
+    for (uint32_t p = threadIdx.x; p < d / 8; p += blockDim.x) dst[p] = reinterpret_cast<const uint4*>(row_s)[p];
+}
+
 // residual_add_fp16 (Sources/Mference/Metal/Primitives/utility.metal:83-92) in the activation dtype.
 __global__ void residual_add_kernel(const void* __restrict__ a, const void* __restrict__ b, uint64_t n,
                                     void* __restrict__ out, int dtype) {
@@ -77,7 +113,12 @@ __global__ void combine_kernel(const float* __restrict__ partial, const uint16_t
 cudaError_t launch_rmsnorm(cudaStream_t s, const void* x, int in_dtype, const __nv_bfloat16* w, uint32_t n_rows,
                            uint32_t d, float eps, void* out, int out_dtype) {
     if (n_rows == 0) return cudaSuccess;
-    rmsnorm_kernel<<<n_rows, 256, 0, s>>>(x, in_dtype, w, d, eps, out, out_dtype);
+    const bool rows16 = in_dtype != MFB_DT_F32 && out_dtype != MFB_DT_F32 && d % 8 == 0 && d * 2 <= 48 * 1024 &&
+                        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    if (rows16)
+        rmsnorm_rows16_kernel<<<n_rows, 256, d * 2, s>>>((const uint16_t*)x, in_dtype, w, d, eps, (uint16_t*)out, out_dtype);
+    else
+        rmsnorm_kernel<<<n_rows, 256, 0, s>>>(x, in_dtype, w, d, eps, out, out_dtype);
     count_launches(1);
     return cudaGetLastError();
 }

@@ -82,30 +82,50 @@ __global__ void group_finalize_kernel(const uint32_t* __restrict__ counts, uint3
                                       uint32_t* __restrict__ n_groups, uint32_t* __restrict__ tile_prefix,
                                       mfb_pair* __restrict__ sorted) {
     __shared__ uint32_t s_total;
-    if (threadIdx.x == 0) {
+    __shared__ uint32_t s_cnt[MFB_MAX_EXPERTS];
+    for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) s_cnt[e] = counts[e];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // one warp, 32 experts per round: exclusive prefixes of the pair counts, of the non-empty flags (group index)
+        // and of the tile counts by shuffles, carried from round to round
+        const uint32_t lane = threadIdx.x;
         uint32_t run = 0, ng = 0, tiles = 0;
-        for (uint32_t e = 0; e < num_experts; ++e) {
-            const uint32_t c = counts[e];
-            offsets[e] = c ? run : 0xFFFFFFFFu;
-            if (c) {
-                groups[ng].expert = e;
+        for (uint32_t base = 0; base < num_experts; base += 32) {
+            const uint32_t e = base + lane;
+            const uint32_t c = e < num_experts ? s_cnt[e] : 0u;
+            const uint32_t t = tile_prefix ? (c + tile_rows - 1) / tile_rows : 0u;
+            uint32_t ic = c, it = t;
+            for (uint32_t off = 1; off < 32; off <<= 1) {
+                const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, ic, off), b2 = __shfl_up_sync(0xFFFFFFFFu, it, off);
+                if (lane >= off) { ic += a; it += b2; }
+            }
+            const uint32_t live = __ballot_sync(0xFFFFFFFFu, c != 0u);
+            const uint32_t g = ng + __popc(live & ((1u << lane) - 1u));
+            if (e < num_experts) {
+                offsets[e] = c ? run + ic - c : 0xFFFFFFFFu;
+                if (c) {
+                    groups[g].expert = e;
+                    groups[g].pair_start = run + ic - c;
+                    groups[g].pair_count = c;
+                    if (tile_prefix) tile_prefix[g] = tiles + it - t;
+                }
+            }
+            run += __shfl_sync(0xFFFFFFFFu, ic, 31);
+            tiles += __shfl_sync(0xFFFFFFFFu, it, 31);
+            ng += __popc(live);
+        }
+        if (lane == 0) {
+            if (append_shared) {
+                groups[ng].expert = num_experts;
                 groups[ng].pair_start = run;
-                groups[ng].pair_count = c;
-                if (tile_prefix) { tile_prefix[ng] = tiles; tiles += (c + tile_rows - 1) / tile_rows; }
+                groups[ng].pair_count = n_tokens;
+                if (tile_prefix) { tile_prefix[ng] = tiles; tiles += (n_tokens + tile_rows - 1) / tile_rows; }
                 ++ng;
             }
-            run += c;
+            if (tile_prefix) tile_prefix[ng] = tiles;
+            *n_groups = ng;
+            s_total = run;
         }
-        if (append_shared) {
-            groups[ng].expert = num_experts;
-            groups[ng].pair_start = run;
-            groups[ng].pair_count = n_tokens;
-            if (tile_prefix) { tile_prefix[ng] = tiles; tiles += (n_tokens + tile_rows - 1) / tile_rows; }
-            ++ng;
-        }
-        if (tile_prefix) tile_prefix[ng] = tiles;
-        *n_groups = ng;
-        s_total = run;
     }
     __syncthreads();
     if (append_shared) {
@@ -123,15 +143,12 @@ __global__ void group_finalize_kernel(const uint32_t* __restrict__ counts, uint3
 __global__ void group_scatter_kernel(const uint32_t* __restrict__ idx, const uint16_t* __restrict__ route_w,
                                      uint32_t n_pairs, uint32_t top_k, uint32_t num_experts, uint32_t slot_mask,
                                      uint32_t n_chunks, const uint32_t* __restrict__ chunk_hist,
-                                     const uint32_t* __restrict__ counts, mfb_pair* __restrict__ sorted) {
+                                     const uint32_t* __restrict__ offsets, mfb_pair* __restrict__ sorted) {
     extern __shared__ uint32_t sh[];
     uint32_t* s_off = sh;  // [num_experts] expert offsets, shared by the block
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     uint32_t* run = sh + num_experts + warp * num_experts;
-    if (threadIdx.x == 0) {
-        uint32_t r = 0;
-        for (uint32_t e = 0; e < num_experts; ++e) { s_off[e] = r; r += counts[e]; }
-    }
+    for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) s_off[e] = offsets[e];   // unused where the expert has no pair
     __syncthreads();
     const uint32_t chunk = blockIdx.x * warps + warp;
     if (chunk >= n_chunks) return;
@@ -184,7 +201,7 @@ cudaError_t launch_group(cudaStream_t s, const uint32_t* idx, const uint16_t* ro
     count_launches(1);
     if (n_chunks > 0) {
         group_scatter_kernel<<<blocks, warps * 32, (warps + 1) * num_experts * sizeof(uint32_t), s>>>(
-            idx, route_w, n_pairs, top_k, num_experts, slot_mask, n_chunks, a.chunk_hist, out_counts, out_sorted);
+            idx, route_w, n_pairs, top_k, num_experts, slot_mask, n_chunks, a.chunk_hist, out_offsets, out_sorted);
         count_launches(1);
     }
     return cudaGetLastError();

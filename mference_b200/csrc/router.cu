@@ -439,6 +439,16 @@ __global__ void slot_lookup_kernel(const uint32_t* __restrict__ idx, uint32_t n_
 
 }  // namespace
 
+// Set by router_init(): the prefill-size kernel's shared-memory attribute is in place (done when a handle is created, so
+// that no later call changes function attributes).
+static bool g_router_ready = false;
+
+cudaError_t router_init() {
+    const cudaError_t e = cudaFuncSetAttribute(router_logits_lane_major_kernel<RQ_NW, RQ_EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RQ_SMEM_BYTES);
+    if (e == cudaSuccess) g_router_ready = true;
+    return e;
+}
+
 size_t router_workspace_floats(uint32_t max_tokens, uint32_t num_experts, uint32_t d) {
     if (max_tokens <= 64 || d % RQ_KC != 0) return 0;
     const uint64_t rows = max_tokens < ROUTER_WS_MAX_ROWS ? max_tokens : ROUTER_WS_MAX_ROWS;
@@ -457,14 +467,8 @@ cudaError_t launch_router_logits(cudaStream_t s, const void* x, int x_dtype, uin
     } else if (n_tokens <= 64) {
         dim3 grid((num_experts + RT_WARPS - 1) / RT_WARPS, (n_tokens + 7) / 8);
         router_logits_kernel<8, 1><<<grid, RT_WARPS * 32, 0, s>>>(x, x_dtype, ldx, n_tokens, w, num_experts, d, logit_bias, logits);
-    } else if (workspace && d % RQ_KC == 0 && workspace_floats >= (size_t)(num_experts + 1) * d) {
+    } else if (g_router_ready && workspace && d % RQ_KC == 0 && workspace_floats >= (size_t)(num_experts + 1) * d) {
         // lane-major fp32 copies of the gate and of as many token rows as the workspace holds at a time
-        static bool attr_set = false;   // benign race: the attribute call is idempotent
-        if (!attr_set) {
-            const cudaError_t e = cudaFuncSetAttribute(router_logits_lane_major_kernel<RQ_NW, RQ_EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RQ_SMEM_BYTES);
-            if (e != cudaSuccess) return e;
-            attr_set = true;
-        }
         float* wq = workspace;
         float* xq = workspace + (size_t)num_experts * d;
         const uint32_t cap = (uint32_t)std::min<size_t>((workspace_floats - (size_t)num_experts * d) / d, n_tokens);

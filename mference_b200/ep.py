@@ -295,3 +295,19 @@ class PeerExpertParallelLayer:
                                        h_out.data_ptr(), h_in.shape[0], ops.K, ops.d, ops.x_dtype))
         mark("combined")
         return h_out
+
+    def capture(self, weights, local_weights, shared_weights, h_in, h_out):
+        """Records one `forward` over these (fixed) tensors into a CUDA graph.  A layer is some twenty-five small
+        launches with no host synchronisation between them; issued one by one from the host they leave the GPU idle for
+        a third of a short step, replayed as a graph they run back to back.  The exchange epoch lives in device memory
+        and is advanced by the first kernel of the dispatch, so every replay is a new epoch on every rank.  Call
+        `forward` at least once before (caches, lazily created buffers), and `replay()` on every rank the same number
+        of times."""
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            self.forward(weights, local_weights, shared_weights, h_in, h_out)
+        self.graph = graph
+        return graph
+
+    def replay(self):
+        self.graph.replay()

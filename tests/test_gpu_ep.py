@@ -49,6 +49,14 @@ def _worker(rank, world, port, tokens, q, kind="nccl"):
             layer.forward(full, local, shared, x, y2)
             torch.cuda.synchronize()
             assert torch.equal(y, y2)
+            # and as a CUDA graph, replayed twice (every rank replays the same number of times)
+            xg, yg = torch.empty_like(x), torch.empty_like(x)
+            layer.capture(full, local, shared, xg, yg)
+            for _ in range(2):
+                xg.copy_(x)
+                layer.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(y, yg)
             st, counts = layer.ex.status(with_counts=True)
             assert st == 0, st
         ref_moe = MoE(D, F, E, K, max_tokens=T, tensor_core_prefill=True)
@@ -127,6 +135,16 @@ def test_peer_exchange_with_one_rank_equals_the_prefill_layer():
             layer.forward(full, local, shared, x, y)
             torch.cuda.synchronize()
             assert torch.equal(y, y_ref)
+        # the same layer recorded into a CUDA graph and replayed on other rows (the epoch advances on the device)
+        xg, yg = torch.empty_like(x), torch.empty_like(x)
+        layer.capture(full, local, shared, xg, yg)
+        for seed in (1, 2):
+            x2 = synth_normal(ROOT + seed, "x.ep1", T * d, dtype=L.DT_BF16).view(T, d)
+            xg.copy_(x2)
+            layer.replay()
+            ref_moe.encode_layer_prefill(full, x2, y_ref)
+            torch.cuda.synchronize()
+            assert torch.equal(yg, y_ref)
         st, counts = layer.ex.status(with_counts=True)
         assert st == 0 and counts == [T * k]
         assert ref_moe.device_status() == 0 and ops.expert.device_status() == 0
