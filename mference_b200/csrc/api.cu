@@ -104,6 +104,7 @@ FastParams fast_params(mfb_moe* m, const mfb_layer_weights* w, uint32_t n_tokens
     P.xp = a.xp; P.xp_shared = a.xp2 ? a.xp2 : a.xp; P.x_in_smem = 0; P.dbg = nullptr; P.actp = a.actp; P.partial = a.partial; P.route_w = route_w;
     P.residual = residual; P.y = y; P.x_dtype = (int)c.x_dtype; P.n_tokens = n_tokens; P.status = a.status;
     P.maps = maps;
+    P.ready = nullptr;   // separate launches are ordered by the stream
     return P;
 }
 
@@ -292,7 +293,7 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device);
         m->coop = coop != 0;
         ok(fast_init());
-        ok(dev_alloc(m->mega_bar, 2));
+        ok(dev_alloc(m->mega_bar, MEGA_BAR_WORDS));
         const uint64_t ft = T < FAST_MAX_TOKENS ? T : FAST_MAX_TOKENS;
         ok(dev_alloc(a.xp, ft * c.d));
         if (c.shared_bits && c.shared_bits != c.bits) ok(dev_alloc(a.xp2, ft * c.d));
@@ -602,7 +603,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
         M.limit = c.swiglu_limit; M.route_scale = c.route_scale; M.eps = c.rms_eps;
         M.hidden = rows; M.layer_stride = layer_stride; M.n_tokens = n_tokens;
         M.xn = a.xn; M.xp = a.xp; M.xp2 = a.xp2; M.logits = a.logits; M.idx = a.idx; M.route_w = a.route_w; M.actp = a.actp; M.partial = a.partial;
-        M.bar_counter = moe->mega_bar; M.abort = moe->mega_bar + 1; M.status = a.status; M.trace = moe->trace;
+        M.bar_counter = moe->mega_bar; M.abort = moe->mega_bar + 1; M.ready = moe->mega_bar + 2; M.status = a.status; M.trace = moe->trace;
         M.wide = all_maps ? 1 : 0;
         MFB_CUDA(launch_stack_mega(s, M, c, moe->sm_count));
         return MFB_OK;

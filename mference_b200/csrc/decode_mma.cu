@@ -741,7 +741,12 @@ struct Ctx {
     uint64_t* sfull;      // [2]
     uint64_t* sempty;     // [2]
     const uint32_t* pref; // exclusive prefix of units per group
+    const uint32_t* pref_dep;   // phase 2 with P.ready: the phase-1 prefix (units of a group that must have finished)
 };
+
+__device__ __forceinline__ void red_release_add(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint32_t c0, uint32_t c1, uint32_t c2, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -807,9 +812,25 @@ __device__ __forceinline__ bool run(const FastParams& P, const Geom& geo, const 
         fence_proxy_async();   // activation rows written through the generic proxy by other CTAs before the grid barrier
         if (lane < 18) tensormap_acquire(&P.maps->m[lane / 9][lane % 9]);
         __syncwarp();
+        uint32_t checked = 0xFFFFFFFFu;
         for (uint32_t u = first; u < last && ok; ++u) {
             if (G.ok) {
                 ++ok_units;
+                if (PHASE == 2 && P.ready && g != checked) {
+                    // no grid barrier in front of this phase: the hidden activations of group g are complete once every
+                    // computing warp of every phase-1 unit of the group has counted itself in
+                    const uint32_t need = (C.pref_dep[g + 1] - C.pref_dep[g]) * CW;
+                    uint32_t good = 1;
+                    if (lane == 0) {
+                        const long long t0 = clock64();
+                        while (ld_acquire_u32(P.ready + g) < need)
+                            if (clock64() - t0 > MBAR_WAIT_CYCLES) { good = 0; break; }
+                    }
+                    good = __shfl_sync(0xFFFFFFFFu, good, 0);
+                    if (!good) { ok = false; break; }
+                    fence_proxy_async();
+                    checked = g;
+                }
                 const uint32_t cols = min(8u, G.pair_count - tt * 8), pair0 = G.pair_start + tt * 8;
                 const uint32_t row0 = PHASE == 1 ? tile * TILE_ROWS : tile * NT * TILE_ROWS;
                 // source of this lane's activation row (lanes 2 .. 2 + cols)
@@ -956,6 +977,11 @@ __device__ __forceinline__ bool run(const FastParams& P, const Geom& geo, const 
                             P.actp[(size_t)(pair0 + n) * P.f + act_col] = __float2half_rn(a * act_scale);
                         }
                     }
+                    if (P.ready) {   // this warp's rows of the unit are written: count it in (release, cumulative over the warp)
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) red_release_add(P.ready + g, 1u);
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
@@ -1067,6 +1093,11 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) ffn_phase_kernel(const FastPa
 
 // Unit weights of the row-stationary form: a unit's cost is its k loop, the token columns in use add next to nothing.
 __device__ __forceinline__ UnitBases wide_unit_bases() { return UnitBases{64u, 64u}; }
+// relative time of a phase-1 and of a phase-2 unit of the row-stationary form (measured: ~10 us and ~3.7 us)
+#ifndef MFB_WIDE_T1
+#define MFB_WIDE_T1 10
+#endif
+constexpr uint64_t WIDE_T1 = MFB_WIDE_T1, WIDE_T2 = 4;
 
 __device__ __forceinline__ uint8_t* align_1k(uint8_t* p) {
     return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~(uintptr_t)1023);
@@ -1089,7 +1120,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) ffn_wide_kernel(const FastPar
         warp_unit_ranges<true>(S, P.groups, n_groups, geo.tiles, geo.tiles, ub, wpref2, lane);
     }
     __syncthreads();
-    const wide::Ctx C{smem, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1};
+    const wide::Ctx C{smem, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1, nullptr};
     uint32_t seq = 0, sseq = 0;
     const uint32_t first = S.range[0], last = S.range[1];
     const bool ok = P.scale_dtype == MFB_DT_BF16 ? wide::run<PHASE, MFB_DT_BF16>(P, geo, C, n_groups, first, last, seq, sseq, warp, lane)
@@ -1670,6 +1701,21 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             uint32_t* wpref2 = reinterpret_cast<uint32_t*>(region_a);   // the stage ring is not in use yet
             warp_unit_prefix2<LARGE_BATCH>(groups_s, n_groups, tiles1, tiles2, S.pref1, S.pref2, S.wpref1, wpref2, ub, lane);
             warp_unit_ranges<LARGE_BATCH>(S, groups_s, n_groups, tiles1, tiles2, ub, wpref2, lane);
+            if (WIDE && M.ready && lane == 0) {
+                // Without a barrier between the phases a CTA's time is the sum of its two shares, so phase 2 is cut to
+                // even out what the whole-unit cuts of phase 1 left uneven (six or seven units of ~10 us each): CTA k
+                // starts phase 2 at the unit where k / n of the total time, less the phase-1 time in front of its
+                // phase-1 cut, is spent.  Depends only on k and cut k, so neighbours agree on their common boundary.
+                const uint64_t u1 = S.pref1[n_groups], u2 = S.pref2[n_groups], n = gridDim.x;
+                const uint64_t total = WIDE_T1 * u1 + WIDE_T2 * u2;
+                auto cut2 = [&](uint64_t k, uint64_t cut1) -> uint32_t {
+                    if (k >= n) return (uint32_t)u2;
+                    const long long v = ((long long)(k * total / n) - (long long)(WIDE_T1 * cut1)) / (long long)WIDE_T2;
+                    return (uint32_t)(v < 0 ? 0 : (v > (long long)u2 ? (long long)u2 : v));
+                };
+                S.range[2] = cut2(blockIdx.x, S.range[0]);
+                S.range[3] = cut2(blockIdx.x + 1, S.range[1]);
+            }
         }
         __syncthreads();
 
@@ -1685,11 +1731,16 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
         P.dbg = M.trace ? reinterpret_cast<unsigned long long*>(M.trace + (size_t)M.n_layers * 8) : nullptr;
         P.residual = h; P.y = h; P.x_dtype = M.x_dtype; P.n_tokens = M.n_tokens; P.status = M.status;
         P.maps = Ly.maps;
+        // row-stationary form: no grid barrier between the FFN phases - a phase-2 unit waits for the phase-1 units of its
+        // own group only (per-group counters, one array per layer parity)
+        P.ready = (WIDE && M.ready) ? M.ready + (l & 1u) * MEGA_READY_WORDS : nullptr;
+        if (WIDE && M.ready && blockIdx.x == 0)   // the other parity's counters were last read before the previous layer's final barrier
+            for (uint32_t i = threadIdx.x; i < MEGA_READY_WORDS; i += blockDim.x) M.ready[((l + 1) & 1u) * MEGA_READY_WORDS + i] = 0u;
         stamp(4);
 
         // ---- phase 1: this CTA's contiguous share of the (group, token tile, row tile) units
         if constexpr (WIDE) {
-            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1};
+            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref1, nullptr};
             const uint32_t first = S.range[0], last = S.range[1];
             const bool ok = M.scale_dtype == MFB_DT_BF16 ? wide::run<1, MFB_DT_BF16>(P, wgeo1, C, n_groups, first, last, seq1, seq2, warp, lane)
                                                          : wide::run<1, MFB_DT_F16>(P, wgeo1, C, n_groups, first, last, seq1, seq2, warp, lane);
@@ -1708,11 +1759,11 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
             }
         }
         stamp(5);
-        if (!(alive = grid_barrier(M, S, epoch))) break;
+        if (!(WIDE && M.ready) && !(alive = grid_barrier(M, S, epoch))) break;
         stamp(6);
         // ---- phase 2: down projections of every (group, token tile, 128-row block) into the fp32 partial rows
         if constexpr (WIDE) {
-            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref2};
+            const wide::Ctx C{region_a, S.wfull, S.wempty, S.sfull, S.sempty, S.pref2, S.pref1};
             const uint32_t first = S.range[2], last = S.range[3];
             const bool ok = M.scale_dtype == MFB_DT_BF16 ? wide::run<2, MFB_DT_BF16>(P, wgeo2, C, n_groups, first, last, seq1, seq2, warp, lane)
                                                          : wide::run<2, MFB_DT_F16>(P, wgeo2, C, n_groups, first, last, seq1, seq2, warp, lane);
@@ -1888,7 +1939,7 @@ cudaError_t launch_fast_ffn(cudaStream_t s, const FastParams& P, const mfb_moe_c
 }
 
 cudaError_t launch_stack_mega(cudaStream_t s, const MegaParams& M, const mfb_moe_config& c, int sm_count) {
-    cudaError_t e = cudaMemsetAsync(M.bar_counter, 0, 2 * sizeof(uint32_t), s);   // barrier counter and abort word are adjacent
+    cudaError_t e = cudaMemsetAsync(M.bar_counter, 0, MEGA_BAR_WORDS * sizeof(uint32_t), s);   // barrier counter, abort word, group counters
     if (e != cudaSuccess) return e;
     MegaParams copy = M;
     void* args[] = {&copy};

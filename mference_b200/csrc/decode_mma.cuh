@@ -39,6 +39,7 @@ struct FastParams {
     uint32_t* status;
     unsigned long long* dbg;  // optional cycle counters of CTA 0: [17 warps][8] (wait / compute per phase), or NULL
     const WideMaps* maps;     // tensor maps of the layer (row-stationary phases, batches above 16 rows), or NULL
+    uint32_t* ready;          // fused kernel, row-stationary form: per-group count of finished phase-1 units (x CW warps), or NULL
 };
 
 // Per-layer weights as the fused stack kernel reads them (device array, one entry per layer).
@@ -74,6 +75,8 @@ struct MegaParams {
     __half* actp;
     float* partial;
     uint32_t* bar_counter;    // [2]: arrivals, abort word (zeroed before every launch)
+    uint32_t* ready;          // [2][MEGA_READY_WORDS] finished phase-1 units per expert group, by layer parity (zeroed before
+                              // every launch and by the kernel one layer ahead), or NULL: a grid barrier between the FFN phases
     uint32_t* abort;
     uint32_t* status;
     int wide;                 // every layer carries tensor maps: batches above 16 rows run the row-stationary phases
@@ -81,6 +84,8 @@ struct MegaParams {
                               // [17][8] cycle counters (per warp of CTA 0: phase-1 wait, phase-1 compute, phase-2 wait, phase-2 compute)
 };
 
+constexpr uint32_t MEGA_READY_WORDS = MFB_MAX_EXPERTS + 1;
+constexpr uint32_t MEGA_BAR_WORDS = 2 + 2 * MEGA_READY_WORDS;   // what the handle allocates behind bar_counter
 constexpr size_t FAST_SMEM_LIMIT = 220 * 1024;   // dynamic shared memory the fast kernels may ask for (static use on top)
 constexpr uint32_t FAST_MAX_TOKENS = 64;   // phase 2 keeps (token, slot) x 16 partial rows in shared memory
 
