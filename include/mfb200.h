@@ -92,7 +92,8 @@ typedef struct mfb_moe_config {
     uint32_t num_experts;   /* <= MFB_MAX_EXPERTS */
     uint32_t top_k;         /* <= MFB_MAX_TOP_K */
     uint32_t bits;          /* routed expert code width: 4 or 2 */
-    uint32_t shared_bits;   /* shared expert code width: 4 or 2; 0 = the layer has no shared expert */
+    uint32_t shared_bits;   /* shared expert code width: 4, 2 or 8 (SharedExpertInt8, Sources/Mference/Kernels/MoE/
+                               SharedExpertInt8.swift: generic kernels only); 0 = the layer has no shared expert */
     uint32_t group_size;    /* 64 */
     uint32_t scale_dtype;   /* MFB_DT_F16 (MLX files) or MFB_DT_BF16 (reference .gturbo files) */
     uint32_t x_dtype;       /* activation dtype in and out: MFB_DT_BF16 or MFB_DT_F16 */

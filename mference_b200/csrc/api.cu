@@ -223,7 +223,7 @@ extern "C" uint64_t mfb_launch_count(void) { return g_launches.load(std::memory_
 
 extern "C" int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes) {
     MFB_REQUIRE(off && blob_bytes, MFB_ERR_INVALID_ARGUMENT, "layout: NULL output");
-    MFB_REQUIRE(bits == 4 || bits == 2, MFB_ERR_INVALID_ARGUMENT, "layout: bits must be 4 or 2");
+    MFB_REQUIRE(bits == 4 || bits == 2 || bits == 8, MFB_ERR_INVALID_ARGUMENT, "layout: bits must be 2, 4 or 8");
     MFB_REQUIRE(d && f && d % 64 == 0 && f % 64 == 0, MFB_ERR_INVALID_ARGUMENT, "layout: d and f must be multiples of 64");
     const uint64_t wbytes = (uint64_t)d * f * bits / 8, sbytes = (uint64_t)d * f / 64 * 2;
     MFB_REQUIRE(3 * (wbytes + 2 * sbytes) <= 0xFFFFFFFFull, MFB_ERR_UNSUPPORTED_SHAPE, "layout: blob exceeds 4 GiB");
@@ -241,7 +241,10 @@ extern "C" int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out) {
     MFB_REQUIRE(c.d && c.f && c.d % 64 == 0 && c.f % 64 == 0, MFB_ERR_INVALID_ARGUMENT, "d and f must be multiples of 64");
     MFB_REQUIRE(c.group_size == 64, MFB_ERR_UNSUPPORTED_SHAPE, "group size must be 64");
     MFB_REQUIRE(c.bits == 4 || c.bits == 2, MFB_ERR_INVALID_ARGUMENT, "bits must be 4 or 2");
-    MFB_REQUIRE(c.shared_bits == 0 || c.shared_bits == 4 || c.shared_bits == 2, MFB_ERR_INVALID_ARGUMENT, "shared_bits must be 0, 4 or 2");
+    // 8-bit codes for the shared expert only (SharedExpertInt8, Sources/Mference/Kernels/MoE/SharedExpertInt8.swift): such
+    // a handle runs the generic kernels
+    MFB_REQUIRE(c.shared_bits == 0 || c.shared_bits == 4 || c.shared_bits == 2 || c.shared_bits == 8, MFB_ERR_INVALID_ARGUMENT,
+                "shared_bits must be 0, 2, 4 or 8");
     MFB_REQUIRE(c.num_experts >= 1 && c.num_experts <= MFB_MAX_EXPERTS, MFB_ERR_UNSUPPORTED_SHAPE, "num_experts must be in 1..%d", MFB_MAX_EXPERTS);
     MFB_REQUIRE(c.top_k >= 1 && c.top_k <= MFB_MAX_TOP_K, MFB_ERR_UNSUPPORTED_SHAPE, "top_k must be in 1..%d", MFB_MAX_TOP_K);
     MFB_REQUIRE(c.scale_dtype == MFB_DT_F16 || c.scale_dtype == MFB_DT_BF16, MFB_ERR_INVALID_ARGUMENT, "scale dtype must be fp16 or bf16");

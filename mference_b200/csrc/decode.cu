@@ -145,6 +145,7 @@ __device__ __forceinline__ void row_dot(const uint8_t* const (&wrow)[NMAT], cons
             for (int t = 0; t < NT; ++t) {
                 float xsum = xs[t * xstride + padded(elem0 & ~31u) + 32];
                 if (CPP == 64) xsum += xs[t * xstride + padded((elem0 & ~31u) + 32) + 32];
+                if (CPP == 16 && (pc & 1u)) xsum = 0.0f;   // 8-bit codes: the 32-element sum goes with the block's first piece
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
                     acc[m][t] = fmaf(sc[m], dot[m][t], acc[m][t]);
@@ -282,6 +283,7 @@ __global__ void __launch_bounds__(FFN_THREADS) ffn_phase1_kernel(const FfnParams
     const GroupView G = view_group(P, blockIdx.y);
     if (!G.ok) return;
     if (G.bits == 4) phase1_body<4, NT>(P, G, xs);
+    else if (G.bits == 8) phase1_body<8, NT>(P, G, xs);
     else phase1_body<2, NT>(P, G, xs);
 }
 
@@ -291,6 +293,7 @@ __global__ void __launch_bounds__(FFN_THREADS) ffn_phase2_kernel(const FfnParams
     const GroupView G = view_group(P, blockIdx.y);
     if (!G.ok) return;
     if (G.bits == 4) phase2_body<4, NT>(P, G, xs);
+    else if (G.bits == 8) phase2_body<8, NT>(P, G, xs);
     else phase2_body<2, NT>(P, G, xs);
 }
 

@@ -1798,6 +1798,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 1) stack_mega_kernel(const MegaP
 static uint32_t cfg_max_bits(const mfb_moe_config& c) { return c.shared_bits > c.bits ? c.shared_bits : c.bits; }
 
 bool fast_supported(const mfb_moe_config& c) {
+    if (c.shared_bits == 8) return false;                             // 8-bit shared expert: generic kernels
     if (!(c.d == 512 || c.d == 1024 || c.d == 2048)) return false;   // 1, 2 or 4 groups per warp in phase 1 (k split 8)
     if (!(c.f == 256 || c.f == 512)) return false;                   // 4 groups per warp in phase 2 (k split 1 or 2)
     if (c.top_k + 1 > 32) return false;

@@ -695,8 +695,9 @@ int32_t make_map(CUtensorMap* map, void* base, uint64_t inner, uint64_t rows) {
 }  // namespace
 
 bool tc_supported(const mfb_moe_config& c) {
-    // scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512
-    return c.d % 512 == 0 && c.f % 512 == 0;
+    // scales are fetched 8 groups (16 bytes) at a time, so both contraction lengths are multiples of 512; the
+    // dequantising warps handle 4-bit and 2-bit codes (an 8-bit shared expert runs the generic kernels)
+    return c.d % 512 == 0 && c.f % 512 == 0 && c.shared_bits != 8;
 }
 
 // Everything the tensor-core path needs besides its launches, built once when the handle is created: the tensor maps

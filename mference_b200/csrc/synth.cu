@@ -94,7 +94,7 @@ extern "C" int32_t mfb_synth_expert_pool(void* stream, uint64_t root_seed, uint3
                                          uint32_t d, uint32_t f, uint8_t* pool, uint64_t slot_stride) {
     using namespace mfb;
     MFB_REQUIRE(pool != nullptr, MFB_ERR_INVALID_ARGUMENT, "synth: pool is NULL");
-    MFB_REQUIRE(bits == 4 || bits == 2, MFB_ERR_INVALID_ARGUMENT, "synth: bits must be 4 or 2");
+    MFB_REQUIRE(bits == 4 || bits == 2 || bits == 8, MFB_ERR_INVALID_ARGUMENT, "synth: bits must be 2, 4 or 8");
     MFB_REQUIRE(scale_dtype == MFB_DT_F16 || scale_dtype == MFB_DT_BF16, MFB_ERR_INVALID_ARGUMENT, "synth: scale dtype");
     MFB_REQUIRE(d % 64 == 0 && f % 64 == 0 && d && f, MFB_ERR_INVALID_ARGUMENT, "synth: d and f must be multiples of 64");
     mfb_expert_offsets off;

@@ -632,6 +632,9 @@ static inline float row_dot_f32(const uint8_t* crow, const uint16_t* s, const ui
                 dot += (float)(cg[k] & 0xF) * xg[2 * k];
                 dot += (float)(cg[k] >> 4) * xg[2 * k + 1];
             }
+        } else if (bits == 8) {
+            const uint8_t* cg = crow + g * 64;
+            for (uint32_t k = 0; k < 64; ++k) dot += (float)cg[k] * xg[k];
         } else {
             const uint8_t* cg = crow + g * 16;
             for (uint32_t k = 0; k < 16; ++k) {

@@ -52,6 +52,10 @@ SHAPES = [
     (512, 128, 8, 2, 4, 4, 5),
     (1024, 256, 8, 3, 2, 2, 11),
     (4096, 512, 6, 2, 4, 2, 2),
+    # 8-bit shared expert (SharedExpertInt8): generic kernels
+    (256, 128, 16, 4, 4, 8, 5),
+    (128, 64, 8, 2, 2, 8, 1),
+    (512, 256, 8, 2, 4, 8, 19),
 ]
 
 
