@@ -135,6 +135,10 @@ typedef struct mfb_layer_weights {
     const void* shared_gate_w;
     const void* shared_gate_s;
     const void* shared_gate_b;
+    /* Scale group of the routed experts' gate_proj: 0 or 64 = the handle's group size; 32 = DeepSeek V4's conversion on
+     * most layers (routedGateGroupSize, Sources/Mference/Runtime/Inference/ModelExpertIO.swift:118-135; kernels
+     * moe.metal:962-1062): gate_s / gate_b then hold d/32 entries per row.  Such a layer runs the generic kernels. */
+    uint32_t gate_group_size;
 } mfb_layer_weights;
 
 typedef struct mfb_moe mfb_moe;
@@ -145,6 +149,9 @@ int32_t mfb_version(void);
 uint64_t mfb_launch_count(void);
 /* Fills the offsets of the canonical blob layout (gate W,S,B · up W,S,B · down W,S,B, row-major). */
 int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes);
+/* The same with gate_proj's scales and biases per `gate_group_size` (32 or 64) elements. */
+int32_t mfb_expert_layout_gate(uint32_t bits, uint32_t d, uint32_t f, uint32_t gate_group_size, mfb_expert_offsets* off,
+                               uint64_t* blob_bytes);
 
 /* MoE.init / deinit (MoE.swift:65-151): builds the handle and its scratch arena. */
 int32_t mfb_moe_create(const mfb_moe_config* cfg, mfb_moe** out);

@@ -68,7 +68,8 @@ class LayerWeightsC(C.Structure):
                 ("slot_stride", C.c_uint64), ("slot_of", C.c_void_p), ("shared_blob", C.c_void_p),
                 ("routed_off", ExpertOffsets), ("shared_off", ExpertOffsets),
                 ("router_scales", C.c_void_p), ("router_biases", C.c_void_p), ("router_effective_scale", C.c_void_p),
-                ("shared_gate_w", C.c_void_p), ("shared_gate_s", C.c_void_p), ("shared_gate_b", C.c_void_p)]
+                ("shared_gate_w", C.c_void_p), ("shared_gate_s", C.c_void_p), ("shared_gate_b", C.c_void_p),
+                ("gate_group_size", C.c_uint32)]
 
 
 # name -> (restype, argtypes); every symbol include/mfb200.h declares
@@ -78,6 +79,7 @@ SIGNATURES = {
     "mfb_version": (_I32, []),
     "mfb_launch_count": (_U64, []),
     "mfb_expert_layout": (_I32, [_U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
+    "mfb_expert_layout_gate": (_I32, [_U32, _U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "mfb_moe_create": (_I32, [C.POINTER(MoEConfig), C.POINTER(_V)]),
     "mfb_moe_destroy": (_I32, [_V]),
     "mfb_moe_set_generic": (_I32, [_V, _I32]),

@@ -76,6 +76,8 @@ int32_t check_weights(const mfb_moe* m, const mfb_layer_weights* w, bool need_ro
     MFB_REQUIRE(!w->router_scales || !w->logit_bias, MFB_ERR_INVALID_ARGUMENT, "logit_bias is not supported with an INT8 gate");
     MFB_REQUIRE(!w->shared_gate_w || (w->shared_gate_s && w->shared_gate_b), MFB_ERR_INVALID_ARGUMENT,
                 "the shared-expert gate needs its scales and biases");
+    MFB_REQUIRE(w->gate_group_size == 0 || w->gate_group_size == 64 || w->gate_group_size == 32, MFB_ERR_INVALID_ARGUMENT,
+                "gate_group_size must be 0, 32 or 64");
     if (w->shared_blob) {
         MFB_REQUIRE(m->cfg.shared_bits != 0, MFB_ERR_INVALID_ARGUMENT, "shared blob given but the handle has shared_bits = 0");
         MFB_REQUIRE(((uintptr_t)w->shared_blob % 16) == 0 && offsets_aligned(w->shared_off), MFB_ERR_INVALID_ARGUMENT,
@@ -85,6 +87,9 @@ int32_t check_weights(const mfb_moe* m, const mfb_layer_weights* w, bool need_ro
 }
 
 uint32_t all_slots(const mfb_moe* m) { return (1u << m->cfg.top_k) - 1u; }
+
+// A layer whose routed gate_proj uses 32-element scale groups takes the generic kernels.
+bool gate64(const mfb_layer_weights* w) { return w->gate_group_size == 0 || w->gate_group_size == 64; }
 
 bool use_fast(const mfb_moe* m, uint32_t n_tokens) {
     return m->a.xp != nullptr && n_tokens <= FAST_MAX_TOKENS && (uint64_t)n_tokens * m->cfg.top_k <= 1024 &&
@@ -222,14 +227,20 @@ extern "C" int32_t mfb_version(void) { return 100; }
 extern "C" uint64_t mfb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int32_t mfb_expert_layout(uint32_t bits, uint32_t d, uint32_t f, mfb_expert_offsets* off, uint64_t* blob_bytes) {
+    return mfb_expert_layout_gate(bits, d, f, 64, off, blob_bytes);
+}
+
+extern "C" int32_t mfb_expert_layout_gate(uint32_t bits, uint32_t d, uint32_t f, uint32_t gate_group_size, mfb_expert_offsets* off,
+                                          uint64_t* blob_bytes) {
     MFB_REQUIRE(off && blob_bytes, MFB_ERR_INVALID_ARGUMENT, "layout: NULL output");
+    MFB_REQUIRE(gate_group_size == 64 || gate_group_size == 32, MFB_ERR_INVALID_ARGUMENT, "layout: gate group size must be 32 or 64");
     MFB_REQUIRE(bits == 4 || bits == 2 || bits == 8, MFB_ERR_INVALID_ARGUMENT, "layout: bits must be 2, 4 or 8");
     MFB_REQUIRE(d && f && d % 64 == 0 && f % 64 == 0, MFB_ERR_INVALID_ARGUMENT, "layout: d and f must be multiples of 64");
-    const uint64_t wbytes = (uint64_t)d * f * bits / 8, sbytes = (uint64_t)d * f / 64 * 2;
-    MFB_REQUIRE(3 * (wbytes + 2 * sbytes) <= 0xFFFFFFFFull, MFB_ERR_UNSUPPORTED_SHAPE, "layout: blob exceeds 4 GiB");
+    const uint64_t wbytes = (uint64_t)d * f * bits / 8, sbytes = (uint64_t)d * f / 64 * 2, gbytes = (uint64_t)d * f / gate_group_size * 2;
+    MFB_REQUIRE(3 * (wbytes + 2 * sbytes) + 2 * (gbytes - sbytes) <= 0xFFFFFFFFull, MFB_ERR_UNSUPPORTED_SHAPE, "layout: blob exceeds 4 GiB");
     uint32_t o = 0;
     uint32_t* p = &off->gate_w;
-    for (int i = 0; i < 9; ++i) { p[i] = o; o += (uint32_t)(i % 3 == 0 ? wbytes : sbytes); }
+    for (int i = 0; i < 9; ++i) { p[i] = o; o += (uint32_t)(i % 3 == 0 ? wbytes : (i < 3 ? gbytes : sbytes)); }
     *blob_bytes = o;
     return MFB_OK;
 }
@@ -486,7 +497,7 @@ extern "C" int32_t mfb_moe_decode(mfb_moe* moe, void* stream, const mfb_layer_we
                                   void* y) {
     int32_t rc = check_handle(moe, n_tokens);   // capacity first: the fast path below writes n_tokens rows of the arena
     if (rc) return rc;
-    if (w && x && idx && route_w && y && n_tokens && use_fast(moe, n_tokens) && ldx == moe->cfg.d) {
+    if (w && x && idx && route_w && y && n_tokens && use_fast(moe, n_tokens) && gate64(w) && ldx == moe->cfg.d) {
         rc = check_weights(moe, w, false);
         if (rc) return rc;
         const mfb_moe_config& c = moe->cfg;
@@ -522,7 +533,7 @@ extern "C" int32_t mfb_moe_layer(mfb_moe* moe, void* stream, const mfb_layer_wei
     const mfb_moe_config& c = moe->cfg;
     Arena& a = moe->a;
     cudaStream_t s = (cudaStream_t)stream;
-    if (use_fast(moe, n_tokens)) {
+    if (use_fast(moe, n_tokens) && gate64(w)) {
         const bool shared = w->shared_blob != nullptr;
         MFB_CUDA(launch_fast_prep(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, true, a.xn,
                                   a.xp, c.bits, a.xp2, c.shared_bits));
@@ -589,7 +600,7 @@ extern "C" int32_t mfb_moe_stack_rows(mfb_moe* moe, void* stream, const mfb_laye
     cudaStream_t s = (cudaStream_t)stream;
     const bool want_maps = n_tokens > 16 && moe->wide_cache != nullptr;
     bool plain = true;   // the fused kernel computes the bf16 gate itself and has no scalar gate on the shared expert
-    for (uint32_t l = 0; l < n_layers; ++l) plain = plain && !layers[l].router_scales && !layers[l].shared_gate_w;
+    for (uint32_t l = 0; l < n_layers; ++l) plain = plain && !layers[l].router_scales && !layers[l].shared_gate_w && gate64(&layers[l]);
     if (plain && use_fast(moe, n_tokens) && moe->coop && !moe->no_fused && fast_smem_stack(c, n_tokens, want_maps) <= FAST_SMEM_LIMIT) {
         for (uint32_t l = 0; l < n_layers; ++l) {
             rc = check_weights(moe, &layers[l], true);
@@ -651,7 +662,7 @@ extern "C" int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb
     const mfb_moe_config& c = moe->cfg;
     const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
     const uint32_t max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts);
-    if ((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c))
+    if ((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c) && gate64(w))
         return tc_grouped_ffn(moe, (cudaStream_t)stream, w, x, ldx, n_tokens, sorted, groups, n_groups, max_groups,
                               /*routed_only=*/true, partial, c.top_k);
     DecodeArgs d;
@@ -676,8 +687,8 @@ extern "C" int32_t mfb_moe_prefill_grouped_rows(mfb_moe* moe, void* stream, cons
     MFB_REQUIRE(x && sorted && groups && n_groups && row_dest, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped_rows: NULL argument");
     MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "prefill_grouped_rows: row stride smaller than d");
     const mfb_moe_config& c = moe->cfg;
-    MFB_REQUIRE((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c), MFB_ERR_UNSUPPORTED_SHAPE,
-                "prefill_grouped_rows needs the tensor-core path (MFB_FLAG_PREFILL_TENSOR_CORE, d and f multiples of 512)");
+    MFB_REQUIRE((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c) && gate64(w), MFB_ERR_UNSUPPORTED_SHAPE,
+                "prefill_grouped_rows needs the tensor-core path (MFB_FLAG_PREFILL_TENSOR_CORE, d and f multiples of 512, gate group 64)");
     if (n_tokens == 0) return MFB_OK;
     const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
     const uint32_t max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts);
@@ -705,7 +716,7 @@ extern "C" int32_t mfb_moe_layer_prefill(mfb_moe* moe, void* stream, const mfb_l
     MFB_REQUIRE(h_in && h_out, MFB_ERR_INVALID_ARGUMENT, "layer_prefill: NULL argument");
     if (n_tokens == 0) return MFB_OK;
     const mfb_moe_config& c = moe->cfg;
-    if (!((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c))) return mfb_moe_layer(moe, stream, w, h_in, h_out, n_tokens);
+    if (!((c.flags & MFB_FLAG_PREFILL_TENSOR_CORE) && tc_supported(c) && gate64(w))) return mfb_moe_layer(moe, stream, w, h_in, h_out, n_tokens);
     Arena& a = moe->a;
     cudaStream_t s = (cudaStream_t)stream;
     MFB_CUDA(launch_rmsnorm(s, h_in, (int)c.x_dtype, (const __nv_bfloat16*)w->norm_w, n_tokens, c.d, c.rms_eps, a.xn, (int)c.x_dtype));

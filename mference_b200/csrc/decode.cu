@@ -40,6 +40,7 @@ struct FfnParams {
     float* acts;
     float* partial;
     uint32_t slots;
+    uint32_t gate32;   // routed experts' gate_proj carries one scale and bias per 32 elements (DeepSeek V4)
 };
 
 // Shared-memory layout of one staged activation row: every 32 elements are followed by 4 pad floats, the
@@ -92,7 +93,7 @@ template <int BITS, int NT, int NMAT>
 __device__ __forceinline__ void row_dot(const uint8_t* const (&wrow)[NMAT], const uint16_t* const (&srow)[NMAT],
                                         const uint16_t* const (&brow)[NMAT], int scale_dtype, bool row_ok,
                                         uint32_t pieces, uint32_t sw, uint32_t sl, const float* xs, uint32_t xstride,
-                                        float (&acc)[NMAT][NT]) {
+                                        float (&acc)[NMAT][NT], bool gate32 = false) {
     constexpr uint32_t CPP = 128 / BITS;   // codes per 16-byte piece
     constexpr uint32_t CPW = 32 / BITS;    // codes per 32-bit word
     constexpr uint32_t MASK = (1u << BITS) - 1u;
@@ -108,9 +109,19 @@ __device__ __forceinline__ void row_dot(const uint8_t* const (&wrow)[NMAT], cons
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 q[m] = ldg_stream(wrow[m] + (size_t)pc * 16);
-                sc[m] = widen16(srow[m][elem0 >> 6], scale_dtype);
-                bi[m] = widen16(brow[m][elem0 >> 6], scale_dtype);
+                const uint32_t gidx = (gate32 && m == 0) ? elem0 >> 5 : elem0 >> 6;   // matrix 0 is gate where gate32 applies
+                sc[m] = widen16(srow[m][gidx], scale_dtype);
+                bi[m] = widen16(brow[m][gidx], scale_dtype);
             }
+            // 2-bit pieces hold 64 codes: with 32-element gate groups the piece's second half has a scale of its own
+            const bool split = gate32 && CPP == 64;
+            float sc_hi = 0.0f, bi_hi = 0.0f, dot_hi[NT];
+            if (split) {
+                sc_hi = widen16(srow[0][(elem0 >> 5) + 1], scale_dtype);
+                bi_hi = widen16(brow[0][(elem0 >> 5) + 1], scale_dtype);
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) dot_hi[t] = 0.0f;
             float dot[NMAT][NT];
 #pragma unroll
             for (int m = 0; m < NMAT; ++m)
@@ -131,25 +142,43 @@ __device__ __forceinline__ void row_dot(const uint8_t* const (&wrow)[NMAT], cons
                         const float c1 = code_f32((word >> ((j0 + 1) * BITS)) & MASK);
                         const float c2 = code_f32((word >> ((j0 + 2) * BITS)) & MASK);
                         const float c3 = code_f32((word >> ((j0 + 3) * BITS)) & MASK);
+                        if (split && m == 0 && wi >= 2) {
 #pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            dot[m][t] = fmaf(c0, xv[t].x, dot[m][t]);
-                            dot[m][t] = fmaf(c1, xv[t].y, dot[m][t]);
-                            dot[m][t] = fmaf(c2, xv[t].z, dot[m][t]);
-                            dot[m][t] = fmaf(c3, xv[t].w, dot[m][t]);
+                            for (int t = 0; t < NT; ++t) {
+                                dot_hi[t] = fmaf(c0, xv[t].x, dot_hi[t]);
+                                dot_hi[t] = fmaf(c1, xv[t].y, dot_hi[t]);
+                                dot_hi[t] = fmaf(c2, xv[t].z, dot_hi[t]);
+                                dot_hi[t] = fmaf(c3, xv[t].w, dot_hi[t]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                dot[m][t] = fmaf(c0, xv[t].x, dot[m][t]);
+                                dot[m][t] = fmaf(c1, xv[t].y, dot[m][t]);
+                                dot[m][t] = fmaf(c2, xv[t].z, dot[m][t]);
+                                dot[m][t] = fmaf(c3, xv[t].w, dot[m][t]);
+                            }
                         }
                     }
                 }
             }
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                float xsum = xs[t * xstride + padded(elem0 & ~31u) + 32];
-                if (CPP == 64) xsum += xs[t * xstride + padded((elem0 & ~31u) + 32) + 32];
+                const float xsum_lo = xs[t * xstride + padded(elem0 & ~31u) + 32];
+                const float xsum_hi = CPP == 64 ? xs[t * xstride + padded((elem0 & ~31u) + 32) + 32] : 0.0f;
+                float xsum = xsum_lo + xsum_hi;
                 if (CPP == 16 && (pc & 1u)) xsum = 0.0f;   // 8-bit codes: the 32-element sum goes with the block's first piece
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
-                    acc[m][t] = fmaf(sc[m], dot[m][t], acc[m][t]);
-                    acc[m][t] = fmaf(bi[m], xsum, acc[m][t]);
+                    if (split && m == 0) {
+                        acc[m][t] = fmaf(sc[m], dot[m][t], acc[m][t]);
+                        acc[m][t] = fmaf(bi[m], xsum_lo, acc[m][t]);
+                        acc[m][t] = fmaf(sc_hi, dot_hi[t], acc[m][t]);
+                        acc[m][t] = fmaf(bi_hi, xsum_hi, acc[m][t]);
+                    } else {
+                        acc[m][t] = fmaf(sc[m], dot[m][t], acc[m][t]);
+                        acc[m][t] = fmaf(bi[m], xsum, acc[m][t]);
+                    }
                 }
             }
         }
@@ -197,6 +226,8 @@ __device__ void phase1_body(const FfnParams& P, const GroupView& G, float* xs) {
     const uint32_t rows_per_set = 32 / sw, rows_per_block = FFN_WARPS * FFN_SETS_PER_WARP * rows_per_set;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sl = lane % sw, sub = lane / sw;
     const uint32_t row_bytes = d * BITS / 8, groups_per_row = d / 64, xstride = padded(d);
+    const bool gate32 = P.gate32 && !G.shared;                       // 32-element groups: routed experts' gate_proj only
+    const uint32_t gate_groups_per_row = gate32 ? d / 32 : d / 64;
     const uint32_t r_begin = blockIdx.x * rows_per_block;
     for (uint32_t t0 = 0; t0 < G.pair_count; t0 += NT) {
         const uint32_t nv = min((uint32_t)NT, G.pair_count - t0);
@@ -212,12 +243,12 @@ __device__ void phase1_body(const FfnParams& P, const GroupView& G, float* xs) {
             const uint32_t r = r_begin + (warp * FFN_SETS_PER_WARP + set) * rows_per_set + sub;
             const bool ok = r < f;
             const uint8_t* const wr[2] = {G.blob + G.off.gate_w + (size_t)r * row_bytes, G.blob + G.off.up_w + (size_t)r * row_bytes};
-            const uint16_t* const sr[2] = {(const uint16_t*)(G.blob + G.off.gate_s) + (size_t)r * groups_per_row,
+            const uint16_t* const sr[2] = {(const uint16_t*)(G.blob + G.off.gate_s) + (size_t)r * gate_groups_per_row,
                                            (const uint16_t*)(G.blob + G.off.up_s) + (size_t)r * groups_per_row};
-            const uint16_t* const br[2] = {(const uint16_t*)(G.blob + G.off.gate_b) + (size_t)r * groups_per_row,
+            const uint16_t* const br[2] = {(const uint16_t*)(G.blob + G.off.gate_b) + (size_t)r * gate_groups_per_row,
                                            (const uint16_t*)(G.blob + G.off.up_b) + (size_t)r * groups_per_row};
             float acc[2][NT];
-            row_dot<BITS, NT, 2>(wr, sr, br, (int)P.scale_dtype, ok, pieces, sw, sl, xs, xstride, acc);
+            row_dot<BITS, NT, 2>(wr, sr, br, (int)P.scale_dtype, ok, pieces, sw, sl, xs, xstride, acc, gate32);
             if (ok && sl == 0) {
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
@@ -332,6 +363,7 @@ cudaError_t launch_decode_ffn(cudaStream_t s, const DecodeArgs& a) {
     P.shared_bits = a.shared_bits; P.scale_dtype = a.scale_dtype; P.activation = a.activation; P.limit = a.swiglu_limit;
     P.x = a.x; P.x_dtype = a.x_dtype; P.ldx = a.ldx; P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
     P.acts = a.acts; P.partial = a.partial; P.slots = a.slots;
+    P.gate32 = a.w->gate_group_size == 32 ? 1u : 0u;
     if (a.max_groups == 0) return cudaSuccess;
     // rows of one expert are applied to NT token rows per pass over its codes
     if (a.max_groups <= a.top_k + 1) return launch_nt<1>(s, P, a.max_groups);   // single token

@@ -25,11 +25,12 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def expert_layout(bits: int, d: int, f: int):
-    """Canonical blob layout: (ExpertOffsets, blob_bytes)."""
+def expert_layout(bits: int, d: int, f: int, gate_group_size: int = 64):
+    """Canonical blob layout: (ExpertOffsets, blob_bytes); gate_group_size 32 gives gate_proj one scale and bias per 32
+    elements (DeepSeek V4's conversion, ModelExpertIO.swift:118-135)."""
     off = L.ExpertOffsets()
     total = C.c_uint64()
-    L.check(L.load().mfb_expert_layout(bits, d, f, C.byref(off), C.byref(total)))
+    L.check(L.load().mfb_expert_layout_gate(bits, d, f, gate_group_size, C.byref(off), C.byref(total)))
     return off, total.value
 
 
@@ -54,6 +55,7 @@ class MoELayerWeights:
     shared_gate_w: Optional[torch.Tensor] = None            # uint8 [d]
     shared_gate_s: Optional[torch.Tensor] = None            # bf16 [d/64]
     shared_gate_b: Optional[torch.Tensor] = None
+    gate_group_size: int = 0                                # routed gate_proj scale group: 0 / 64, or 32
 
     def c_struct(self) -> L.LayerWeightsC:
         w = L.LayerWeightsC()
@@ -71,6 +73,7 @@ class MoELayerWeights:
         for name in ("router_scales", "router_biases", "router_effective_scale", "shared_gate_w", "shared_gate_s", "shared_gate_b"):
             t = getattr(self, name)
             setattr(w, name, None if t is None else t.data_ptr())
+        w.gate_group_size = self.gate_group_size
         return w
 
 

@@ -83,10 +83,16 @@ void mfbo_fill_normal(uint64_t seed, uint64_t first_value, uint64_t n, double me
 /* Blob layout of Sources/Mference/Kernels/MoE/MoE.swift:4-29: gate W,S,B then up W,S,B then down W,S,B,
  * each sub-tensor row-major; gate/up are [f, d], down is [d, f]; 64 elements per scale group. */
 void mfbo_make_offsets(int bits, uint32_t d, uint32_t f, mfbo_expert_offsets* off, uint64_t* blob_bytes) {
+    mfbo_make_offsets_gate(bits, d, f, 64u, off, blob_bytes);
+}
+
+/* DeepSeek V4 ships most layers' gate_proj at group 32 (ModelExpertIO.swift:118-135, moe.metal:962-965): only the
+ * scale / bias row stride of gate changes. */
+void mfbo_make_offsets_gate(int bits, uint32_t d, uint32_t f, uint32_t gate_group, mfbo_expert_offsets* off, uint64_t* blob_bytes) {
     const uint32_t wbytes = (uint32_t)((uint64_t)d * f * (uint32_t)bits / 8u);
-    const uint32_t sbytes = d * f / 64u * 2u;
+    const uint32_t sbytes = d * f / 64u * 2u, gbytes = d * f / gate_group * 2u;
     uint32_t o = 0;
-    off->gate_w = o; o += wbytes; off->gate_s = o; o += sbytes; off->gate_b = o; o += sbytes;
+    off->gate_w = o; o += wbytes; off->gate_s = o; o += gbytes; off->gate_b = o; o += gbytes;
     off->up_w = o; o += wbytes; off->up_s = o; o += sbytes; off->up_b = o; o += sbytes;
     off->down_w = o; o += wbytes; off->down_s = o; o += sbytes; off->down_b = o; o += sbytes;
     *blob_bytes = o;
@@ -94,16 +100,22 @@ void mfbo_make_offsets(int bits, uint32_t d, uint32_t f, mfbo_expert_offsets* of
 
 void mfbo_synth_expert(uint64_t root, uint32_t layer, int32_t expert, int bits, int scale_dtype, uint32_t d,
                        uint32_t f, uint8_t* blob) {
+    mfbo_synth_expert_gate(root, layer, expert, bits, scale_dtype, d, f, 64u, blob);
+}
+
+void mfbo_synth_expert_gate(uint64_t root, uint32_t layer, int32_t expert, int bits, int scale_dtype, uint32_t d,
+                            uint32_t f, uint32_t gate_group, uint8_t* blob) {
     static const char* proj[3] = {"gate", "up", "down"};
     mfbo_expert_offsets off;
     uint64_t total;
-    mfbo_make_offsets(bits, d, f, &off, &total);
+    mfbo_make_offsets_gate(bits, d, f, gate_group, &off, &total);
     const uint32_t* o = &off.gate_w;
-    const uint64_t wbytes = (uint64_t)d * f * (uint32_t)bits / 8u, n_groups = (uint64_t)d * f / 64u;
+    const uint64_t wbytes = (uint64_t)d * f * (uint32_t)bits / 8u;
     char who[48], label[96];
     if (expert < 0) snprintf(who, sizeof who, "L%u.shared", layer);
     else snprintf(who, sizeof who, "L%u.e%d", layer, expert);
     for (int p = 0; p < 3; ++p) {
+        const uint64_t n_groups = (uint64_t)d * f / (p == 0 ? gate_group : 64u);
         snprintf(label, sizeof label, "%s.%s.q", who, proj[p]);
         mfbo_fill_raw(mfbo_seed_for_label(root, label), 0, wbytes / 8u, (uint64_t*)(blob + o[3 * p]));
         snprintf(label, sizeof label, "%s.%s.s", who, proj[p]);
@@ -361,13 +373,19 @@ typedef struct expert_f32 {
     float *gate, *up, *down; /* [f,d], [f,d], [d,f] */
 } expert_f32;
 
+static void expert_dequant_gate(const uint8_t* blob, const mfbo_expert_offsets* off, int bits, int group_size, int gate_group,
+                                int scale_dtype, uint32_t d, uint32_t f, expert_f32* w);
 static void expert_dequant(const uint8_t* blob, const mfbo_expert_offsets* off, int bits, int group_size,
                            int scale_dtype, uint32_t d, uint32_t f, expert_f32* w) {
+    expert_dequant_gate(blob, off, bits, group_size, group_size, scale_dtype, d, f, w);
+}
+static void expert_dequant_gate(const uint8_t* blob, const mfbo_expert_offsets* off, int bits, int group_size, int gate_group,
+                                int scale_dtype, uint32_t d, uint32_t f, expert_f32* w) {
     w->gate = (float*)malloc(sizeof(float) * (size_t)d * f);
     w->up = (float*)malloc(sizeof(float) * (size_t)d * f);
     w->down = (float*)malloc(sizeof(float) * (size_t)d * f);
     mfbo_dequant_rows(blob + off->gate_w, (const uint16_t*)(blob + off->gate_s), (const uint16_t*)(blob + off->gate_b),
-                      bits, group_size, scale_dtype, f, d, w->gate);
+                      bits, gate_group, scale_dtype, f, d, w->gate);
     mfbo_dequant_rows(blob + off->up_w, (const uint16_t*)(blob + off->up_s), (const uint16_t*)(blob + off->up_b),
                       bits, group_size, scale_dtype, f, d, w->up);
     mfbo_dequant_rows(blob + off->down_w, (const uint16_t*)(blob + off->down_s), (const uint16_t*)(blob + off->down_b),
@@ -425,8 +443,8 @@ void mfbo_moe_layer(const mfbo_layer* L, const uint16_t* x, int x_dtype, uint32_
         expert_f32 w;
         if (shared) expert_dequant(L->shared_blob, &L->shared_off, (int)L->shared_bits, (int)L->group_size,
                                    (int)L->scale_dtype, d, f, &w);
-        else expert_dequant(L->pool + (uint64_t)e * L->expert_stride, &L->routed_off, (int)L->bits,
-                            (int)L->group_size, (int)L->scale_dtype, d, f, &w);
+        else expert_dequant_gate(L->pool + (uint64_t)e * L->expert_stride, &L->routed_off, (int)L->bits, (int)L->group_size,
+                                 (int)(L->gate_group_size ? L->gate_group_size : L->group_size), (int)L->scale_dtype, d, f, &w);
         for (uint32_t t = 0; t < n_tokens; ++t) {
             if (shared) {
                 expert_apply(&w, d, f, (int)L->activation, 0.0f, xf + (size_t)t * d, part + ((size_t)t * slots + K) * d);
@@ -462,7 +480,8 @@ void mfbo_pair_partials(const mfbo_layer* L, const uint16_t* x, int x_dtype, uin
         for (uint32_t p = 0; !any && p < n_pairs; ++p) any = (pairs[p].expert == (uint32_t)e);
         if (!any) continue;
         expert_f32 w;
-        expert_dequant(L->pool + (uint64_t)e * L->expert_stride, &L->routed_off, (int)L->bits, (int)L->group_size,
+        expert_dequant_gate(L->pool + (uint64_t)e * L->expert_stride, &L->routed_off, (int)L->bits, (int)L->group_size,
+                       (int)(L->gate_group_size ? L->gate_group_size : L->group_size),
                        (int)L->scale_dtype, d, f, &w);
         float* xf = (float*)malloc(sizeof(float) * d);
         double* out = (double*)malloc(sizeof(double) * d);

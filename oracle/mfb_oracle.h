@@ -67,8 +67,12 @@ void mfbo_fill_normal(uint64_t seed, uint64_t first_value, uint64_t n, double me
  * Codes are the raw little-endian draw stream (uniform nibbles / crumbs), scales are |N(0,0.02)| and biases
  * N(0,0.01) rounded to the 16-bit scale dtype, router weights are N(0,0.02) in bf16. ---- */
 void mfbo_make_offsets(int bits, uint32_t d, uint32_t f, mfbo_expert_offsets* off, uint64_t* blob_bytes);
+/* the same with gate_proj scales and biases per `gate_group` elements (32 or 64) */
+void mfbo_make_offsets_gate(int bits, uint32_t d, uint32_t f, uint32_t gate_group, mfbo_expert_offsets* off, uint64_t* blob_bytes);
 void mfbo_synth_expert(uint64_t root, uint32_t layer, int32_t expert, int bits, int scale_dtype, uint32_t d,
                        uint32_t f, uint8_t* blob);
+void mfbo_synth_expert_gate(uint64_t root, uint32_t layer, int32_t expert, int bits, int scale_dtype, uint32_t d,
+                            uint32_t f, uint32_t gate_group, uint8_t* blob);
 void mfbo_synth_router(uint64_t root, uint32_t layer, uint32_t num_experts, uint32_t d, uint16_t* w_bf16);
 
 /* ---- scalar conversions (Sources/Mference/Infrastructure/ModelIO/Quantization.swift:16-28) ---- */
@@ -104,6 +108,7 @@ typedef struct mfbo_layer {
     uint64_t expert_stride;
     const uint8_t* shared_blob; /* may be NULL */
     mfbo_expert_offsets routed_off, shared_off;
+    uint32_t gate_group_size;   /* routed experts' gate_proj: 0 = group_size, or 32 (DeepSeek V4: ModelExpertIO.swift:118-135) */
 } mfbo_layer;
 
 void mfbo_expert_ffn(const uint8_t* blob, const mfbo_expert_offsets* off, int bits, int group_size,

@@ -37,7 +37,7 @@ class Layer(C.Structure):
                 ("bits", C.c_uint32), ("shared_bits", C.c_uint32), ("group_size", C.c_uint32),
                 ("scale_dtype", C.c_uint32), ("activation", C.c_uint32), ("swiglu_limit", C.c_float),
                 ("pool", C.c_void_p), ("expert_stride", C.c_uint64), ("shared_blob", C.c_void_p),
-                ("routed_off", ExpertOffsets), ("shared_off", ExpertOffsets)]
+                ("routed_off", ExpertOffsets), ("shared_off", ExpertOffsets), ("gate_group_size", C.c_uint32)]
 
 
 PAIR_DTYPE = np.dtype([("token", "<u4"), ("expert", "<u4"), ("rank", "<u4"), ("weight_bits", "<u4")])
@@ -116,18 +116,20 @@ def fill_normal(seed: int, n: int, mean=0.0, std=1.0, absolute=False, dtype=DT_B
     return out
 
 
-def make_offsets(bits: int, d: int, f: int):
+def make_offsets(bits: int, d: int, f: int, gate_group_size: int = 64):
     off = ExpertOffsets()
     total = C.c_uint64()
-    lib().mfbo_make_offsets(C.c_int(bits), C.c_uint32(d), C.c_uint32(f), C.byref(off), C.byref(total))
+    lib().mfbo_make_offsets_gate(C.c_int(bits), C.c_uint32(d), C.c_uint32(f), C.c_uint32(gate_group_size), C.byref(off),
+                                 C.byref(total))
     return off, total.value
 
 
-def synth_expert(root: int, layer: int, expert: int, bits: int, scale_dtype: int, d: int, f: int) -> np.ndarray:
-    _, total = make_offsets(bits, d, f)
+def synth_expert(root: int, layer: int, expert: int, bits: int, scale_dtype: int, d: int, f: int,
+                 gate_group_size: int = 64) -> np.ndarray:
+    _, total = make_offsets(bits, d, f, gate_group_size)
     blob = np.empty(total, dtype=np.uint8)
-    lib().mfbo_synth_expert(C.c_uint64(root), C.c_uint32(layer), C.c_int32(expert), C.c_int(bits),
-                            C.c_int(scale_dtype), C.c_uint32(d), C.c_uint32(f), _p(blob))
+    lib().mfbo_synth_expert_gate(C.c_uint64(root), C.c_uint32(layer), C.c_int32(expert), C.c_int(bits),
+                                 C.c_int(scale_dtype), C.c_uint32(d), C.c_uint32(f), C.c_uint32(gate_group_size), _p(blob))
     return blob
 
 
@@ -232,18 +234,20 @@ class LayerWeights:
     """Host copy of one synthetic MoE layer: a pool of expert blobs, a shared blob and the router."""
 
     def __init__(self, d, f, num_experts, top_k, bits=4, shared_bits=4, scale_dtype=DT_F16,
-                 activation=ACT_SILU, swiglu_limit=0.0, root=0xB2000001, layer=0, experts=None, shared=True):
+                 activation=ACT_SILU, swiglu_limit=0.0, root=0xB2000001, layer=0, experts=None, shared=True,
+                 gate_group_size=64):
         self.d, self.f, self.num_experts, self.top_k = d, f, num_experts, top_k
         self.bits, self.shared_bits, self.scale_dtype = bits, shared_bits, scale_dtype
         self.activation, self.swiglu_limit = activation, swiglu_limit
-        self.routed_off, self.blob_bytes = make_offsets(bits, d, f)
+        self.gate_group_size = gate_group_size   # routed experts' gate_proj only (DeepSeek V4: 32 on most layers)
+        self.routed_off, self.blob_bytes = make_offsets(bits, d, f, gate_group_size)
         self.shared_off, self.shared_bytes = make_offsets(shared_bits, d, f)
         self.expert_stride = (self.blob_bytes + 255) // 256 * 256
         self.pool = np.zeros(num_experts * self.expert_stride, dtype=np.uint8)
         which = range(num_experts) if experts is None else experts
         for e in which:
             self.pool[e * self.expert_stride: e * self.expert_stride + self.blob_bytes] = \
-                synth_expert(root, layer, e, bits, scale_dtype, d, f)
+                synth_expert(root, layer, e, bits, scale_dtype, d, f, gate_group_size)
         self.shared_blob = synth_expert(root, layer, -1, shared_bits, scale_dtype, d, f) if shared else None
         self.router = synth_router(root, layer, num_experts, d)
 
@@ -256,6 +260,7 @@ class LayerWeights:
         L.expert_stride = self.expert_stride
         L.shared_blob = None if self.shared_blob is None else self.shared_blob.ctypes.data
         L.routed_off, L.shared_off = self.routed_off, self.shared_off
+        L.gate_group_size = self.gate_group_size
         return L
 
 

@@ -40,7 +40,8 @@ def upload_layer(W: "O.LayerWeights", device="cuda", slot_of=None, norm=True):
         router_w=router, pool=pool, slot_stride=W.expert_stride, routed_off=offs(W.routed_off), shared_blob=shared,
         shared_off=None if shared is None else offs(W.shared_off),
         norm_w=torch.ones(W.d, dtype=torch.bfloat16, device=device) if norm else None,
-        slot_of=None if slot_of is None else torch.tensor(slot_of, dtype=torch.int16, device=device))
+        slot_of=None if slot_of is None else torch.tensor(slot_of, dtype=torch.int16, device=device),
+        gate_group_size=getattr(W, "gate_group_size", 64))
 
 
 def to_dev16(bits: np.ndarray, dtype, device="cuda"):

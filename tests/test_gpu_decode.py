@@ -72,6 +72,23 @@ def test_decode_matches_oracle(d, f, E, K, bits, sbits, T):
     assert O.rel_l2(y, ref) <= TOL_REL_L2
 
 
+@pytest.mark.parametrize("d,f,E,K,bits,T", [(256, 128, 16, 4, 2, 5), (512, 256, 8, 2, 2, 1), (256, 128, 8, 3, 4, 7),
+                                            (2048, 512, 12, 4, 2, 3)])
+def test_decode_with_32_element_gate_groups_matches_oracle(d, f, E, K, bits, T):
+    # DeepSeek V4's conversion: gate_proj of the routed experts with one scale and bias per 32 elements
+    # (routedGateGroupSize, ModelExpertIO.swift:118-135); up, down and the shared expert keep 64
+    W = O.LayerWeights(d, f, E, K, bits=bits, shared_bits=4, gate_group_size=32)
+    x = make_x("x.g32", T, d)
+    idx, w = _route(W, x)
+    res = make_x("res.g32", T, d)
+    y, *_ = _run_decode(W, x, idx, w, residual_bits=res)
+    ref = O.moe_layer(W, x, O.DT_BF16, idx, w, O.bf16_to_f32(res))
+    assert O.rel_l2(y, ref) <= TOL_REL_L2, O.rel_l2(y, ref)
+    # and it is not the 64-element reading of the same bytes
+    W64 = O.LayerWeights(d, f, E, K, bits=bits, shared_bits=4, gate_group_size=64)
+    assert W.blob_bytes > W64.blob_bytes
+
+
 def test_decode_config0_qwen_layer_single_token():
     # BASELINE configs[0]: hidden 2048, 256 experts top-8 + 1 shared, intermediate 512, 4-bit group-64
     K = 8
