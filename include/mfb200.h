@@ -312,6 +312,15 @@ int32_t mfb_moe_prefill_grouped(mfb_moe* moe, void* stream, const mfb_layer_weig
 int32_t mfb_moe_prefill_grouped_rows(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
                                      uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
                                      const uint32_t* n_groups, float* const* row_dest);
+/* The Inkling batched expert application (inkling_prefill_expert_act + inkling_prefill_expert_down_accum,
+ * Sources/Mference/Metal/Prefill/prefill.metal:654-746): the grouped expert FFN with gate and up rounded to fp16
+ * before the activation and the product stored as fp16, accumulated expert by expert - ascending expert id, the order
+ * the reference's host loop dispatches them - into an fp32 accumulator with fp32 pair weights:
+ * acc[t,:] = fma(pair_weights[t*top_k + rank], down_row, acc[t,:]).  acc is f32 [n_tokens, d], read and written
+ * (the caller zeroes it, or leaves the shared expert's contribution in it); routed experts only; generic kernels. */
+int32_t mfb_moe_prefill_accumulate_f32(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                       uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
+                                       const uint32_t* n_groups, const float* pair_weights, float* acc);
 /* h2[t,:] = sum_r w[t,r] * partial[t,r,:] in rank order (+ residual).  Replaces
  * PrefillMoE.encodeReduceTokenMajor (Sources/Mference/Kernels/Prefill/MoE/PrefillMoE.swift:11-38). */
 int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w, uint32_t n_tokens,

@@ -79,6 +79,7 @@ SIGNATURES = {
     "mfb_version": (_I32, []),
     "mfb_launch_count": (_U64, []),
     "mfb_expert_layout": (_I32, [_U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
+    "mfb_moe_prefill_accumulate_f32": (_I32, [_V, _V, C.POINTER(LayerWeightsC), _V, _U32, _U32, _V, _V, _V, _V, _V]),
     "mfb_expert_layout_gate": (_I32, [_U32, _U32, _U32, _U32, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "mfb_moe_create": (_I32, [C.POINTER(MoEConfig), C.POINTER(_V)]),
     "mfb_moe_destroy": (_I32, [_V]),

@@ -696,6 +696,34 @@ extern "C" int32_t mfb_moe_prefill_grouped_rows(mfb_moe* moe, void* stream, cons
                           nullptr, c.top_k, row_dest);
 }
 
+extern "C" int32_t mfb_moe_prefill_accumulate_f32(mfb_moe* moe, void* stream, const mfb_layer_weights* w, const void* x, uint32_t ldx,
+                                                  uint32_t n_tokens, const mfb_pair* sorted, const mfb_group* groups,
+                                                  const uint32_t* n_groups, const float* pair_weights, float* acc) {
+    int32_t rc = check_handle(moe, n_tokens);
+    if (rc) return rc;
+    rc = check_weights(moe, w, false);
+    if (rc) return rc;
+    MFB_REQUIRE(x && sorted && groups && n_groups && pair_weights && acc, MFB_ERR_INVALID_ARGUMENT, "prefill_accumulate_f32: NULL argument");
+    MFB_REQUIRE(ldx >= moe->cfg.d, MFB_ERR_INVALID_ARGUMENT, "prefill_accumulate_f32: row stride smaller than d");
+    if (n_tokens == 0) return MFB_OK;
+    const mfb_moe_config& c = moe->cfg;
+    Arena& a = moe->a;
+    const uint64_t pairs = (uint64_t)n_tokens * c.top_k;
+    DecodeArgs d;
+    mfb_layer_weights routed_only = *w;
+    routed_only.shared_blob = nullptr;
+    d.w = &routed_only; d.d = c.d; d.f = c.f; d.num_experts = c.num_experts; d.top_k = c.top_k; d.bits = c.bits;
+    d.shared_bits = c.shared_bits; d.scale_dtype = c.scale_dtype; d.activation = c.activation;
+    d.swiglu_limit = c.swiglu_limit; d.x = x; d.x_dtype = (int)c.x_dtype; d.ldx = ldx; d.sorted = sorted;
+    d.groups = groups; d.n_groups = n_groups; d.max_groups = (uint32_t)(pairs < c.num_experts ? pairs : c.num_experts);
+    d.acts = a.acts; d.partial = a.partial; d.slots = c.top_k; d.round16 = 1;
+    MFB_CUDA(launch_decode_ffn((cudaStream_t)stream, d));
+    // the (token, rank) -> expert table lives in the index scratch of the router, which this call does not use
+    MFB_CUDA(launch_accumulate_expert_order((cudaStream_t)stream, sorted, groups, n_groups, n_tokens, c.top_k, c.d, a.partial,
+                                            pair_weights, a.idx, acc));
+    return MFB_OK;
+}
+
 extern "C" int32_t mfb_moe_reduce(mfb_moe* moe, void* stream, const float* partial, const uint16_t* route_w,
                                   uint32_t n_tokens, const void* residual, void* y) {
     int32_t rc = check_handle(moe, 0);

@@ -167,8 +167,13 @@ struct DecodeArgs {
     float* acts;     // [rows, f]
     float* partial;  // [rows, d]
     uint32_t slots;  // top_k + 1
+    uint32_t round16 = 0;   // gate, up and the activation product rounded to fp16 (inkling_prefill_expert_act, prefill.metal:695-721)
 };
 cudaError_t launch_decode_ffn(cudaStream_t s, const DecodeArgs& a);
+// acc[t, :] = fma(w[t, r], partial[t * top_k + r, :], acc[t, :]) over the ranks of token t in ascending expert order
+cudaError_t launch_accumulate_expert_order(cudaStream_t s, const mfb_pair* sorted, const mfb_group* groups, const uint32_t* n_groups,
+                                           uint32_t n_tokens, uint32_t top_k, uint32_t d, const float* partial,
+                                           const float* pair_weights, uint32_t* tok_expert, float* acc);
 // synth.cu
 cudaError_t launch_synth_pool(cudaStream_t s, const uint64_t* seeds_dev, uint32_t n_experts, uint32_t bits,
                               uint32_t scale_dtype, uint32_t d, uint32_t f, uint8_t* pool, uint64_t slot_stride,

@@ -41,6 +41,7 @@ struct FfnParams {
     float* partial;
     uint32_t slots;
     uint32_t gate32;   // routed experts' gate_proj carries one scale and bias per 32 elements (DeepSeek V4)
+    uint32_t round16;  // gate, up and their activation product rounded to fp16 (the Inkling batched expert kernels)
 };
 
 // Shared-memory layout of one staged activation row: every 32 elements are followed by 4 pad floats, the
@@ -258,7 +259,13 @@ __device__ void phase1_body(const FfnParams& P, const GroupView& G, float* xs) {
                             g = fminf(g, P.limit);
                             u = fminf(fmaxf(u, -P.limit), P.limit);
                         }
-                        P.acts[(size_t)(G.pair_start + t0 + t) * f + r] = hidden_act(g, (int)P.activation) * u;
+                        if (P.round16) {   // prefill.metal:714-721: the two GEMV results pass through fp16 before they are combined
+                            g = __half2float(__float2half_rn(g));
+                            u = __half2float(__float2half_rn(u));
+                        }
+                        float a = hidden_act(g, (int)P.activation) * u;
+                        if (P.round16) a = __half2float(__float2half_rn(a));
+                        P.acts[(size_t)(G.pair_start + t0 + t) * f + r] = a;
                     }
                 }
             }
@@ -364,6 +371,7 @@ cudaError_t launch_decode_ffn(cudaStream_t s, const DecodeArgs& a) {
     P.x = a.x; P.x_dtype = a.x_dtype; P.ldx = a.ldx; P.sorted = a.sorted; P.groups = a.groups; P.n_groups = a.n_groups;
     P.acts = a.acts; P.partial = a.partial; P.slots = a.slots;
     P.gate32 = a.w->gate_group_size == 32 ? 1u : 0u;
+    P.round16 = a.round16;
     if (a.max_groups == 0) return cudaSuccess;
     // rows of one expert are applied to NT token rows per pass over its codes
     if (a.max_groups <= a.top_k + 1) return launch_nt<1>(s, P, a.max_groups);   // single token

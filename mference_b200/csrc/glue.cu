@@ -110,6 +110,57 @@ __global__ void combine_kernel(const float* __restrict__ partial, const uint16_t
 
 }  // namespace
 
+// Expert id of every (token, rank) from the expert-major pair list; pairs that are not in the list keep 0xFFFFFFFF.
+__global__ void pair_expert_table_kernel(const mfb_pair* __restrict__ sorted, const mfb_group* __restrict__ groups,
+                                         const uint32_t* __restrict__ n_groups, uint32_t top_k, uint32_t num_slots,
+                                         uint32_t* __restrict__ tok_expert) {
+    const uint32_t ng = *n_groups;
+    if (ng == 0) return;
+    const mfb_group last = groups[ng - 1];
+    const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= last.pair_start + last.pair_count) return;
+    const mfb_pair pr = sorted[p];
+    if (pr.rank < top_k && pr.token * top_k + pr.rank < num_slots) tok_expert[pr.token * top_k + pr.rank] = pr.expert;
+}
+
+// inkling_prefill_expert_down_accum (Sources/Mference/Metal/Prefill/prefill.metal:723-744) applied expert by expert in
+// the order its host loop dispatches them (ascending expert id): for token t the ranks are visited in ascending expert
+// order and acc = fma(weight, row, acc) in fp32.  One thread per (token, column); no atomics.
+__global__ void accumulate_expert_order_kernel(const float* __restrict__ partial, const float* __restrict__ pair_weights,
+                                               const uint32_t* __restrict__ tok_expert, uint32_t n_tokens, uint32_t top_k,
+                                               uint32_t d, float* __restrict__ acc) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)n_tokens * d) return;
+    const uint32_t t = (uint32_t)(i / d), c = (uint32_t)(i % d);
+    float a = acc[i];
+    uint32_t done = 0;   // bit r: rank r has been applied
+    for (uint32_t step = 0; step < top_k; ++step) {
+        uint32_t best = 0xFFFFFFFFu, best_r = 0;
+        for (uint32_t r = 0; r < top_k; ++r) {
+            const uint32_t e = tok_expert[t * top_k + r];
+            if (!((done >> r) & 1u) && e < best) { best = e; best_r = r; }
+        }
+        if (best == 0xFFFFFFFFu) break;   // the remaining ranks are not in the pair list
+        done |= 1u << best_r;
+        a = fmaf(pair_weights[t * top_k + best_r], partial[((size_t)t * top_k + best_r) * d + c], a);
+    }
+    acc[i] = a;
+}
+
+cudaError_t launch_accumulate_expert_order(cudaStream_t s, const mfb_pair* sorted, const mfb_group* groups, const uint32_t* n_groups,
+                                           uint32_t n_tokens, uint32_t top_k, uint32_t d, const float* partial,
+                                           const float* pair_weights, uint32_t* tok_expert, float* acc) {
+    if (n_tokens == 0) return cudaSuccess;
+    const uint32_t slots = n_tokens * top_k;
+    cudaError_t e = cudaMemsetAsync(tok_expert, 0xFF, (size_t)slots * sizeof(uint32_t), s);
+    if (e != cudaSuccess) return e;
+    pair_expert_table_kernel<<<(slots + 255) / 256, 256, 0, s>>>(sorted, groups, n_groups, top_k, slots, tok_expert);
+    const uint64_t n = (uint64_t)n_tokens * d;
+    accumulate_expert_order_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, pair_weights, tok_expert, n_tokens, top_k, d, acc);
+    count_launches(2);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_rmsnorm(cudaStream_t s, const void* x, int in_dtype, const __nv_bfloat16* w, uint32_t n_rows,
                            uint32_t d, float eps, void* out, int out_dtype) {
     if (n_rows == 0) return cudaSuccess;

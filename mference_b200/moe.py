@@ -227,6 +227,14 @@ class MoE:
         L.check(self.lib.mfb_moe_prefill_grouped(self.handle, _stream(), C.byref(w), _ptr(x), x.stride(0), x.shape[0],
                                                  _ptr(sorted_pairs), _ptr(groups), _ptr(n_groups), _ptr(partial)))
 
+    def encode_prefill_accumulate_f32(self, weights, x, sorted_pairs, groups, n_groups, pair_weights, acc):
+        """The Inkling batched expert application (inkling_prefill_expert_act / _down_accum, prefill.metal:654-746):
+        acc (f32 [T, d], read and written) += the routed experts' rows, expert by expert, with f32 pair weights [T, top_k]."""
+        w = weights.c_struct()
+        L.check(self.lib.mfb_moe_prefill_accumulate_f32(self.handle, _stream(), C.byref(w), _ptr(x), x.stride(0), x.shape[0],
+                                                        _ptr(sorted_pairs), _ptr(groups), _ptr(n_groups), _ptr(pair_weights),
+                                                        _ptr(acc)))
+
     def encode_reduce_token_major(self, partial, routing_weights, y, residual=None):
         """PrefillMoE.encodeReduceTokenMajor."""
         L.check(self.lib.mfb_moe_reduce(self.handle, _stream(), _ptr(partial), _ptr(routing_weights), y.shape[0],

@@ -285,6 +285,25 @@ def pair_partials(W: LayerWeights, x, x_dtype, pairs) -> np.ndarray:
     return out
 
 
+def inkling_accumulate(W: LayerWeights, x, x_dtype, idx, w_f32, acc0=None) -> np.ndarray:
+    """inkling_prefill_expert_act + inkling_prefill_expert_down_accum (Sources/Mference/Metal/Prefill/prefill.metal:
+    654-746): expert by expert in ascending expert id, acc[t] = fma(w[t, r], down_row(t, r), acc[t]) in fp32; idx is
+    [T, K] expert ids, w_f32 [T, K].  The rows come from the float64 definition (`pair_partials`); the reference's
+    fp16 roundings of gate, up and their product are below the parity tolerance and are not modelled."""
+    idx = np.asarray(idx)
+    T, K = idx.shape
+    pairs = np.zeros(T * K, dtype=PAIR_DTYPE)
+    pairs["token"] = np.repeat(np.arange(T, dtype=np.uint32), K)
+    pairs["expert"] = idx.reshape(-1)
+    pairs["rank"] = np.tile(np.arange(K, dtype=np.uint32), T)
+    rows = pair_partials(W, x, x_dtype, pairs).reshape(T, K, W.d).astype(np.float32)
+    acc = np.zeros((T, W.d), dtype=np.float32) if acc0 is None else np.array(acc0, dtype=np.float32, copy=True)
+    for t in range(T):
+        for r in np.argsort(idx[t], kind="stable"):
+            acc[t] = np.float32(w_f32[t, r]) * rows[t, r] + acc[t]
+    return acc
+
+
 def ref_moe_layer_f32(W: LayerWeights, x_f32, idx, w_f16, residual=None) -> np.ndarray:
     x = _c(x_f32, np.float32); idx = _c(idx, np.uint32); w = _c(w_f16, np.uint16)
     T, d = x.shape

@@ -44,6 +44,33 @@ def test_grouped_ffn_and_reduce_match_oracle(d, f, E, K, bits, T):
     assert O.rel_l2(y, h2) <= TOL_REL_L2
 
 
+@pytest.mark.parametrize("d,f,E,K,bits,T", [(256, 128, 8, 2, 4, 40), (512, 256, 16, 4, 2, 33)])
+def test_expert_order_fp32_accumulate_matches_oracle(d, f, E, K, bits, T):
+    # the Inkling batched expert application: fp32 accumulator, fp32 pair weights, experts in ascending order
+    import torch
+    from mference_b200.moe import MoE
+    W = O.LayerWeights(d, f, E, K, bits=bits, shared=False)
+    x = make_x("x.ink", T, d)
+    lg = O.router_logits(x, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, K)
+    w32 = (O.f16_to_f32(w).reshape(T, K) * np.float32(1.5)).astype(np.float32)    # fp32 weights the fp16 path could not hold exactly
+    acc0 = np.linspace(-1.0, 1.0, T * d, dtype=np.float32).reshape(T, d)          # e.g. the shared expert's contribution
+    moe = MoE(d, f, E, K, bits=bits, shared_bits=0, max_tokens=T)
+    lw = upload_layer(W)
+    xd = to_dev16(x, O.DT_BF16)
+    idxd = torch.from_numpy(idx.view(np.int32)).cuda()
+    wd = torch.from_numpy(w.view(np.int16)).cuda().view(torch.float16)
+    sp, _, _, groups, n_groups = moe.encode_group(idxd, wd)
+    acc = torch.from_numpy(acc0.copy()).cuda()
+    moe.encode_prefill_accumulate_f32(lw, xd, sp, groups, n_groups, torch.from_numpy(w32).cuda(), acc)
+    torch.cuda.synchronize()
+    ref = O.inkling_accumulate(W, x, O.DT_BF16, idx.reshape(T, K), w32, acc0)
+    got = acc.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, ref) <= TOL_REL_L2, O.rel_l2(got, ref)
+    assert O.rel_l2(got - acc0, ref - acc0) <= TOL_REL_L2
+
+
 # ---- tensor-core (tcgen05 / TMEM) grouped GEMM ---------------------------------------------------------------
 # d and f multiples of 512; token counts chosen to give groups below 16 rows, around a TMA box, and above one
 # 256-row MMA tile (several passes per expert).
