@@ -25,6 +25,17 @@ public final class PrefillGroupedRoutedMoE {
                                              groupCount, partial))
     }
 
+    /// The Inkling batched expert application (inkling_prefill_expert_act + inkling_prefill_expert_down_accum,
+    /// prefill.metal:654-746): acc (Float, rows x d, read and written) += the routed experts' rows, expert by expert in
+    /// ascending expert order, with Float pair weights (rows x topK).
+    public func encodeExpertAccumulateFloat32(stream: MfbStream, weights: inout LayerWeights, x: UnsafeRawPointer, rows: Int,
+                                              sortedPairs: UnsafePointer<mfb_pair>, groups: UnsafePointer<mfb_group>,
+                                              groupCount: UnsafePointer<UInt32>, pairWeights: UnsafePointer<Float>,
+                                              acc: UnsafeMutablePointer<Float>) throws {
+        try mfbCheck(mfb_moe_prefill_accumulate_f32(moe.raw, stream, &weights, x, UInt32(moe.d), UInt32(rows), sortedPairs, groups,
+                                                    groupCount, pairWeights, acc))
+    }
+
     /// encodeReduceTokenMajor (PrefillMoE.swift:11-38).
     public func encodeReduceTokenMajor(stream: MfbStream, partial: UnsafePointer<Float>, routingWeights: UnsafePointer<UInt16>,
                                        rows: Int, residual: UnsafeRawPointer?, y: UnsafeMutableRawPointer) throws {
