@@ -192,6 +192,67 @@ def test_pair_partials_and_reduce_equal_layer():
     assert O.rel_l2(h2, y) < 1e-6
 
 
+def test_gate_group_32_layout_and_dequant():
+    # DeepSeek V4's gate_proj: one scale and bias per 32 elements (routedGateGroupSize, ModelExpertIO.swift:118-135); only
+    # the gate's scale and bias arrays grow, the codes and the other two matrices keep their sizes
+    d, f = 128, 64
+    o64, b64 = O.make_offsets(2, d, f, 64)
+    o32, b32 = O.make_offsets(2, d, f, 32)
+    assert o32.gate_w == o64.gate_w and o32.gate_s == o64.gate_s
+    assert o32.gate_b - o32.gate_s == 2 * (o64.gate_b - o64.gate_s)
+    assert b32 - b64 == 2 * (d * f // 64 * 2)
+    blob = O.synth_expert(0xB2000001, 0, 3, 2, O.DT_BF16, d, f, 32)
+    codes = blob[o32.gate_w:o32.gate_s]
+    sc = blob[o32.gate_s:o32.gate_b].view(np.uint16)
+    bi = blob[o32.gate_b:o32.up_w].view(np.uint16)
+    w32 = O.dequant_rows(codes, sc, bi, 2, f, d, scale_dtype=O.DT_BF16, group_size=32)
+    # element (r, c) = code * scale[r, c // 32] + bias[r, c // 32], 2-bit codes LSB first
+    r, c = 5, 77
+    byte = codes[r * d // 4 + c // 4]
+    q = (int(byte) >> (2 * (c % 4))) & 3
+    g = r * (d // 32) + c // 32
+    want = np.float32(np.float32(q) * O.bf16_to_f32(sc[g:g + 1])[0]) + O.bf16_to_f32(bi[g:g + 1])[0]
+    assert w32[r, c] == np.float32(want)
+    # the layer function reads a pool of such blobs with the gate group taken from the layer
+    W = O.LayerWeights(d, f, 6, 2, bits=2, shared_bits=4, scale_dtype=O.DT_BF16, gate_group_size=32)
+    x = make_x("x.g32", 3, d)
+    lg = O.router_logits(x, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, 2)
+    y = O.moe_layer(W, x, O.DT_BF16, idx, w)
+    assert np.isfinite(y).all() and y.shape == (3, d)
+
+
+def test_int8_shared_expert_rows_are_plain_bytes():
+    # SharedExpertInt8: unsigned byte codes, one scale and bias per 64 elements
+    d, f = 128, 64
+    off, total = O.make_offsets(8, d, f)
+    assert off.gate_s - off.gate_w == d * f
+    blob = O.synth_expert(0xB2000001, 0, -1, 8, O.DT_BF16, d, f)
+    codes = blob[off.down_w:off.down_s]
+    sc = blob[off.down_s:off.down_b].view(np.uint16)
+    bi = blob[off.down_b:total].view(np.uint16)
+    w8 = O.dequant_rows(codes, sc, bi, 8, d, f, scale_dtype=O.DT_BF16)
+    r, c = 17, 33
+    g = r * (f // 64) + c // 64
+    want = np.float32(np.float32(codes[r * f + c]) * O.bf16_to_f32(sc[g:g + 1])[0]) + O.bf16_to_f32(bi[g:g + 1])[0]
+    assert w8[r, c] == np.float32(want)
+
+
+def test_inkling_accumulate_is_expert_ordered():
+    # inkling_prefill_expert_down_accum: experts in ascending order, fp32 accumulator and weights; with weights whose
+    # ranks are not in expert order the result differs from the rank-ordered reduce only by rounding
+    W = O.LayerWeights(128, 64, 6, 3, shared=False)
+    x = make_x("x.ink", 4, 128)
+    lg = O.router_logits(x, O.DT_BF16, W.router)
+    idx, w = O.topk_softmax(lg, 3)
+    w32 = O.f16_to_f32(w).reshape(4, 3).astype(np.float32)
+    acc = O.inkling_accumulate(W, x, O.DT_BF16, idx.reshape(4, 3), w32)
+    y = O.moe_layer(W, x, O.DT_BF16, idx, w)          # rank order, no residual, no shared expert
+    assert O.rel_l2(acc, y) < 1e-5
+    acc2 = O.inkling_accumulate(W, x, O.DT_BF16, idx.reshape(4, 3), w32, acc0=np.ones((4, 128), dtype=np.float32))
+    assert np.abs((acc2 - acc) - 1.0).max() < 1e-3
+
+
 def test_rmsnorm_definition():
     x = O.bf16_to_f32(make_x("h", 3, 128))
     out = O.rmsnorm(x, None, 1e-6)
